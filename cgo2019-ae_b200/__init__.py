@@ -1,0 +1,239 @@
+"""Host-side mirror of the contraction operator over the C-ABI library.
+
+The reference is driven by one expression line per contraction
+(``t3 [a,312,b,24,c,296] += sum(d,312) * t2 [d,c,a] * v2 [b,d];``,
+cogent/input_strings/tccg/input_tccg_02.in:4) that ``tc_code_generator.py``
+turns into a ``.cu`` file with the entry ``sd_t_d2_fusion_``
+(cogent/src/codes/kernels/tc_interface.py:1444-1598).  Here the same line makes
+a :class:`Plan`; ``Plan.execute`` enqueues the hand-written sm_100a kernels on
+device tensors.  Everything numeric happens inside ``libtc_b200.so``; there is
+no Python or CPU compute path, and a missing library is an error.
+"""
+import ctypes
+import json
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtc_b200.so")
+
+F64, F32 = 0, 1
+PATH_AUTO, PATH_DMMA, PATH_DFMA, PATH_FFMA, PATH_3XTF32 = 0, 1, 2, 3, 4
+TENSOR_OUT, TENSOR_LEFT, TENSOR_RIGHT = 0, 1, 2
+
+PEAK_NAMES = {0: "dmma_m8n8k4", 1: "dmma_m16n8k4", 2: "dmma_m16n8k8", 3: "dmma_m16n8k16",
+              4: "dfma", 5: "ffma", 6: "tf32_mma_sync"}
+
+
+class TcError(RuntimeError):
+    def __init__(self, status, where, detail=""):
+        self.status = status
+        msg = "%s failed: %s (status %d)" % (where, _status_string(status), status)
+        if detail:
+            msg += " -- " + detail
+        super().__init__(msg)
+
+
+class Options(ctypes.Structure):
+    _fields_ = [("path", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
+                ("split_k", ctypes.c_int), ("reserved", ctypes.c_int * 4)]
+
+
+_lib = None
+
+# name -> (restype, argtypes); every symbol include/tc_b200.h declares.
+_SIGNATURES = {
+    "tc_expr_describe": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t]),
+    "tc_plan_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(Options),
+                                      ctypes.POINTER(ctypes.c_void_p)]),
+    "tc_plan_set_extents": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                           ctypes.POINTER(ctypes.c_int64)]),
+    "tc_plan_set_strides": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                           ctypes.POINTER(ctypes.c_int64)]),
+    "tc_plan_commit": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_plan_destroy": (None, [ctypes.c_void_p]),
+    "tc_plan_describe": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]),
+    "tc_plan_cost": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double),
+                                    ctypes.POINTER(ctypes.c_double)]),
+    "tc_plan_launches": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_plan_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
+    "tc_execute": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                  ctypes.c_void_p]),
+    "tc_execute_ws": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                     ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "tc_execute_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
+    "tc_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "tc_last_cuda_error": (ctypes.c_char_p, []),
+    "tc_version": (ctypes.c_char_p, []),
+    "tc_fill_uniform": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint64,
+                                       ctypes.c_int, ctypes.c_int64, ctypes.c_void_p]),
+    "tc_axpy": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+                               ctypes.c_double, ctypes.c_void_p]),
+    "tc_peak_measure": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
+    "tc_peak_measure_rmw": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(ctypes.c_double)]),
+}
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: run `python %s` (or __graft_entry__.build()) first; "
+                              "there is no fallback path" % (LIB_PATH, os.path.join(_HERE, "build.py")))
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def _status_string(status):
+    try:
+        return lib().tc_status_string(status).decode()
+    except Exception:  # pragma: no cover - library missing
+        return "?"
+
+
+def _check(status, where):
+    if status != 0:
+        detail = lib().tc_last_cuda_error().decode() if status == 5 else ""
+        raise TcError(status, where, detail)
+
+
+def parse(expr):
+    """Parsed form of one expression line (dict), or raises TcError(status 1 / 3)."""
+    buf = ctypes.create_string_buffer(8192)
+    st = lib().tc_expr_describe(expr.encode(), buf, len(buf))
+    if st != 0:
+        raise TcError(st, "tc_expr_describe", json.loads(buf.value.decode() or "{}").get("error", ""))
+    return json.loads(buf.value.decode())
+
+
+def _ptr(x):
+    """Device/host address of a torch tensor, numpy array or raw int."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x)
+    if hasattr(x, "data_ptr"):
+        return ctypes.c_void_p(x.data_ptr())
+    if hasattr(x, "ctypes"):
+        return ctypes.c_void_p(x.ctypes.data)
+    raise TypeError("expected a tensor, array or address, got %r" % type(x))
+
+
+class Plan:
+    """One contraction: expression + dtype (+ extents, strides, options)."""
+
+    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None):
+        self._h = ctypes.c_void_p()
+        opt = Options()
+        opt.path = path
+        if tile:
+            opt.tile_m, opt.tile_n = tile
+        opt.split_k = split_k
+        self.expr = expr
+        self.dtype = dtype
+        _check(lib().tc_plan_create(expr.encode(), dtype, ctypes.byref(opt), ctypes.byref(self._h)), "tc_plan_create")
+        if extents:
+            self.set_extents(extents)
+
+    def set_extents(self, extents):
+        names = list(extents)
+        arr_n = (ctypes.c_char_p * len(names))(*[n.encode() for n in names])
+        arr_e = (ctypes.c_int64 * len(names))(*[int(extents[n]) for n in names])
+        _check(lib().tc_plan_set_extents(self._h, len(names), arr_n, arr_e), "tc_plan_set_extents")
+        return self
+
+    def set_strides(self, tensor, strides):
+        arr = (ctypes.c_int64 * len(strides))(*[int(s) for s in strides])
+        _check(lib().tc_plan_set_strides(self._h, tensor, len(strides), arr), "tc_plan_set_strides")
+        return self
+
+    def commit(self):
+        _check(lib().tc_plan_commit(self._h), "tc_plan_commit")
+        return self
+
+    def describe(self):
+        buf = ctypes.create_string_buffer(16384)
+        st = lib().tc_plan_describe(self._h, buf, len(buf))
+        if st != 0:
+            raise TcError(st, "tc_plan_describe", json.loads(buf.value.decode() or "{}").get("error", ""))
+        return json.loads(buf.value.decode())
+
+    def cost(self):
+        f, b = ctypes.c_double(), ctypes.c_double()
+        _check(lib().tc_plan_cost(self._h, ctypes.byref(f), ctypes.byref(b)), "tc_plan_cost")
+        return f.value, b.value
+
+    @property
+    def launches(self):
+        return lib().tc_plan_launches(self._h)
+
+    def workspace_bytes(self):
+        n = ctypes.c_size_t()
+        _check(lib().tc_plan_workspace_bytes(self._h, ctypes.byref(n)), "tc_plan_workspace_bytes")
+        return n.value
+
+    def execute(self, C, A, B, stream=None, workspace=None):
+        """Enqueue C (op)= sum A*B on device tensors (torch CUDA tensors or raw device addresses)."""
+        s = ctypes.c_void_p(stream) if stream else None
+        if workspace is None:
+            _check(lib().tc_execute(self._h, _ptr(C), _ptr(A), _ptr(B), s), "tc_execute")
+        else:
+            nbytes = workspace.numel() * workspace.element_size()
+            _check(lib().tc_execute_ws(self._h, _ptr(C), _ptr(A), _ptr(B), _ptr(workspace), nbytes, s), "tc_execute_ws")
+
+    def execute_host(self, C, A, B):
+        """Blocking call on host arrays (numpy, C-contiguous 1-D storage in column-major element order)."""
+        _check(lib().tc_execute_host(self._h, _ptr(C), _ptr(A), _ptr(B)), "tc_execute_host")
+
+    def close(self):
+        if self._h:
+            lib().tc_plan_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fill_uniform(t, seed, tensor_id, first_index=0, stream=None):
+    """Fills a CUDA tensor with the seeded uniform[-1,1) stream for (seed, tensor_id)."""
+    import torch
+    dt = F64 if t.dtype == torch.float64 else F32
+    s = ctypes.c_void_p(stream) if stream else None
+    _check(lib().tc_fill_uniform(_ptr(t), t.numel(), dt, seed, tensor_id, first_index, s), "tc_fill_uniform")
+    return t
+
+
+def axpy(y, x, alpha=1.0, stream=None):
+    import torch
+    dt = F64 if y.dtype == torch.float64 else F32
+    s = ctypes.c_void_p(stream) if stream else None
+    _check(lib().tc_axpy(_ptr(y), _ptr(x), y.numel(), dt, alpha, s), "tc_axpy")
+    return y
+
+
+def measure_peaks(which=(0, 4, 5), iters=4096, ctas_per_sm=2):
+    """TFLOP/s of the arithmetic pipes (register-only loops) on the current device."""
+    out = {}
+    for w in which:
+        v = ctypes.c_double()
+        _check(lib().tc_peak_measure(w, iters, ctas_per_sm, ctypes.byref(v)), "tc_peak_measure")
+        out[PEAK_NAMES[w]] = v.value
+    return out
+
+
+def measure_rmw(nbytes=4 << 30):
+    v = ctypes.c_double()
+    _check(lib().tc_peak_measure_rmw(nbytes, ctypes.byref(v)), "tc_peak_measure_rmw")
+    return v.value

@@ -1,0 +1,362 @@
+// C ABI: plan / execute / free, the seeded input generator and small utilities.
+// Declarations and the reference interfaces they replace are in include/tc_b200.h.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "tc_inst.cuh"
+#include "tc_internal.h"
+
+// ---------------------------------------------------------------- errors ----
+static thread_local char g_cuda_error[256] = "";
+
+void tc_note_cuda_error(int code, const char* what) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%d)", what, cudaGetErrorString((cudaError_t)code), code);
+}
+
+extern "C" const char* tc_last_cuda_error(void) { return g_cuda_error; }
+
+extern "C" const char* tc_status_string(int s) {
+  switch (s) {
+    case TC_OK: return "ok";
+    case TC_ERR_PARSE: return "expression rejected by the grammar";
+    case TC_ERR_INVALID_ARG: return "invalid argument";
+    case TC_ERR_UNSUPPORTED: return "unsupported contraction";
+    case TC_ERR_EXTENT: return "bad extent or stride";
+    case TC_ERR_CUDA: return "CUDA error";
+    case TC_ERR_ALIGNMENT: return "misaligned tensor pointer";
+    case TC_ERR_STATE: return "call order violated";
+    case TC_ERR_WORKSPACE: return "workspace missing or too small";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* tc_version(void) { return "tc_b200 0.1 (sm_100a)"; }
+
+static void copy_out(const std::string& s, char* buf, size_t cap) {
+  if (!buf || cap == 0) return;
+  const size_t n = std::min(cap - 1, s.size());
+  std::memcpy(buf, s.data(), n);
+  buf[n] = '\0';
+}
+
+// ------------------------------------------------------------ expression ----
+extern "C" int tc_expr_describe(const char* expr, char* buf, size_t cap) {
+  TcExpr e;
+  std::string why;
+  const int st = tc_parse_expr(expr, &e, &why);
+  copy_out(st == TC_OK ? tc_expr_to_json(e) : "{\"error\":\"" + why + "\"}", buf, cap);
+  return st;
+}
+
+// -------------------------------------------------------- kernel dispatch ----
+extern "C" {
+int tc_inst_dmma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_dmma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_dfma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_dfma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_ffma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_ffma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+}
+
+static tc_inst_fn pick_inst(const TcKernelChoice& c) {
+  const bool big = c.bm == 128;
+  if (c.dtype == TC_F64 && c.math == TC_MATH_DMMA) return big ? tc_inst_dmma_128 : tc_inst_dmma_64;
+  if (c.dtype == TC_F64) return big ? tc_inst_dfma_128 : tc_inst_dfma_64;
+  return big ? tc_inst_ffma_128 : tc_inst_ffma_64;
+}
+
+int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk) {
+  if (bk) *bk = tc_tile_bk(c.dtype, c.math);
+  return pick_inst(c)(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
+}
+
+int tc_kernels_prepare(const TcKernelChoice& c) {
+  // Both loader variants of each operand: a misaligned base pointer at execute
+  // time demotes 16-byte loads to element loads.
+  for (int vx = 0; vx <= (c.vec_x ? 1 : 0); ++vx)
+    for (int vy = 0; vy <= (c.vec_y ? 1 : 0); ++vy) {
+      const int st = pick_inst(c)(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
+      if (st != TC_OK) return st;
+    }
+  return TC_OK;
+}
+
+int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, const void* X, const void* Y,
+                          cudaStream_t stream) {
+  const TcKernelChoice& c = p.choice;
+  TcKernelArgs a = args;
+  // Alignment-driven demotions (base pointers are the only run-time unknowns).
+  const bool x16 = (reinterpret_cast<uintptr_t>(X) & 15) == 0, y16 = (reinterpret_cast<uintptr_t>(Y) & 15) == 0;
+  const uintptr_t cu = reinterpret_cast<uintptr_t>(C);
+  if ((cu & 15) != 0) a.vec_c = 1;
+  const int vx = c.vec_x && x16, vy = c.vec_y && y16;
+  int st = pick_inst(c)(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
+  if (st != TC_OK) return st;
+  if (a.ksplit > 1) {
+    const unsigned grid = a.tiles_m * a.tiles_n;
+    if (p.dtype == TC_F64) {
+      if (c.bm == 128) tck::tc_combine_kernel<double, 128, 128><<<grid, 256, 0, stream>>>(a, static_cast<double*>(C));
+      else tck::tc_combine_kernel<double, 64, 64><<<grid, 256, 0, stream>>>(a, static_cast<double*>(C));
+    } else {
+      if (c.bm == 128) tck::tc_combine_kernel<float, 128, 128><<<grid, 256, 0, stream>>>(a, static_cast<float*>(C));
+      else tck::tc_combine_kernel<float, 64, 64><<<grid, 256, 0, stream>>>(a, static_cast<float*>(C));
+    }
+    TC_CUDA_OK(cudaGetLastError());
+  }
+  return TC_OK;
+}
+
+// ------------------------------------------------------------------ plan ----
+extern "C" int tc_plan_create(const char* expr, int dtype, const tc_options* options, tc_plan** out) {
+  if (!expr || !out) return TC_ERR_INVALID_ARG;
+  *out = nullptr;
+  if (dtype != TC_F64 && dtype != TC_F32) return TC_ERR_INVALID_ARG;
+  TcExpr e;
+  std::string why;
+  const int st = tc_parse_expr(expr, &e, &why);
+  if (st != TC_OK) return st;
+  tc_plan* p = new (std::nothrow) tc_plan();
+  if (!p) return TC_ERR_INVALID_ARG;
+  p->expr = e;
+  p->dtype = dtype;
+  if (options) p->opt = *options;
+  if (p->opt.path < TC_PATH_AUTO || p->opt.path > TC_PATH_3XTF32 || p->opt.split_k < 0) {
+    delete p;
+    return TC_ERR_INVALID_ARG;
+  }
+  for (size_t i = 0; i < e.out_idx.size(); ++i) { p->idx_names.push_back(e.out_idx[i]); p->idx_extent.push_back(e.out_ext[i]); }
+  for (size_t i = 0; i < e.sum_idx.size(); ++i) { p->idx_names.push_back(e.sum_idx[i]); p->idx_extent.push_back(e.sum_ext[i]); }
+  *out = p;
+  return TC_OK;
+}
+
+extern "C" int tc_plan_set_extents(tc_plan* p, int n, const char* const* names, const int64_t* extents) {
+  if (!p || n < 0 || (n > 0 && (!names || !extents))) return TC_ERR_INVALID_ARG;
+  if (p->committed) return TC_ERR_STATE;
+  std::vector<int64_t> next = p->idx_extent;
+  for (int i = 0; i < n; ++i) {
+    if (!names[i]) return TC_ERR_INVALID_ARG;
+    if (extents[i] <= 0) return TC_ERR_EXTENT;
+    size_t j = 0;
+    for (; j < p->idx_names.size(); ++j)
+      if (p->idx_names[j] == names[i]) break;
+    if (j == p->idx_names.size()) return TC_ERR_INVALID_ARG;
+    next[j] = extents[i];
+  }
+  p->idx_extent = next;
+  return TC_OK;
+}
+
+extern "C" int tc_plan_set_strides(tc_plan* p, int tensor, int n, const int64_t* strides) {
+  if (!p || tensor < 0 || tensor > 2 || n < 0 || (n > 0 && !strides)) return TC_ERR_INVALID_ARG;
+  if (p->committed) return TC_ERR_STATE;
+  const size_t rank = tensor == 0 ? p->expr.out_idx.size() : tensor == 1 ? p->expr.left_idx.size() : p->expr.right_idx.size();
+  if ((size_t)n != rank) return TC_ERR_INVALID_ARG;
+  for (int i = 0; i < n; ++i)
+    if (strides[i] <= 0) return TC_ERR_EXTENT;
+  p->strides[tensor].assign(strides, strides + n);
+  p->custom_strides[tensor] = true;
+  return TC_OK;
+}
+
+extern "C" int tc_plan_commit(tc_plan* p) {
+  if (!p) return TC_ERR_INVALID_ARG;
+  if (p->committed) return TC_OK;
+  int st = tc_plan_build(p, &p->why);
+  if (st != TC_OK) return st;
+  int dev = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  st = tc_kernels_prepare(p->choice);
+  if (st != TC_OK) return st;
+  const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
+  TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));
+  TC_CUDA_OK(cudaMemcpy(p->d_koff, p->h_koff_x.data(), kb, cudaMemcpyHostToDevice));
+  TC_CUDA_OK(cudaMemcpy(static_cast<char*>(p->d_koff) + kb, p->h_koff_y.data(), kb, cudaMemcpyHostToDevice));
+  p->args.koff_x = static_cast<const int64_t*>(p->d_koff);
+  p->args.koff_y = p->args.koff_x + p->h_koff_x.size();
+  if (p->ws_bytes) TC_CUDA_OK(cudaMalloc(&p->d_ws, p->ws_bytes));
+  p->device = dev;
+  p->committed = true;
+  return TC_OK;
+}
+
+extern "C" void tc_plan_destroy(tc_plan* p) {
+  if (!p) return;
+  if (p->d_koff) cudaFree(p->d_koff);
+  if (p->d_ws) cudaFree(p->d_ws);
+  delete p;
+}
+
+extern "C" int tc_plan_describe(const tc_plan* p, char* buf, size_t cap) {
+  if (!p) return TC_ERR_INVALID_ARG;
+  if (p->committed) { copy_out(tc_plan_to_json(*p), buf, cap); return TC_OK; }
+  // Not committed yet: run the host-side planner on a copy (needs no GPU).
+  tc_plan tmp = *p;
+  std::string why;
+  const int st = tc_plan_build(&tmp, &why);
+  if (st != TC_OK) { copy_out("{\"error\":\"" + why + "\"}", buf, cap); return st; }
+  tmp.committed = true;
+  std::string js = tc_plan_to_json(tmp);
+  tmp.committed = false;
+  copy_out(js, buf, cap);
+  return TC_OK;
+}
+
+extern "C" int tc_plan_cost(const tc_plan* p, double* flops, double* bytes) {
+  if (!p) return TC_ERR_INVALID_ARG;
+  tc_plan tmp = *p;
+  if (!p->committed) {
+    std::string why;
+    const int st = tc_plan_build(&tmp, &why);
+    if (st != TC_OK) return st;
+  }
+  if (flops) *flops = tmp.flops;
+  if (bytes) *bytes = tmp.bytes;
+  return TC_OK;
+}
+
+extern "C" int tc_plan_launches(const tc_plan* p) { return p && p->committed ? p->launches : -1; }
+
+extern "C" int tc_plan_workspace_bytes(const tc_plan* p, size_t* bytes) {
+  if (!p || !bytes) return TC_ERR_INVALID_ARG;
+  if (!p->committed) return TC_ERR_STATE;
+  *bytes = p->ws_bytes;
+  return TC_OK;
+}
+
+// --------------------------------------------------------------- execute ----
+static int execute_impl(tc_plan* p, void* C, const void* A, const void* B, void* ws, size_t ws_bytes, void* stream) {
+  if (!p || !C || !A || !B) return TC_ERR_INVALID_ARG;
+  if (!p->committed) {
+    const int st = tc_plan_commit(p);
+    if (st != TC_OK) return st;
+  }
+  int dev = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev != p->device) return TC_ERR_STATE;
+  const uintptr_t es = p->dtype == TC_F64 ? 8 : 4;
+  if ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & (es - 1))
+    return TC_ERR_ALIGNMENT;
+  TcKernelArgs a = p->args;
+  if (a.ksplit > 1) {
+    if (!ws || ws_bytes < p->ws_bytes || (reinterpret_cast<uintptr_t>(ws) & 15)) return TC_ERR_WORKSPACE;
+    a.ws = ws;
+  }
+  const void* X = p->swapped ? B : A;
+  const void* Y = p->swapped ? A : B;
+  return tc_launch_contraction(*p, a, C, X, Y, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tc_execute(tc_plan* p, void* C, const void* A, const void* B, void* stream) {
+  if (p && !p->committed) {
+    const int st = tc_plan_commit(p);
+    if (st != TC_OK) return st;
+  }
+  return execute_impl(p, C, A, B, p ? p->d_ws : nullptr, p ? p->ws_bytes : 0, stream);
+}
+
+extern "C" int tc_execute_ws(tc_plan* p, void* C, const void* A, const void* B, void* ws, size_t ws_bytes, void* stream) {
+  return execute_impl(p, C, A, B, ws, ws_bytes, stream);
+}
+
+extern "C" int tc_execute_host(tc_plan* p, void* C, const void* A, const void* B) {
+  if (!p || !C || !A || !B) return TC_ERR_INVALID_ARG;
+  if (!p->committed) {
+    const int st = tc_plan_commit(p);
+    if (st != TC_OK) return st;
+  }
+  const size_t es = p->dtype == TC_F64 ? 8 : 4;
+  void *dC = nullptr, *dA = nullptr, *dB = nullptr;
+  int st = TC_OK;
+  auto cleanup = [&]() {
+    if (dC) cudaFree(dC);
+    if (dA) cudaFree(dA);
+    if (dB) cudaFree(dB);
+  };
+#define TC_HOST_OK(call)                                   \
+  do {                                                     \
+    cudaError_t e_ = (call);                               \
+    if (e_ != cudaSuccess) {                               \
+      tc_note_cuda_error((int)e_, #call);                  \
+      cleanup();                                           \
+      return TC_ERR_CUDA;                                  \
+    }                                                      \
+  } while (0)
+  TC_HOST_OK(cudaMalloc(&dC, p->size_c * es));
+  TC_HOST_OK(cudaMalloc(&dA, p->size_a * es));
+  TC_HOST_OK(cudaMalloc(&dB, p->size_b * es));
+  cudaStream_t s = nullptr;
+  TC_HOST_OK(cudaMemcpyAsync(dA, A, p->size_a * es, cudaMemcpyHostToDevice, s));
+  TC_HOST_OK(cudaMemcpyAsync(dB, B, p->size_b * es, cudaMemcpyHostToDevice, s));
+  if (p->args.beta || p->size_c != p->count_c)
+    TC_HOST_OK(cudaMemcpyAsync(dC, C, p->size_c * es, cudaMemcpyHostToDevice, s));
+  st = execute_impl(p, dC, dA, dB, p->d_ws, p->ws_bytes, s);
+  if (st != TC_OK) { cleanup(); return st; }
+  TC_HOST_OK(cudaMemcpyAsync(C, dC, p->size_c * es, cudaMemcpyDeviceToHost, s));
+  TC_HOST_OK(cudaStreamSynchronize(s));
+#undef TC_HOST_OK
+  cleanup();
+  return TC_OK;
+}
+
+// -------------------------------------------------------- seeded inputs ----
+namespace {
+
+__host__ __device__ inline uint64_t splitmix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void fill_kernel(T* dst, int64_t count, uint64_t key, int64_t first) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < count; i += stride) {
+    const uint64_t x = splitmix64(key ^ (uint64_t)(first + i));
+    if constexpr (sizeof(T) == 8) dst[i] = (double)(x >> 11) * (1.0 / 9007199254740992.0) * 2.0 - 1.0;
+    else dst[i] = (float)(x >> 40) * (1.0f / 16777216.0f) * 2.0f - 1.0f;
+  }
+}
+
+template <typename T>
+__global__ void axpy_kernel(T* y, const T* x, int64_t count, T alpha) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < count; i += stride) y[i] += alpha * x[i];
+}
+
+int grid_for(int64_t count) {
+  int64_t g = (count + 255) / 256;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(g, 148 * 16));
+}
+
+}  // namespace
+
+extern "C" int tc_fill_uniform(void* dst, int64_t count, int dtype, uint64_t seed, int tensor_id, int64_t first_index,
+                               void* stream) {
+  if (!dst || count < 0 || tensor_id < 0 || tensor_id > 15 || (dtype != TC_F64 && dtype != TC_F32)) return TC_ERR_INVALID_ARG;
+  if (count == 0) return TC_OK;
+  const uint64_t key = (seed * 0x9E3779B97F4A7C15ull) ^ ((uint64_t)tensor_id << 60);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == TC_F64) fill_kernel<double><<<grid_for(count), 256, 0, s>>>(static_cast<double*>(dst), count, key, first_index);
+  else fill_kernel<float><<<grid_for(count), 256, 0, s>>>(static_cast<float*>(dst), count, key, first_index);
+  TC_CUDA_OK(cudaGetLastError());
+  return TC_OK;
+}
+
+extern "C" int tc_axpy(void* y, const void* x, int64_t count, int dtype, double alpha, void* stream) {
+  if (!y || !x || count < 0 || (dtype != TC_F64 && dtype != TC_F32)) return TC_ERR_INVALID_ARG;
+  if (count == 0) return TC_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == TC_F64) axpy_kernel<double><<<grid_for(count), 256, 0, s>>>(static_cast<double*>(y), static_cast<const double*>(x), count, alpha);
+  else axpy_kernel<float><<<grid_for(count), 256, 0, s>>>(static_cast<float*>(y), static_cast<const float*>(x), count, (float)alpha);
+  TC_CUDA_OK(cudaGetLastError());
+  return TC_OK;
+}

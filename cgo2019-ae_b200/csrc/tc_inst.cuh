@@ -1,0 +1,46 @@
+// Instantiation helper: one translation unit per (arithmetic, dtype, CTA tile)
+// so the variants compile in parallel.  Each unit exports one dispatcher that
+// selects the loader variant (16-byte loads along the external index of X / Y
+// or element-wise loads) and either launches, prepares (opt-in shared memory)
+// or reports the launch shape.
+#pragma once
+#include "tc_kernels.cuh"
+
+enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2 };
+
+typedef int (*tc_inst_fn)(int vec_x, int vec_y, const TcKernelArgs* args, void* C, const void* X, const void* Y,
+                          cudaStream_t stream, int mode, int* threads, int* smem_bytes);
+
+namespace tck {
+
+template <class CF>
+int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
+                int* threads, int* smem_bytes) {
+  using T = typename CF::T;
+  auto kern = tc_contract_kernel<CF>;
+  if (mode == TC_INST_QUERY) {
+    if (threads) *threads = CF::THREADS;
+    if (smem_bytes) *smem_bytes = CF::SMEM_BYTES;
+    return TC_OK;
+  }
+  if (mode == TC_INST_PREPARE) {
+    TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CF::SMEM_BYTES));
+    return TC_OK;
+  }
+  const unsigned grid = a->tiles_m * a->tiles_n * a->ksplit;
+  kern<<<grid, CF::THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<T*>(C), static_cast<const T*>(X),
+                                                       static_cast<const T*>(Y));
+  TC_CUDA_OK(cudaGetLastError());
+  return TC_OK;
+}
+
+}  // namespace tck
+
+#define TC_DEFINE_INST(NAME, T, MATH, BM, BN, WMN, WNN, STAGES)                                                  \
+  extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,              \
+                      cudaStream_t s, int mode, int* threads, int* smem) {                                       \
+    if (vx && vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, true, true>>(a, C, X, Y, s, mode, threads, smem);   \
+    if (vx) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, true, false>>(a, C, X, Y, s, mode, threads, smem);        \
+    if (vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, false, true>>(a, C, X, Y, s, mode, threads, smem);        \
+    return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, false, false>>(a, C, X, Y, s, mode, threads, smem);               \
+  }

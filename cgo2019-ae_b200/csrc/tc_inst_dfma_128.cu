@@ -1,0 +1,2 @@
+#include "tc_inst.cuh"
+TC_DEFINE_INST(tc_inst_dfma_128, double, TC_MATH_SIMT, 128, 128, 1, 1, 3)

@@ -1,0 +1,2 @@
+#include "tc_inst.cuh"
+TC_DEFINE_INST(tc_inst_dfma_64, double, TC_MATH_SIMT, 64, 64, 1, 1, 4)

@@ -1,0 +1,131 @@
+// Internal declarations shared by the parser, the planner, the kernels and the C ABI.
+#ifndef TC_INTERNAL_H_
+#define TC_INTERNAL_H_
+
+#include <stdint.h>
+#include <stddef.h>
+#include <string>
+#include <vector>
+
+#include "../../include/tc_b200.h"
+
+#ifdef __CUDACC__
+#include <cuda_runtime.h>
+#endif
+
+// ---------------------------------------------------------------- errors ----
+void tc_note_cuda_error(int code, const char* what);  // stores text for tc_last_cuda_error()
+
+#define TC_CUDA_OK(call)                                   \
+  do {                                                     \
+    cudaError_t tc_e_ = (call);                            \
+    if (tc_e_ != cudaSuccess) {                            \
+      tc_note_cuda_error((int)tc_e_, #call);               \
+      return TC_ERR_CUDA;                                  \
+    }                                                      \
+  } while (0)
+
+// ------------------------------------------------------------ expression ----
+// One parsed line of the contraction grammar
+// (reference: cogent/src/algs/bases/tc_gen_inputs.py:28-108).
+struct TcExpr {
+  std::string out_name, left_name, right_name;
+  std::vector<std::string> out_idx;    // output indices, first = fastest
+  std::vector<std::string> sum_idx;    // contraction indices in sum(...) order
+  std::vector<std::string> left_idx;   // left input's indices, first = fastest
+  std::vector<std::string> right_idx;  // right input's indices
+  std::vector<int64_t> out_ext;        // extents written next to out_idx
+  std::vector<int64_t> sum_ext;        // extents written inside sum(...)
+  int op = 0;                          // +1 for "+=", -1 for "-=", 0 for "="
+};
+
+// Returns TC_OK / TC_ERR_PARSE / TC_ERR_UNSUPPORTED; `why` gets a one-line reason.
+int tc_parse_expr(const char* line, TcExpr* out, std::string* why);
+std::string tc_expr_to_json(const TcExpr& e);
+
+// ------------------------------------------------------------------ plan ----
+constexpr int TC_MAX_DIMS = 8;  // fused dimensions per index class
+
+// One index class (rows of the left operand, rows of the right operand) as a
+// mixed-radix number: dimension 0 is the fastest digit of the flattened index.
+struct TcDims {
+  int32_t n;
+  uint32_t extent[TC_MAX_DIMS];
+  int64_t s_in[TC_MAX_DIMS];   // element stride in the input that carries the class
+  int64_t s_out[TC_MAX_DIMS];  // element stride in the output
+};
+
+// Everything a kernel launch needs besides the three tensor pointers.
+// "M" is the external class of operand X (the one holding the output's fastest
+// index after the planner's optional operand swap), "N" the class of operand Y.
+struct TcKernelArgs {
+  TcDims M, N;
+  uint32_t Mflat, Nflat, Kflat;
+  uint32_t tiles_m, tiles_n;
+  uint32_t k_chunk;  // flattened contraction range per K slice (multiple of the K step)
+  uint32_t ksplit;   // number of K slices (1 = the kernel applies the result to C itself)
+  const int64_t* koff_x;  // [Kflat] offset of flattened contraction index k inside X
+  const int64_t* koff_y;  // [Kflat] the same inside Y
+  int32_t lanes_k_x;  // element-wise loader: consecutive lanes that walk k (1 = lanes walk the external index)
+  int32_t lanes_k_y;
+  int32_t vec_c;     // contiguous output elements a thread may touch with one access (1, 2 or 4)
+  int32_t beta;      // 1: C is read and accumulated into; 0: C is overwritten
+  double alpha;      // +1 or -1
+  void* ws;          // K-slice partials: [ksplit][tiles][BN][BM]
+};
+
+enum TcMath { TC_MATH_DMMA = 0, TC_MATH_SIMT = 1 };
+
+struct TcKernelChoice {
+  int dtype;      // tc_dtype
+  int math;       // TcMath
+  int bm, bn;     // CTA tile
+  bool vec_x, vec_y;  // 16-byte loads along the external index of X / Y
+};
+
+// Host-side plan.
+struct tc_plan {
+  TcExpr expr;
+  int dtype = TC_F64;
+  tc_options opt{};
+  // current extents by index name (out_idx then sum_idx order)
+  std::vector<std::string> idx_names;
+  std::vector<int64_t> idx_extent;
+  bool custom_strides[3] = {false, false, false};
+  std::vector<int64_t> strides[3];  // per tensor, per written index
+
+  // ---- filled by commit ----
+  bool committed = false;
+  int device = -1;
+  bool swapped = false;  // X = right input, Y = left input
+  TcKernelArgs args{};
+  TcKernelChoice choice{};
+  std::vector<int64_t> h_koff_x, h_koff_y;
+  void* d_koff = nullptr;      // device copy of both tables
+  void* d_ws = nullptr;        // plan-owned K-slice workspace
+  size_t ws_bytes = 0;
+  int64_t size_c = 0, size_a = 0, size_b = 0;  // elements spanned (max offset + 1)
+  int64_t count_c = 0, count_a = 0, count_b = 0;  // logical element counts
+  double flops = 0, bytes = 0;
+  int launches = 1;
+  std::string why;  // last planner message
+};
+
+int tc_plan_build(tc_plan* p, std::string* why);           // host-only part of commit
+std::string tc_plan_to_json(const tc_plan& p);
+
+// ------------------------------------------------------------- kernels ----
+#ifdef __CUDACC__
+// Enqueues the contraction (and, for K-sliced plans, the combine step).
+int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, const void* X,
+                          const void* Y, cudaStream_t stream);
+// Shared memory bytes / threads of the chosen kernel (for tc_plan_describe).
+int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk);
+int tc_kernels_prepare(const TcKernelChoice& c);  // opt-in shared memory attribute
+#endif
+
+// Compiled CTA tiles.
+bool tc_tile_supported(int dtype, int math, int bm, int bn);
+int tc_tile_bk(int dtype, int math);
+
+#endif  // TC_INTERNAL_H_

@@ -1,0 +1,466 @@
+// Contraction kernel template for sm_100a.
+//
+// One CTA computes a BM x BN tile of the FLATTENED external index spaces
+// (M = external indices of operand X, N = external indices of operand Y) and
+// walks the flattened contraction range in steps of BK.  It takes over the
+// roles of the reference's generated kernel pieces:
+//   * prologue / index decode   cogent/src/codes/kernels/tc_code_kernel.py:166-552
+//   * permuted global->shared   cogent/src/codes/kernels/tc_code_kernel_load_inputs_abstract.py:32-317
+//   * register-tile product     cogent/src/codes/kernels/tc_code_kernel_compute.py:4-204
+//   * guarded store             cogent/src/codes/kernels/tc_code_kernel_store_output.py:6-89
+// but not their structure: tiles are ranges of the flattened index (no partial
+// tiles inside the tensor, whatever the extents), addresses are separable sums
+// off_ext[m] + off_k[k] looked up from a per-CTA table in shared memory and a
+// per-plan table in global memory, the staging is an asynchronous multi-stage
+// cp.async pipeline, fp64 products run on the tensor pipe (DMMA m8n8k4), and the
+// epilogue is a true read-modify-write with up to 32 contiguous bytes per thread.
+//
+// Shared-memory image of both operands is "external-index major":
+//   Xs[stage][k][m], row pitch BM+4; Ys[stage][k][n], row pitch BN+4.
+// The pitch makes the 16-byte DMMA fragment reads, the 16-byte SIMT reads and
+// the element-wise transposing writes all bank-conflict free.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tc_internal.h"
+
+namespace tck {
+
+// ------------------------------------------------------------- primitives ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int sz = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src, bool pred) {
+  const int sz = pred ? 8 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, bool pred) {
+  const int sz = pred ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+template <int ES>
+__device__ __forceinline__ void cp_async_elem(uint32_t dst, const void* src, bool pred) {
+  if constexpr (ES == 8) cp_async8(dst, src, pred);
+  else cp_async4(dst, src, pred);
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void dmma884(double& d0, double& d1, double a, double b) {
+  asm("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+      : "+d"(d0), "+d"(d1)
+      : "d"(a), "d"(b));
+}
+
+template <typename T> struct Vec16;
+template <> struct Vec16<double> { using type = double2; static constexpr int W = 2; };
+template <> struct Vec16<float> { using type = float4; static constexpr int W = 4; };
+
+// ------------------------------------------------------------ configuration ----
+template <typename T_, int MATH_, int BM_, int BN_, int WARPS_M_, int WARPS_N_, int STAGES_, bool VECX_, bool VECY_>
+struct Cfg {
+  using T = T_;
+  static constexpr int MATH = MATH_;
+  static constexpr int BM = BM_, BN = BN_, BK = 16;
+  static constexpr int STAGES = STAGES_;
+  static constexpr bool VECX = VECX_, VECY = VECY_;
+  static constexpr int ES = (int)sizeof(T);
+  static constexpr int VW = 16 / ES;  // elements per 16 bytes
+  // DMMA: WARPS_M x WARPS_N warps, each a (BM/WARPS_M) x (BN/WARPS_N) tile.
+  // SIMT: (BM/8) x (BN/8) threads, each an 8 x 8 tile.
+  static constexpr int THREADS = MATH == TC_MATH_DMMA ? 32 * WARPS_M_ * WARPS_N_ : (BM / 8) * (BN / 8);
+  static constexpr int WARPS = THREADS / 32;
+  static constexpr int WM = BM / WARPS_M_, WN = BN / WARPS_N_;
+  static constexpr int WARPS_M = WARPS_M_, WARPS_N = WARPS_N_;
+  static constexpr int LDX = BM + 4, LDY = BN + 4;
+  static constexpr int TABLE_BYTES = (2 * BM + 2 * BN) * 8;
+  static constexpr int STAGE_ELEMS = BK * (LDX + LDY);
+  static constexpr int SMEM_BYTES = TABLE_BYTES + STAGES * STAGE_ELEMS * ES;
+};
+
+// ------------------------------------------------------- offset tables ----
+// Entry i of a class table: flattened index base+i decomposed over the class's
+// dimensions; -1 marks "outside the tensor".
+__device__ __forceinline__ void decode(const TcDims& d, uint32_t flat, uint32_t limit, int64_t* off_in, int64_t* off_out) {
+  if (flat >= limit) { *off_in = -1; *off_out = -1; return; }
+  int64_t oi = 0, oo = 0;
+#pragma unroll 1
+  for (int i = 0; i < d.n; ++i) {
+    const uint32_t q = flat / d.extent[i];
+    const uint32_t c = flat - q * d.extent[i];
+    flat = q;
+    oi += (int64_t)c * d.s_in[i];
+    oo += (int64_t)c * d.s_out[i];
+  }
+  *off_in = oi;
+  *off_out = oo;
+}
+
+// ------------------------------------------------------------- loaders ----
+// 16-byte loads along the external index: thread -> (vector of VW externals, k).
+template <class CF, int ROWS, int LD>
+__device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
+                                               const int64_t* s_off, const int64_t* __restrict__ koff,
+                                               uint32_t k0, uint32_t kend, int tid) {
+  constexpr int VPR = ROWS / CF::VW;            // vectors per k row
+  constexpr int SLOTS = VPR * CF::BK;
+  static_assert(SLOTS % CF::THREADS == 0 || SLOTS < CF::THREADS, "loader shape");
+  constexpr int PER = (SLOTS + CF::THREADS - 1) / CF::THREADS;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int s = tid + j * CF::THREADS;
+    if (SLOTS % CF::THREADS != 0 && s >= SLOTS) break;
+    const int ev = s % VPR, kk = s / VPR;
+    const int64_t eo = s_off[ev * CF::VW];
+    const uint32_t k = k0 + kk;
+    const bool ok = eo >= 0 && k < kend;
+    const int64_t ko = ok ? koff[k] : 0;
+    const typename CF::T* src = ok ? g + eo + ko : g;
+    cp_async16(smem_u32(s_stage + kk * LD + ev * CF::VW), src, ok);
+  }
+}
+
+// Element-wise loads.  A warp covers `lanes_k` consecutive k by 32/lanes_k
+// consecutive externals, so that the lanes that walk the tensor's fastest index
+// read whole 32-byte sectors; the write into the external-major image is a
+// transposing scatter.
+template <class CF, int ROWS, int LD>
+__device__ __forceinline__ void load_stage_elem(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
+                                                const int64_t* s_off, const int64_t* __restrict__ koff,
+                                                uint32_t k0, uint32_t kend, int tid, int lanes_k) {
+  constexpr int PER = ROWS * CF::BK / CF::THREADS;  // elements per thread per stage
+  static_assert(ROWS * CF::BK % CF::THREADS == 0, "loader shape");
+  const int lane = tid & 31, warp = tid >> 5;
+  const int lanes_e = 32 / lanes_k;
+  const int kslabs = CF::BK / lanes_k;  // slabs along k
+  const int lk = lane % lanes_k, le = lane / lanes_k;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int slab = warp * PER + j;
+    const int ks = slab % kslabs, esl = slab / kslabs;
+    const int kk = ks * lanes_k + lk;
+    const int el = esl * lanes_e + le;
+    const int64_t eo = s_off[el];
+    const uint32_t k = k0 + kk;
+    const bool ok = eo >= 0 && k < kend;
+    const int64_t ko = ok ? koff[k] : 0;
+    const typename CF::T* src = ok ? g + eo + ko : g;
+    cp_async_elem<CF::ES>(smem_u32(s_stage + kk * LD + el), src, ok);
+  }
+}
+
+// --------------------------------------------------------------- kernel ----
+template <class CF>
+__global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_constant__ TcKernelArgs p,
+                                                                   typename CF::T* __restrict__ C,
+                                                                   const typename CF::T* __restrict__ X,
+                                                                   const typename CF::T* __restrict__ Y) {
+  using T = typename CF::T;
+  constexpr int BM = CF::BM, BN = CF::BN, BK = CF::BK, LDX = CF::LDX, LDY = CF::LDY, STAGES = CF::STAGES;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int64_t* offx_m = reinterpret_cast<int64_t*>(smem_raw);
+  int64_t* offc_m = offx_m + BM;
+  int64_t* offy_n = offc_m + BM;
+  int64_t* offc_n = offy_n + BN;
+  T* Xs = reinterpret_cast<T*>(offc_n + BN);
+  T* Ys = Xs + STAGES * BK * LDX;
+
+  const int tid = threadIdx.x;
+  const uint32_t bid = blockIdx.x;
+  const uint32_t tile_m = bid % p.tiles_m;
+  const uint32_t rest = bid / p.tiles_m;
+  const uint32_t tile_n = rest % p.tiles_n;
+  const uint32_t slice = rest / p.tiles_n;
+  const uint32_t m0 = tile_m * BM, n0 = tile_n * BN;
+  const uint32_t kbeg = slice * p.k_chunk;
+  const uint32_t kend = min(p.Kflat, kbeg + p.k_chunk);
+
+  for (int i = tid; i < BM + BN; i += CF::THREADS) {
+    if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
+    else decode(p.N, n0 + (i - BM), p.Nflat, &offy_n[i - BM], &offc_n[i - BM]);
+  }
+  __syncthreads();
+
+  const int nk = (int)((kend - kbeg + BK - 1) / BK);
+  auto issue = [&](int it) {
+    if (it < nk) {
+      const int st = it % STAGES;
+      const uint32_t k0 = kbeg + it * BK;
+      T* xs = Xs + st * BK * LDX;
+      T* ys = Ys + st * BK * LDY;
+      if constexpr (CF::VECX) load_stage_vec<CF, BM, LDX>(xs, X, offx_m, p.koff_x, k0, kend, tid);
+      else load_stage_elem<CF, BM, LDX>(xs, X, offx_m, p.koff_x, k0, kend, tid, p.lanes_k_x);
+      if constexpr (CF::VECY) load_stage_vec<CF, BN, LDY>(ys, Y, offy_n, p.koff_y, k0, kend, tid);
+      else load_stage_elem<CF, BN, LDY>(ys, Y, offy_n, p.koff_y, k0, kend, tid, p.lanes_k_y);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue(s);
+
+  if constexpr (CF::MATH == TC_MATH_DMMA) {
+    // ---------------- fp64 on the tensor pipe ----------------
+    // D(8x8) += Aop(8x4) * Bop(4x8) with rows of D = n, columns of D = m, so a
+    // thread's two D registers are consecutive m (the output's fastest index).
+    // MMA row/column r of block b is mapped to tile element 16*(b/2) + 2r + (b&1):
+    // one 16-byte shared load feeds two blocks, and the four D values a thread
+    // holds for a block pair are four CONSECUTIVE m.
+    constexpr int WM = CF::WM, WN = CF::WN;
+    constexpr int MB2 = WM / 16, NB2 = WN / 16;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int wm0 = (warp % CF::WARPS_M) * WM, wn0 = (warp / CF::WARPS_M) * WN;
+    double acc[2 * NB2][2 * MB2][2];
+#pragma unroll
+    for (int j = 0; j < 2 * NB2; ++j)
+#pragma unroll
+      for (int i = 0; i < 2 * MB2; ++i) { acc[j][i][0] = 0.0; acc[j][i][1] = 0.0; }
+
+    for (int it = 0; it < nk; ++it) {
+      cp_async_wait<STAGES - 2>();
+      __syncthreads();
+      issue(it + STAGES - 1);
+      const int st = it % STAGES;
+      const T* xs = Xs + st * BK * LDX + wm0 + 2 * g;
+      const T* ys = Ys + st * BK * LDY + wn0 + 2 * g;
+      const int kleft = (int)(kend - (kbeg + it * BK));
+      const int nks = kleft >= BK ? BK / 4 : (kleft + 3) / 4;
+#pragma unroll
+      for (int ks = 0; ks < BK / 4; ++ks) {
+        if (ks < nks) {
+          const int k = ks * 4 + t;
+          double2 xf[MB2], yf[NB2];
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) xf[i] = *reinterpret_cast<const double2*>(xs + k * LDX + i * 16);
+#pragma unroll
+          for (int j = 0; j < NB2; ++j) yf[j] = *reinterpret_cast<const double2*>(ys + k * LDY + j * 16);
+#pragma unroll
+          for (int j = 0; j < NB2; ++j)
+#pragma unroll
+            for (int i = 0; i < MB2; ++i) {
+              dmma884(acc[2 * j][2 * i][0], acc[2 * j][2 * i][1], yf[j].x, xf[i].x);
+              dmma884(acc[2 * j][2 * i + 1][0], acc[2 * j][2 * i + 1][1], yf[j].x, xf[i].y);
+              dmma884(acc[2 * j + 1][2 * i][0], acc[2 * j + 1][2 * i][1], yf[j].y, xf[i].x);
+              dmma884(acc[2 * j + 1][2 * i + 1][0], acc[2 * j + 1][2 * i + 1][1], yf[j].y, xf[i].y);
+            }
+        }
+      }
+    }
+    cp_async_wait<0>();
+
+    // ---------------- epilogue ----------------
+    // Thread holds, per n row (nb = 2j+h -> n = wn0 + 16j + 2g + h) and block
+    // pair i, the four m = wm0 + 16i + 4t + {0,1,2,3}:
+    //   acc[nb][2i][0], acc[nb][2i+1][0], acc[nb][2i][1], acc[nb][2i+1][1].
+    const double alpha = p.alpha;
+    if (p.ksplit > 1) {
+      double* ws = reinterpret_cast<double*>(p.ws) +
+                   ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        const int nl = wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1);
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          const int ml = wm0 + 16 * i + 4 * t;
+          double2* dst = reinterpret_cast<double2*>(ws + (size_t)nl * BM + ml);
+          dst[0] = make_double2(acc[nb][2 * i][0], acc[nb][2 * i + 1][0]);
+          dst[1] = make_double2(acc[nb][2 * i][1], acc[nb][2 * i + 1][1]);
+        }
+      }
+      return;
+    }
+    int64_t cm[MB2];
+#pragma unroll
+    for (int i = 0; i < MB2; ++i) cm[i] = offc_m[wm0 + 16 * i + 4 * t];
+#pragma unroll
+    for (int nb = 0; nb < 2 * NB2; ++nb) {
+      const int nl = wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1);
+      const int64_t cn = offc_n[nl];
+      if (cn < 0) continue;
+      if (p.vec_c == 4) {
+        double2 c0[MB2], c1[MB2];
+        if (p.beta) {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i)
+            if (cm[i] >= 0) {
+              const double2* src = reinterpret_cast<const double2*>(C + cn + cm[i]);
+              c0[i] = src[0];
+              c1[i] = src[1];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MB2; ++i)
+          if (cm[i] >= 0) {
+            double2 r0, r1;
+            r0.x = alpha * acc[nb][2 * i][0];
+            r0.y = alpha * acc[nb][2 * i + 1][0];
+            r1.x = alpha * acc[nb][2 * i][1];
+            r1.y = alpha * acc[nb][2 * i + 1][1];
+            if (p.beta) { r0.x += c0[i].x; r0.y += c0[i].y; r1.x += c1[i].x; r1.y += c1[i].y; }
+            double2* dst = reinterpret_cast<double2*>(C + cn + cm[i]);
+            dst[0] = r0;
+            dst[1] = r1;
+          }
+      } else if (p.vec_c == 2) {
+#pragma unroll
+        for (int i = 0; i < MB2; ++i)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int64_t co = offc_m[wm0 + 16 * i + 4 * t + 2 * e];
+            if (co < 0) continue;
+            double2* dst = reinterpret_cast<double2*>(C + cn + co);
+            double2 r;
+            r.x = alpha * acc[nb][2 * i][e];
+            r.y = alpha * acc[nb][2 * i + 1][e];
+            if (p.beta) { const double2 c = *dst; r.x += c.x; r.y += c.y; }
+            *dst = r;
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < MB2; ++i)
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
+            if (co < 0) continue;
+            double r = alpha * acc[nb][2 * i + (q & 1)][q >> 1];
+            if (p.beta) r += C[cn + co];
+            C[cn + co] = r;
+          }
+      }
+    }
+  } else {
+    // ---------------- vector pipe (FFMA / DFMA) ----------------
+    // (BM/8) x (BN/8) threads, 8 x 8 outputs each, as groups of VW contiguous
+    // elements: m(gq,e) = gq*TX*VW + tx*VW + e, same along n.
+    using V = typename Vec16<T>::type;
+    constexpr int VW = CF::VW, GR = 8 / VW;
+    constexpr int TX = BM / 8, TY = BN / 8;
+    const int tx = tid % TX, ty = tid / TX;
+    T acc[8][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[j][i] = T(0);
+
+    for (int it = 0; it < nk; ++it) {
+      cp_async_wait<STAGES - 2>();
+      __syncthreads();
+      issue(it + STAGES - 1);
+      const int st = it % STAGES;
+      const T* xs = Xs + st * BK * LDX + tx * VW;
+      const T* ys = Ys + st * BK * LDY + ty * VW;
+      const int kleft = (int)(kend - (kbeg + it * BK));
+      const int kv = kleft >= BK ? BK : kleft;
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        if (kk < kv) {
+          T xv[8], yv[8];
+#pragma unroll
+          for (int q = 0; q < GR; ++q) {
+            *reinterpret_cast<V*>(&xv[q * VW]) = *reinterpret_cast<const V*>(xs + kk * LDX + q * TX * VW);
+            *reinterpret_cast<V*>(&yv[q * VW]) = *reinterpret_cast<const V*>(ys + kk * LDY + q * TY * VW);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[j][i] = fma(yv[j], xv[i], acc[j][i]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+
+    const T alpha = (T)p.alpha;
+    if (p.ksplit > 1) {
+      T* ws = reinterpret_cast<T*>(p.ws) +
+              ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int nl = (j / VW) * TY * VW + ty * VW + (j % VW);
+#pragma unroll
+        for (int q = 0; q < GR; ++q) {
+          const int ml = q * TX * VW + tx * VW;
+          *reinterpret_cast<V*>(ws + (size_t)nl * BM + ml) = *reinterpret_cast<const V*>(&acc[j][q * VW]);
+        }
+      }
+      return;
+    }
+    int64_t cm[GR];
+#pragma unroll
+    for (int q = 0; q < GR; ++q) cm[q] = offc_m[q * TX * VW + tx * VW];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int nl = (j / VW) * TY * VW + ty * VW + (j % VW);
+      const int64_t cn = offc_n[nl];
+      if (cn < 0) continue;
+      if (p.vec_c >= VW) {
+        V cv[GR];
+        if (p.beta) {
+#pragma unroll
+          for (int q = 0; q < GR; ++q)
+            if (cm[q] >= 0) cv[q] = *reinterpret_cast<const V*>(C + cn + cm[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < GR; ++q)
+          if (cm[q] >= 0) {
+            T r[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) r[e] = alpha * acc[j][q * VW + e];
+            if (p.beta) {
+              const T* cp = reinterpret_cast<const T*>(&cv[q]);
+#pragma unroll
+              for (int e = 0; e < VW; ++e) r[e] += cp[e];
+            }
+            *reinterpret_cast<V*>(C + cn + cm[q]) = *reinterpret_cast<const V*>(r);
+          }
+      } else {
+#pragma unroll
+        for (int q = 0; q < GR; ++q)
+#pragma unroll
+          for (int e = 0; e < VW; ++e) {
+            const int64_t co = offc_m[q * TX * VW + tx * VW + e];
+            if (co < 0) continue;
+            T r = alpha * acc[j][q * VW + e];
+            if (p.beta) r += C[cn + co];
+            C[cn + co] = r;
+          }
+      }
+    }
+  }
+}
+
+// K-slice combine: C (op)= sum over slices of the partial tiles, slices in
+// ascending order (deterministic).
+template <typename T, int BM, int BN>
+__global__ void __launch_bounds__(256) tc_combine_kernel(const __grid_constant__ TcKernelArgs p, T* __restrict__ C) {
+  __shared__ int64_t offc_m[BM];
+  __shared__ int64_t offc_n[BN];
+  const uint32_t bid = blockIdx.x;
+  const uint32_t tile_m = bid % p.tiles_m, tile_n = bid / p.tiles_m;
+  const size_t tiles = (size_t)p.tiles_m * p.tiles_n;
+  for (int i = threadIdx.x; i < BM + BN; i += 256) {
+    int64_t dummy;
+    if (i < BM) decode(p.M, tile_m * BM + i, p.Mflat, &dummy, &offc_m[i]);
+    else decode(p.N, tile_n * BN + (i - BM), p.Nflat, &dummy, &offc_n[i - BM]);
+  }
+  __syncthreads();
+  const T* ws = reinterpret_cast<const T*>(p.ws) + (size_t)bid * (BM * BN);
+  const T alpha = (T)p.alpha;
+  for (int e = threadIdx.x; e < BM * BN; e += 256) {
+    const int ml = e % BM, nl = e / BM;
+    const int64_t cm = offc_m[ml], cn = offc_n[nl];
+    if (cm < 0 || cn < 0) continue;
+    T s = T(0);
+    for (uint32_t sl = 0; sl < p.ksplit; ++sl) s += ws[sl * tiles * (size_t)(BM * BN) + e];
+    T r = alpha * s;
+    if (p.beta) r += C[cn + cm];
+    C[cn + cm] = r;
+  }
+}
+
+}  // namespace tck

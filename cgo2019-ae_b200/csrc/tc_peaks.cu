@@ -1,0 +1,218 @@
+// Arithmetic-pipe peak probes for the roofline denominators.
+//
+// The driver-measured peak file only carries HBM copy bandwidth and a bf16
+// GEMM rate.  The contraction kernels are bounded by the FP64 tensor pipe
+// (DMMA), the FP64 vector pipe (DFMA) and the FP32 vector pipe (FFMA), so those
+// peaks are measured here with register-only loops (no memory traffic) and
+// reported by the bench beside every "fraction of peak".
+//
+// Every probe launches `ctas_per_sm * #SMs` CTAs of 256 threads, each warp
+// running `iters` rounds of independent accumulation chains.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "tc_internal.h"
+
+namespace {
+
+constexpr int kChains = 8;
+
+__device__ __forceinline__ void dmma884(double (&d)[2], double a, double b) {
+  asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
+               : "+d"(d[0]), "+d"(d[1]) : "d"(a), "d"(b));
+}
+__device__ __forceinline__ void dmma1684(double (&d)[4], const double (&a)[2], double b) {
+  asm volatile("mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+               : "+d"(d[0]), "+d"(d[1]), "+d"(d[2]), "+d"(d[3]) : "d"(a[0]), "d"(a[1]), "d"(b));
+}
+__device__ __forceinline__ void dmma1688(double (&d)[4], const double (&a)[4], const double (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+d"(d[0]), "+d"(d[1]), "+d"(d[2]), "+d"(d[3])
+               : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(b[0]), "d"(b[1]));
+}
+__device__ __forceinline__ void dmma16816(double (&d)[4], const double (&a)[8], const double (&b)[4]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f64.f64.f64.f64 {%0,%1,%2,%3}, {%4,%5,%6,%7,%8,%9,%10,%11}, {%12,%13,%14,%15}, {%0,%1,%2,%3};\n"
+               : "+d"(d[0]), "+d"(d[1]), "+d"(d[2]), "+d"(d[3])
+               : "d"(a[0]), "d"(a[1]), "d"(a[2]), "d"(a[3]), "d"(a[4]), "d"(a[5]), "d"(a[6]), "d"(a[7]),
+                 "d"(b[0]), "d"(b[1]), "d"(b[2]), "d"(b[3]));
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+// which: 0 DMMA m8n8k4, 1 DMMA m16n8k4, 2 DMMA m16n8k8, 3 DMMA m16n8k16,
+//        4 DFMA, 5 FFMA, 6 TF32 mma.sync m16n8k8
+template <int WHICH>
+__global__ void __launch_bounds__(256) peak_kernel(int iters, double* sink) {
+  const double seed = 1.0 + 1e-9 * threadIdx.x;
+  double out = 0.0;
+  if constexpr (WHICH == 0) {
+    double d[kChains][2];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) { d[c][0] = seed; d[c][1] = seed; }
+    double a = seed * 1e-3, b = seed * 1e-3;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) dmma884(d[c], a, b);
+    }
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) out += d[c][0] + d[c][1];
+  } else if constexpr (WHICH >= 1 && WHICH <= 3) {
+    double d[kChains][4];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c)
+      for (int j = 0; j < 4; ++j) d[c][j] = seed;
+    double a[8], b[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = seed * 1e-3 * (j + 1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) b[j] = seed * 1e-3 * (j + 2);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) {
+        if constexpr (WHICH == 1) { double a2[2] = {a[0], a[1]}; dmma1684(d[c], a2, b[0]); }
+        if constexpr (WHICH == 2) { double a4[4] = {a[0], a[1], a[2], a[3]}; double b2[2] = {b[0], b[1]}; dmma1688(d[c], a4, b2); }
+        if constexpr (WHICH == 3) { dmma16816(d[c], a, b); }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) out += d[c][0] + d[c][1] + d[c][2] + d[c][3];
+  } else if constexpr (WHICH == 4) {
+    double d[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) d[c] = seed + c;
+    double a = 1.0 + 1e-12 * threadIdx.x, b = 1e-12;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int c = 0; c < 16; ++c) d[c] = fma(d[c], a, b);
+    }
+#pragma unroll
+    for (int c = 0; c < 16; ++c) out += d[c];
+  } else if constexpr (WHICH == 5) {
+    float d[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) d[c] = (float)seed + c;
+    float a = 1.0f + 1e-7f * threadIdx.x, b = 1e-7f;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int c = 0; c < 16; ++c) d[c] = fmaf(d[c], a, b);
+    }
+#pragma unroll
+    for (int c = 0; c < 16; ++c) out += d[c];
+  } else {
+    float d[kChains][4];
+#pragma unroll
+    for (int c = 0; c < kChains; ++c)
+      for (int j = 0; j < 4; ++j) d[c][j] = (float)seed;
+    uint32_t a[4], b[2];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) a[j] = __float_as_uint(1e-3f * (j + 1));
+    b[0] = __float_as_uint(2e-3f); b[1] = __float_as_uint(3e-3f);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int c = 0; c < kChains; ++c) mma_tf32_1688(d[c], a, b);
+    }
+#pragma unroll
+    for (int c = 0; c < kChains; ++c) out += d[c][0] + d[c][1] + d[c][2] + d[c][3];
+  }
+  if (out == 123.456) sink[0] = out;  // keeps the chains alive; never true in practice
+}
+
+// FLOPs one warp performs per loop iteration of the probe.
+double flops_per_warp_iter(int which) {
+  switch (which) {
+    case 0: return kChains * 2.0 * 8 * 8 * 4;
+    case 1: return kChains * 2.0 * 16 * 8 * 4;
+    case 2: return kChains * 2.0 * 16 * 8 * 8;
+    case 3: return kChains * 2.0 * 16 * 8 * 16;
+    case 4: return 16 * 2.0 * 32;
+    case 5: return 16 * 2.0 * 32;
+    default: return kChains * 2.0 * 16 * 8 * 8;
+  }
+}
+
+// Streaming read-modify-write of 16-byte words: the ceiling for a `+=` epilogue.
+__global__ void __launch_bounds__(256) rmw_kernel(double2* p, int64_t n16, double add) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n16; i += stride) {
+    double2 v = p[i];
+    v.x += add; v.y += add;
+    p[i] = v;
+  }
+}
+
+}  // namespace
+
+extern "C" int tc_peak_measure(int which, int iters, int ctas_per_sm, double* tflops) {
+  if (!tflops || which < 0 || which > 6 || iters <= 0 || ctas_per_sm <= 0) return TC_ERR_INVALID_ARG;
+  int dev = 0, sms = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  double* sink = nullptr;
+  TC_CUDA_OK(cudaMalloc(&sink, sizeof(double)));
+  cudaEvent_t e0, e1;
+  TC_CUDA_OK(cudaEventCreate(&e0));
+  TC_CUDA_OK(cudaEventCreate(&e1));
+  const int grid = sms * ctas_per_sm;
+  auto launch = [&](int n) {
+    switch (which) {
+      case 0: peak_kernel<0><<<grid, 256>>>(n, sink); break;
+      case 1: peak_kernel<1><<<grid, 256>>>(n, sink); break;
+      case 2: peak_kernel<2><<<grid, 256>>>(n, sink); break;
+      case 3: peak_kernel<3><<<grid, 256>>>(n, sink); break;
+      case 4: peak_kernel<4><<<grid, 256>>>(n, sink); break;
+      case 5: peak_kernel<5><<<grid, 256>>>(n, sink); break;
+      default: peak_kernel<6><<<grid, 256>>>(n, sink); break;
+    }
+  };
+  launch(iters / 8 + 1);  // warm-up
+  float best_ms = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    TC_CUDA_OK(cudaEventRecord(e0));
+    launch(iters);
+    TC_CUDA_OK(cudaEventRecord(e1));
+    TC_CUDA_OK(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    TC_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+    if (ms < best_ms) best_ms = ms;
+  }
+  TC_CUDA_OK(cudaGetLastError());
+  const double flops = flops_per_warp_iter(which) * (double)iters * 8.0 * grid;
+  *tflops = flops / (best_ms * 1e-3) * 1e-12;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(sink);
+  return TC_OK;
+}
+
+extern "C" int tc_peak_measure_rmw(int64_t bytes, double* gbs) {
+  if (!gbs || bytes < (1 << 20)) return TC_ERR_INVALID_ARG;
+  int dev = 0, sms = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  double2* buf = nullptr;
+  const int64_t n16 = bytes / 16;
+  TC_CUDA_OK(cudaMalloc(&buf, n16 * 16));
+  TC_CUDA_OK(cudaMemset(buf, 0, n16 * 16));
+  cudaEvent_t e0, e1;
+  TC_CUDA_OK(cudaEventCreate(&e0));
+  TC_CUDA_OK(cudaEventCreate(&e1));
+  float best_ms = 1e30f;
+  for (int rep = 0; rep < 6; ++rep) {
+    TC_CUDA_OK(cudaEventRecord(e0));
+    rmw_kernel<<<sms * 8, 256>>>(buf, n16, 1.0);
+    TC_CUDA_OK(cudaEventRecord(e1));
+    TC_CUDA_OK(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    TC_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+    if (rep > 0 && ms < best_ms) best_ms = ms;
+  }
+  TC_CUDA_OK(cudaGetLastError());
+  *gbs = 2.0 * n16 * 16 / (best_ms * 1e-3) * 1e-9;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(buf);
+  return TC_OK;
+}

@@ -1,0 +1,307 @@
+// Planner: from a parsed expression + extents to the launch description.
+//
+// This replaces the reference's offline search
+// (cogent/src/generators/configurations.py:15-289 -> enumeration.py:15-278 ->
+// cost_models.py:11-39), which enumerates thread-block / register-tile index
+// groups and ranks them by estimated DRAM transactions.  The B200 kernels tile
+// the FLATTENED external index spaces instead of per-index boxes, so the search
+// collapses to: classify and order the indices, fuse what is contiguous, pick
+// the loader per operand, pick a CTA tile and (for small outputs) a K split.
+//
+//   M  = external indices of X, ordered by their stride in the output
+//   N  = external indices of Y, ordered by their stride in the output
+//   K  = contraction indices, ordered by their stride in whichever operand has
+//        a contraction index as its fastest index
+// where X is the operand that carries the output's fastest index (operands are
+// swapped if that is the right one; the product is commutative).  The reference
+// makes the same choice when it maps the input holding the output's fastest
+// index to the thread-block X dimension (enumeration.py:72-100).
+#include <algorithm>
+#include <cstring>
+#include <numeric>
+#include <sstream>
+
+#include "tc_internal.h"
+
+namespace {
+
+struct Dim {
+  int64_t extent, s_in, s_out;  // for K: s_in = stride in X, s_out = stride in Y
+};
+
+int find(const std::vector<std::string>& v, const std::string& s) {
+  for (size_t i = 0; i < v.size(); ++i)
+    if (v[i] == s) return (int)i;
+  return -1;
+}
+
+std::vector<int64_t> compact_strides(const std::vector<std::string>& idx, const tc_plan& p) {
+  std::vector<int64_t> s(idx.size());
+  int64_t acc = 1;
+  for (size_t i = 0; i < idx.size(); ++i) {
+    s[i] = acc;
+    acc *= p.idx_extent[find(p.idx_names, idx[i])];
+  }
+  return s;
+}
+
+// Drops unit extents and merges neighbours that are contiguous in both tensors.
+std::vector<Dim> fuse(std::vector<Dim> d) {
+  std::vector<Dim> out;
+  for (const Dim& x : d) {
+    if (x.extent == 1) continue;
+    if (!out.empty()) {
+      Dim& b = out.back();
+      if (x.s_in == b.s_in * b.extent && x.s_out == b.s_out * b.extent) {
+        b.extent *= x.extent;
+        continue;
+      }
+    }
+    out.push_back(x);
+  }
+  return out;
+}
+
+bool to_dims(const std::vector<Dim>& d, TcDims* t, int64_t* flat) {
+  if ((int)d.size() > TC_MAX_DIMS) return false;
+  std::memset(t, 0, sizeof(*t));
+  t->n = (int)d.size();
+  int64_t f = 1;
+  for (size_t i = 0; i < d.size(); ++i) {
+    t->extent[i] = (uint32_t)d[i].extent;
+    t->s_in[i] = d[i].s_in;
+    t->s_out[i] = d[i].s_out;
+    f *= d[i].extent;
+    if (f >= (int64_t(1) << 31)) return false;
+  }
+  *flat = f;
+  return true;
+}
+
+int64_t span(const std::vector<int64_t>& ext, const std::vector<int64_t>& str) {
+  int64_t s = 1;
+  for (size_t i = 0; i < ext.size(); ++i) s += (ext[i] - 1) * str[i];
+  return s;
+}
+
+}  // namespace
+
+bool tc_tile_supported(int dtype, int math, int bm, int bn) {
+  if (dtype == TC_F64 && math == TC_MATH_DMMA) return (bm == 128 && bn == 128) || (bm == 64 && bn == 64);
+  if (math == TC_MATH_SIMT) return (bm == 128 && bn == 128) || (bm == 64 && bn == 64);
+  return false;
+}
+
+int tc_tile_bk(int, int) { return 16; }
+
+int tc_plan_build(tc_plan* p, std::string* why) {
+  std::string dummy;
+  if (!why) why = &dummy;
+  const TcExpr& e = p->expr;
+  const int es = p->dtype == TC_F64 ? 8 : 4;
+  auto ext_of = [&](const std::string& n) { return p->idx_extent[find(p->idx_names, n)]; };
+
+  // Per-tensor extents and strides in written order.
+  const std::vector<std::string>* tidx[3] = {&e.out_idx, &e.left_idx, &e.right_idx};
+  std::vector<int64_t> text[3], tstr[3];
+  for (int t = 0; t < 3; ++t) {
+    for (const std::string& n : *tidx[t]) text[t].push_back(ext_of(n));
+    if (p->custom_strides[t]) {
+      if (p->strides[t].size() != tidx[t]->size()) { *why = "stride count does not match tensor rank"; return TC_ERR_INVALID_ARG; }
+      tstr[t] = p->strides[t];
+      for (int64_t s : tstr[t])
+        if (s <= 0) { *why = "strides must be positive"; return TC_ERR_EXTENT; }
+    } else {
+      tstr[t] = compact_strides(*tidx[t], *p);
+    }
+  }
+  // The output must not alias itself: sorted by stride, each stride must clear the previous extent.
+  {
+    std::vector<std::pair<int64_t, int64_t>> se;
+    for (size_t i = 0; i < text[0].size(); ++i)
+      if (text[0][i] > 1) se.push_back({tstr[0][i], text[0][i]});
+    std::sort(se.begin(), se.end());
+    int64_t need = 1;
+    for (auto& x : se) {
+      if (x.first < need) { *why = "output strides make elements alias"; return TC_ERR_EXTENT; }
+      need = x.first * x.second;
+    }
+  }
+  p->count_c = std::accumulate(text[0].begin(), text[0].end(), int64_t(1), std::multiplies<int64_t>());
+  p->count_a = std::accumulate(text[1].begin(), text[1].end(), int64_t(1), std::multiplies<int64_t>());
+  p->count_b = std::accumulate(text[2].begin(), text[2].end(), int64_t(1), std::multiplies<int64_t>());
+  p->size_c = span(text[0], tstr[0]);
+  p->size_a = span(text[1], tstr[1]);
+  p->size_b = span(text[2], tstr[2]);
+
+  // Which operand carries the output's fastest (non-unit) index?
+  int fvi = -1;
+  for (size_t i = 0; i < e.out_idx.size(); ++i)
+    if (text[0][i] > 1 && (fvi < 0 || tstr[0][i] < tstr[0][fvi])) fvi = (int)i;
+  p->swapped = fvi >= 0 && find(e.left_idx, e.out_idx[fvi]) < 0;
+  const int X = p->swapped ? 2 : 1, Y = p->swapped ? 1 : 2;
+
+  std::vector<Dim> dm, dn, dk;
+  for (size_t i = 0; i < e.out_idx.size(); ++i) {
+    const std::string& n = e.out_idx[i];
+    const int ix = find(*tidx[X], n), iy = find(*tidx[Y], n);
+    if (ix >= 0) dm.push_back({text[0][i], tstr[X][ix], tstr[0][i]});
+    else dn.push_back({text[0][i], tstr[Y][iy], tstr[0][i]});
+  }
+  for (const std::string& n : e.sum_idx) {
+    const int ix = find(*tidx[X], n), iy = find(*tidx[Y], n);
+    dk.push_back({ext_of(n), tstr[X][ix], tstr[Y][iy]});
+  }
+  auto by_out = [](const Dim& a, const Dim& b) { return a.s_out < b.s_out; };
+  std::stable_sort(dm.begin(), dm.end(), by_out);
+  std::stable_sort(dn.begin(), dn.end(), by_out);
+  bool x_k_unit = false, y_k_unit = false;
+  for (const Dim& d : dk) {
+    if (d.extent > 1 && d.s_in == 1) x_k_unit = true;
+    if (d.extent > 1 && d.s_out == 1) y_k_unit = true;
+  }
+  if (!x_k_unit && y_k_unit)
+    std::stable_sort(dk.begin(), dk.end(), [](const Dim& a, const Dim& b) { return a.s_out < b.s_out; });
+  else
+    std::stable_sort(dk.begin(), dk.end(), [](const Dim& a, const Dim& b) { return a.s_in < b.s_in; });
+  dm = fuse(dm);
+  dn = fuse(dn);
+  dk = fuse(dk);
+
+  TcKernelArgs& a = p->args;
+  std::memset(&a, 0, sizeof(a));
+  int64_t mf = 1, nf = 1, kf = 1;
+  TcDims kd;
+  if (!to_dims(dm, &a.M, &mf) || !to_dims(dn, &a.N, &nf) || !to_dims(dk, &kd, &kf)) {
+    *why = "a fused index class has more than 8 dimensions or 2^31 elements";
+    return TC_ERR_UNSUPPORTED;
+  }
+  a.Mflat = (uint32_t)mf;
+  a.Nflat = (uint32_t)nf;
+  a.Kflat = (uint32_t)kf;
+
+  // Contraction offset tables (one entry per flattened k).
+  p->h_koff_x.assign(kf, 0);
+  p->h_koff_y.assign(kf, 0);
+  for (int64_t k = 0; k < kf; ++k) {
+    int64_t r = k, ox = 0, oy = 0;
+    for (int d = 0; d < kd.n; ++d) {
+      const int64_t c = r % kd.extent[d];
+      r /= kd.extent[d];
+      ox += c * kd.s_in[d];
+      oy += c * kd.s_out[d];
+    }
+    p->h_koff_x[k] = ox;
+    p->h_koff_y[k] = oy;
+  }
+
+  // Kernel family.
+  TcKernelChoice& c = p->choice;
+  c.dtype = p->dtype;
+  const int path = p->opt.path;
+  if (p->dtype == TC_F64) {
+    if (path == TC_PATH_FFMA || path == TC_PATH_3XTF32) { *why = "fp32 path requested for an fp64 plan"; return TC_ERR_INVALID_ARG; }
+    c.math = path == TC_PATH_DFMA ? TC_MATH_SIMT : TC_MATH_DMMA;
+  } else {
+    if (path == TC_PATH_DMMA || path == TC_PATH_DFMA) { *why = "fp64 path requested for an fp32 plan"; return TC_ERR_INVALID_ARG; }
+    if (path == TC_PATH_3XTF32) { *why = "the 3xTF32 path is not built into this library"; return TC_ERR_UNSUPPORTED; }
+    c.math = TC_MATH_SIMT;
+  }
+
+  // Loader per operand.
+  const int V = 16 / es;
+  auto loader = [&](const TcDims& ext, bool k_is_in, bool* vec, int32_t* lanes_k) {
+    *vec = false;
+    *lanes_k = 1;
+    if (ext.n > 0 && ext.s_in[0] == 1) {
+      bool ok = ext.extent[0] % V == 0;
+      for (int d = 1; d < ext.n; ++d) ok = ok && ext.s_in[d] % V == 0;
+      for (int d = 0; d < kd.n; ++d) ok = ok && (k_is_in ? kd.s_in[d] : kd.s_out[d]) % V == 0;
+      *vec = ok;
+    } else if (kd.n > 0 && (k_is_in ? kd.s_in[0] : kd.s_out[0]) == 1) {
+      *lanes_k = 32 / es;
+    }
+  };
+  loader(a.M, true, &c.vec_x, &a.lanes_k_x);
+  loader(a.N, false, &c.vec_y, &a.lanes_k_y);
+
+  // Contiguous output elements per thread access.
+  a.vec_c = 1;
+  if (a.M.n > 0 && a.M.s_out[0] == 1) {
+    for (int v : {4, 2}) {
+      bool ok = a.M.extent[0] % v == 0;
+      for (int d = 1; d < a.M.n; ++d) ok = ok && a.M.s_out[d] % v == 0;
+      for (int d = 0; d < a.N.n; ++d) ok = ok && a.N.s_out[d] % v == 0;
+      if (ok && v * es >= 8) { a.vec_c = v; break; }
+    }
+  }
+  a.alpha = e.op < 0 ? -1.0 : 1.0;
+  a.beta = e.op == 0 ? 0 : 1;
+
+  // CTA tile: the large tile unless it leaves most SMs idle.
+  int bm = 128, bn = 128;
+  if (p->opt.tile_m > 0 || p->opt.tile_n > 0) {
+    bm = p->opt.tile_m;
+    bn = p->opt.tile_n;
+    if (!tc_tile_supported(c.dtype, c.math, bm, bn)) { *why = "requested CTA tile is not compiled in"; return TC_ERR_UNSUPPORTED; }
+  } else {
+    const int64_t big = ((mf + 127) / 128) * ((nf + 127) / 128);
+    if (big < 2 * 148) { bm = 64; bn = 64; }
+  }
+  c.bm = bm;
+  c.bn = bn;
+  a.tiles_m = (uint32_t)((mf + bm - 1) / bm);
+  a.tiles_n = (uint32_t)((nf + bn - 1) / bn);
+  const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
+  const int bk = tc_tile_bk(c.dtype, c.math);
+
+  // K split: only when the tile count cannot fill the GPU and K is long.
+  int64_t ksplit = 1;
+  const int64_t ksteps = (kf + bk - 1) / bk;
+  if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
+  else if (p->opt.split_k == 0 && tiles * 2 <= 148 && ksteps >= 16)
+    ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * 148) / tiles, ksteps / 8));
+  int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
+  ksplit = (ksteps + chunk_steps - 1) / chunk_steps;
+  a.ksplit = (uint32_t)ksplit;
+  a.k_chunk = (uint32_t)(chunk_steps * bk);
+  if (tiles * ksplit >= (int64_t(1) << 31)) { *why = "too many tiles"; return TC_ERR_UNSUPPORTED; }
+  p->ws_bytes = ksplit > 1 ? (size_t)(ksplit * tiles * bm * bn) * es : 0;
+  p->launches = ksplit > 1 ? 2 : 1;
+
+  double prod = 1.0;
+  for (int64_t x : p->idx_extent) prod *= (double)x;
+  p->flops = 2.0 * prod;
+  p->bytes = (double)es * ((e.op == 0 ? 1.0 : 2.0) * p->count_c + p->count_a + p->count_b);
+  return TC_OK;
+}
+
+std::string tc_plan_to_json(const tc_plan& p) {
+  std::ostringstream o;
+  const TcKernelArgs& a = p.args;
+  auto dims = [&](const TcDims& d) {
+    o << "[";
+    for (int i = 0; i < d.n; ++i)
+      o << (i ? "," : "") << "{\"extent\":" << d.extent[i] << ",\"s_in\":" << d.s_in[i] << ",\"s_out\":" << d.s_out[i] << "}";
+    o << "]";
+  };
+  o << "{\"expr\":" << tc_expr_to_json(p.expr) << ",\"dtype\":\"" << (p.dtype == TC_F64 ? "f64" : "f32")
+    << "\",\"committed\":" << (p.committed ? "true" : "false");
+  if (p.committed) {
+    o << ",\"swapped\":" << (p.swapped ? "true" : "false") << ",\"M\":";
+    dims(a.M);
+    o << ",\"N\":";
+    dims(a.N);
+    o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
+      << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
+      << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << tc_tile_bk(p.choice.dtype, p.choice.math)
+      << "],\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
+      << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
+      << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
+      << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"beta\":" << a.beta
+      << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches
+      << ",\"flops\":" << p.flops << ",\"bytes\":" << p.bytes;
+  }
+  o << "}";
+  return o.str();
+}

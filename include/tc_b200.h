@@ -1,0 +1,151 @@
+/*
+ * tc_b200.h -- C ABI of the B200 tensor-contraction engine.
+ *
+ * One binary contraction  C[ext...] (+=|-=|=) sum(int...) A[...] * B[...]  on
+ * column-major (first index fastest) tensors, described by COGENT's one-line
+ * expression grammar.  The reference turns such a line into a generated .cu
+ * file whose only entry is
+ *     extern "C" void sd_t_d2_fusion_(int size_<idx>..., T* t3, T* t2, T* v2,
+ *                                     int cond_kernel_1, int opt_register_transpose)
+ * (emitted by cogent/src/codes/kernels/tc_interface.py:1444-1598); this header
+ * replaces that generate-compile-link cycle with plan / execute / free calls.
+ *
+ * Plain pointers and sizes only.  All functions return a tc_status (0 = ok) and
+ * never throw, exit or print.  The library has no CPU compute path: when no
+ * CUDA device is usable every compute call returns TC_ERR_CUDA.
+ */
+#ifndef TC_B200_H_
+#define TC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tc_status {
+  TC_OK = 0,
+  TC_ERR_PARSE = 1,        /* expression rejected by the grammar                       */
+  TC_ERR_INVALID_ARG = 2,  /* null pointer, unknown index name, bad enum value         */
+  TC_ERR_UNSUPPORTED = 3,  /* well-formed but outside the engine's limits              */
+  TC_ERR_EXTENT = 4,       /* extent <= 0, or layouts that make output elements alias  */
+  TC_ERR_CUDA = 5,         /* a CUDA runtime call failed (tc_last_cuda_error has it)   */
+  TC_ERR_ALIGNMENT = 6,    /* a tensor base pointer is not aligned to its element size */
+  TC_ERR_STATE = 7,        /* call order violated (e.g. changing a committed plan)     */
+  TC_ERR_WORKSPACE = 8     /* workspace too small or missing                           */
+} tc_status;
+
+typedef enum tc_dtype { TC_F64 = 0, TC_F32 = 1 } tc_dtype;
+
+/* Arithmetic path.  AUTO picks per dtype what measured fastest on B200. */
+typedef enum tc_path {
+  TC_PATH_AUTO = 0,
+  TC_PATH_DMMA = 1,  /* fp64 on the tensor pipe (mma.sync f64)     */
+  TC_PATH_DFMA = 2,  /* fp64 on the vector pipe                    */
+  TC_PATH_FFMA = 3,  /* fp32 on the vector pipe                    */
+  TC_PATH_3XTF32 = 4 /* fp32 as three TF32 tensor products         */
+} tc_path;
+
+typedef struct tc_options {
+  int path;       /* tc_path                                                          */
+  int tile_m;     /* 0 = planner's choice; otherwise force the CTA tile (must be one  */
+  int tile_n;     /*     of the compiled shapes, see tc_plan_describe)                */
+  int split_k;    /* 0 = planner's choice, 1 = never split, >1 = that many K slices   */
+  int reserved[4];
+} tc_options;
+
+typedef struct tc_plan tc_plan;
+
+/* ---- expression front end -------------------------------------------------
+ * Same whitespace-sensitive grammar as the reference parser
+ * (cogent/src/algs/bases/tc_gen_inputs.py:28-108): after '[', ']' and ';' are
+ * removed the line must split on blanks into
+ *   name  idx,ext,idx,ext..  (+=|-=|=)  sum(idx,ext,..)  *  name  idx,..  *  name  idx,..
+ * Index names may be any length; tensor names are free.
+ *
+ * tc_expr_describe writes a JSON description of the parsed line into buf
+ * (always NUL terminated, truncated to cap) and returns TC_OK or TC_ERR_PARSE.
+ * It needs no GPU. */
+int tc_expr_describe(const char* expr, char* buf, size_t cap);
+
+/* ---- plan -----------------------------------------------------------------
+ * Replaces running tc_code_generator.py + nvcc on one expression
+ * (cogent/tc_code_generator.py:13-60).  The extents written in the expression
+ * are the defaults; tc_plan_set_extents overrides them by index name, as the
+ * reference drivers do from argv (cogent/drivers/tccg/code_main_tccg_02.c:32-38). */
+int tc_plan_create(const char* expr, int dtype, const tc_options* options, tc_plan** out);
+int tc_plan_set_extents(tc_plan* plan, int n, const char* const* index_names, const int64_t* extents);
+
+/* Optional strided views.  tensor: 0 = output, 1 = left input, 2 = right input.
+ * strides[i] is the element stride of the tensor's i-th index as written in the
+ * expression.  Default: compact column-major from the current extents.  Used to
+ * run one slab of a larger tensor (sharding an external or a contraction index
+ * across GPUs) without copying. */
+int tc_plan_set_strides(tc_plan* plan, int tensor, int n, const int64_t* strides);
+
+/* Freezes extents/strides, chooses the tiling for the current device, uploads
+ * the plan's tables.  Implied by the first execute.  After it the plan is
+ * immutable and may be executed from several threads/streams at once. */
+int tc_plan_commit(tc_plan* plan);
+
+void tc_plan_destroy(tc_plan* plan);
+
+/* JSON: index classes, fused dimensions, tile shape, kernel variant, grid,
+ * algorithmic flops and bytes. */
+int tc_plan_describe(const tc_plan* plan, char* buf, size_t cap);
+/* 2 * prod(all extents), and elemsize * (2|C| + |A| + |B|)  ('=' reads C zero times: |C|). */
+int tc_plan_cost(const tc_plan* plan, double* flops, double* bytes);
+/* Kernel launches one tc_execute enqueues. */
+int tc_plan_launches(const tc_plan* plan);
+/* Bytes of caller-provided workspace tc_execute_ws needs (0 when the plan does not split K). */
+int tc_plan_workspace_bytes(const tc_plan* plan, size_t* bytes);
+
+/* ---- execute --------------------------------------------------------------
+ * Replaces the generated host wrapper sd_t_d2_fusion (kernel launch part,
+ * cogent/src/codes/kernels/tc_interface.py:284-362,1147-1352).  Pointers are
+ * DEVICE pointers to the first element of each tensor; the call only enqueues
+ * work on `stream` (a cudaStream_t, 0 = default stream) and never allocates.
+ * The output must not alias an input.  True accumulate semantics: C += sum
+ * (the reference's generated kernel overwrites C and relies on the driver
+ * having zeroed it; its CPU check accumulates, which is what this does). */
+int tc_execute(tc_plan* plan, void* C, const void* A, const void* B, void* stream);
+/* Same with an explicit workspace (plans with split K use the plan-owned
+ * workspace in tc_execute; concurrent executes of such a plan must each bring
+ * their own through this call). */
+int tc_execute_ws(tc_plan* plan, void* C, const void* A, const void* B, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+/* Blocking convenience over HOST pointers: allocate, copy in (C too), run,
+ * copy C back, free -- what the reference's sd_t_d2_fusion does around its
+ * kernel (cogent/src/codes/others/tc_pre_CUDA_Malloc.py:6-47,
+ * cogent/src/codes/kernels/tc_interface.py:1368-1388). */
+int tc_execute_host(tc_plan* plan, void* C, const void* A, const void* B);
+
+/* ---- diagnostics ------------------------------------------------------------ */
+const char* tc_status_string(int status);
+/* Last CUDA error text seen by the calling thread inside this library. */
+const char* tc_last_cuda_error(void);
+const char* tc_version(void);
+
+/* ---- seeded inputs ------------------------------------------------------------
+ * Counter-based uniform[-1,1) generator shared by tests, bench and shards:
+ * element i of tensor `tensor_id` (0 = C, 1 = A, 2 = B) is a pure function of
+ * (seed, tensor_id, first_index + i), so any slab can be produced in place on
+ * any GPU.  dst is a device pointer to `count` elements. */
+int tc_fill_uniform(void* dst, int64_t count, int dtype, uint64_t seed, int tensor_id,
+                    int64_t first_index, void* stream);
+/* y[i] += alpha * x[i] on device (combines reduce-scattered partial sums into C). */
+int tc_axpy(void* y, const void* x, int64_t count, int dtype, double alpha, void* stream);
+
+/* ---- arithmetic peaks (roofline denominators) -------------------------------------
+ * which: 0 DMMA m8n8k4, 1 DMMA m16n8k4, 2 DMMA m16n8k8, 3 DMMA m16n8k16,
+ *        4 DFMA, 5 FFMA, 6 TF32 mma.sync m16n8k8.  Register-only loops. */
+int tc_peak_measure(int which, int iters, int ctas_per_sm, double* tflops);
+/* Streaming 16-byte read-modify-write over `bytes` of device memory (GB/s, read+write). */
+int tc_peak_measure_rmw(int64_t bytes, double* gbs);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TC_B200_H_ */

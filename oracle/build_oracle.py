@@ -1,0 +1,117 @@
+"""Builds the checker libraries (test infrastructure, never the product path).
+
+  oracle/liboracle.so          the C restatement in tc_oracle.c
+  oracle/_ref/libref_nests.so  the reference's OWN loop nests, compiled from the
+                               57 driver files where they lie in the reference
+                               tree (cogent/drivers/tccg/*.c, tccg-float/*.c),
+                               only when that tree is present
+  oracle/_ref/ref_nests.json   what each compiled nest computes, recovered from
+                               its code (not from its comments, which disagree
+                               with the code in places)
+
+No reference source is copied: every driver is compiled in place with its
+`main`, `post_Correctness` and `pre_Initializing_Input_Tensors` renamed through
+-D so that all of them fit in one shared object; the generated entry they call
+(`sd_t_d2_fusion_`) is stubbed.  gcc is used directly (-std=gnu89: the drivers
+rely on implicit declarations and K&R prototypes).
+
+Usage: python oracle/build_oracle.py [--reference DIR]
+"""
+import json
+import os
+import re
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_DEFAULT = "/root/reference"
+REF_OUT = os.path.join(HERE, "_ref")
+LIB_ORACLE = os.path.join(HERE, "liboracle.so")
+LIB_REF = os.path.join(REF_OUT, "libref_nests.so")
+JSON_REF = os.path.join(REF_OUT, "ref_nests.json")
+
+
+def build_oracle():
+    src = os.path.join(HERE, "tc_oracle.c")
+    if os.path.exists(LIB_ORACLE) and os.path.getmtime(LIB_ORACLE) >= os.path.getmtime(src):
+        return LIB_ORACLE
+    cmd = ["gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-shared", "-fPIC", "-std=c99", src, "-o", LIB_ORACLE]
+    subprocess.run(cmd, check=True)
+    return LIB_ORACLE
+
+
+_IDX = re.compile(r"(?<!size_)idx_(\w+)")
+
+
+def describe_driver(path):
+    """Recovers (expression, size-argument order) from a driver's post_Correctness CODE."""
+    text = open(path).read()
+    body = text[text.rindex("void post_Correctness("):]  # the definition (the prototype comes first)
+    sig = body[:body.index(")") + 1]
+    is_float = "float* h_C" in sig or "float *h_C" in sig
+    size_args = re.findall(r"int\s+size_idx_(\w+)", sig)
+    loops = re.findall(r"for\s*\(\s*idx_(\w+)\s*=\s*0", body)
+    m = re.search(r"tmp_r_idx\s*=\s*([^;]+);", body)
+    out_idx = _IDX.findall(m.group(1))
+    m = re.search(r"h_C_chk\[tmp_r_idx\]\s*([+-])=\s*h_A\[(.*?)\]\s*\*\s*h_B\[(.*?)\];", body, re.S)
+    op = m.group(1) + "="
+    a_idx = _IDX.findall(m.group(2))
+    b_idx = _IDX.findall(m.group(3))
+    sum_idx = [i for i in loops if i not in out_idx]
+    assert loops[:len(out_idx)] == out_idx, (path, loops, out_idx)  # output loops outermost, in output order
+    assert sorted(size_args) == sorted(out_idx + sum_idx), (path, size_args, out_idx, sum_idx)
+    expr = "t3 [%s] %s sum(%s) * t2 [%s] * v2 [%s];" % (
+        ",".join("%s,16" % i for i in out_idx), op, ",".join("%s,16" % i for i in sum_idx),
+        ",".join(a_idx), ",".join(b_idx))
+    return {"expr": expr, "size_args": size_args, "dtype": "f32" if is_float else "f64"}
+
+
+def build_ref(reference=REF_DEFAULT):
+    drivers = []
+    for sub, tag in (("tccg", "f64"), ("tccg-float", "f32")):
+        d = os.path.join(reference, "cogent", "drivers", sub)
+        if not os.path.isdir(d):
+            continue
+        for f in sorted(os.listdir(d)):
+            mm = re.match(r"code_main_tccg_(\d+)\.c$", f)
+            if mm:
+                drivers.append(("%s_%s" % (tag, mm.group(1)), os.path.join(d, f)))
+    if not drivers:
+        return None
+    os.makedirs(REF_OUT, exist_ok=True)
+    objs, table = [], {}
+    for tag, path in drivers:
+        info = describe_driver(path)
+        info["symbol"] = "ref_post_" + tag
+        info["source"] = os.path.relpath(path, reference)
+        table[tag] = info
+        obj = os.path.join(REF_OUT, tag + ".o")
+        cmd = ["gcc", "-std=gnu89", "-O2", "-ffp-contract=off", "-w", "-fPIC", "-c", path, "-o", obj,
+               "-Dmain=ref_main_" + tag, "-Dpost_Correctness=ref_post_" + tag,
+               "-Dpre_Initializing_Input_Tensors=ref_pre_" + tag]
+        subprocess.run(cmd, check=True)
+        objs.append(obj)
+    stub = os.path.join(REF_OUT, "stub.c")
+    with open(stub, "w") as f:
+        f.write("/* generated: the drivers' call into the generated GPU entry does nothing here */\n"
+                "void sd_t_d2_fusion_() {}\n")
+    subprocess.run(["gcc", "-std=gnu89", "-w", "-shared", "-fPIC", "-o", LIB_REF, stub] + objs, check=True)
+    for o in objs:
+        os.remove(o)
+    with open(JSON_REF, "w") as f:
+        json.dump(table, f, indent=1, sort_keys=True)
+    return LIB_REF
+
+
+def build_all(reference=REF_DEFAULT):
+    out = [build_oracle()]
+    if os.path.isdir(reference):
+        out.append(build_ref(reference))
+    return out
+
+
+if __name__ == "__main__":
+    ref = REF_DEFAULT
+    if "--reference" in sys.argv:
+        ref = sys.argv[sys.argv.index("--reference") + 1]
+    print(build_all(ref))
