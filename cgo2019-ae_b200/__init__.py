@@ -35,7 +35,7 @@ class TcError(RuntimeError):
 
 class Options(ctypes.Structure):
     _fields_ = [("path", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
-                ("split_k", ctypes.c_int), ("reserved", ctypes.c_int * 4)]
+                ("split_k", ctypes.c_int), ("variant", ctypes.c_int), ("reserved", ctypes.c_int * 3)]
 
 
 _lib = None
@@ -131,13 +131,14 @@ def _ptr(x):
 class Plan:
     """One contraction: expression + dtype (+ extents, strides, options)."""
 
-    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None):
+    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None, variant=0):
         self._h = ctypes.c_void_p()
         opt = Options()
         opt.path = path
         if tile:
             opt.tile_m, opt.tile_n = tile
         opt.split_k = split_k
+        opt.variant = variant
         self.expr = expr
         self.dtype = dtype
         _check(lib().tc_plan_create(expr.encode(), dtype, ctypes.byref(opt), ctypes.byref(self._h)), "tc_plan_create")

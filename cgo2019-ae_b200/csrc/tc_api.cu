@@ -56,6 +56,7 @@ extern "C" int tc_expr_describe(const char* expr, char* buf, size_t cap) {
 // -------------------------------------------------------- kernel dispatch ----
 extern "C" {
 int tc_inst_dmma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+int tc_inst_dmma_128w16(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 int tc_inst_dmma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 int tc_inst_dfma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 int tc_inst_dfma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
@@ -65,7 +66,8 @@ int tc_inst_ffma_64(int, int, const TcKernelArgs*, void*, const void*, const voi
 
 static tc_inst_fn pick_inst(const TcKernelChoice& c) {
   const bool big = c.bm == 128;
-  if (c.dtype == TC_F64 && c.math == TC_MATH_DMMA) return big ? tc_inst_dmma_128 : tc_inst_dmma_64;
+  if (c.dtype == TC_F64 && c.math == TC_MATH_DMMA)
+    return big ? (c.variant == 1 ? tc_inst_dmma_128w16 : tc_inst_dmma_128) : tc_inst_dmma_64;
   if (c.dtype == TC_F64) return big ? tc_inst_dfma_128 : tc_inst_dfma_64;
   return big ? tc_inst_ffma_128 : tc_inst_ffma_64;
 }

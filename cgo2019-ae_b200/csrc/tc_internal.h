@@ -80,6 +80,7 @@ struct TcKernelChoice {
   int dtype;      // tc_dtype
   int math;       // TcMath
   int bm, bn;     // CTA tile
+  int variant;    // warp layout of the tile (0-based)
   bool vec_x, vec_y;  // 16-byte loads along the external index of X / Y
 };
 

@@ -79,7 +79,10 @@ struct Cfg {
   static constexpr int WM = BM / WARPS_M_, WN = BN / WARPS_N_;
   static constexpr int WARPS_M = WARPS_M_, WARPS_N = WARPS_N_;
   static constexpr int LDX = BM + 4, LDY = BN + 4;
-  static constexpr int TABLE_BYTES = (2 * BM + 2 * BN) * 8;
+  // Contraction offsets of the stages in flight live in a shared ring (filled by
+  // cp.async one pipeline depth ahead), so the loaders never wait on global memory.
+  static constexpr int KRING = 2 * STAGES - 2;
+  static constexpr int TABLE_BYTES = (2 * BM + 2 * BN + KRING * 2 * BK) * 8;
   static constexpr int STAGE_ELEMS = BK * (LDX + LDY);
   static constexpr int SMEM_BYTES = TABLE_BYTES + STAGES * STAGE_ELEMS * ES;
 };
@@ -106,7 +109,7 @@ __device__ __forceinline__ void decode(const TcDims& d, uint32_t flat, uint32_t 
 // 16-byte loads along the external index: thread -> (vector of VW externals, k).
 template <class CF, int ROWS, int LD>
 __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
-                                               const int64_t* s_off, const int64_t* __restrict__ koff,
+                                               const int64_t* s_off, const int64_t* s_koff,
                                                uint32_t k0, uint32_t kend, int tid) {
   constexpr int VPR = ROWS / CF::VW;            // vectors per k row
   constexpr int SLOTS = VPR * CF::BK;
@@ -120,8 +123,7 @@ __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const ty
     const int64_t eo = s_off[ev * CF::VW];
     const uint32_t k = k0 + kk;
     const bool ok = eo >= 0 && k < kend;
-    const int64_t ko = ok ? koff[k] : 0;
-    const typename CF::T* src = ok ? g + eo + ko : g;
+    const typename CF::T* src = ok ? g + eo + s_koff[kk] : g;
     cp_async16(smem_u32(s_stage + kk * LD + ev * CF::VW), src, ok);
   }
 }
@@ -129,31 +131,43 @@ __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const ty
 // Element-wise loads.  A warp covers `lanes_k` consecutive k by 32/lanes_k
 // consecutive externals, so that the lanes that walk the tensor's fastest index
 // read whole 32-byte sectors; the write into the external-major image is a
-// transposing scatter.
+// transposing scatter.  The thread -> element map does not change from stage to
+// stage, so it is computed once (elem_slots) and kept packed in registers:
+//   bits 0-15 element offset inside the stage image, 16-23 k, 24-31 external.
 template <class CF, int ROWS, int LD>
-__device__ __forceinline__ void load_stage_elem(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
-                                                const int64_t* s_off, const int64_t* __restrict__ koff,
-                                                uint32_t k0, uint32_t kend, int tid, int lanes_k) {
-  constexpr int PER = ROWS * CF::BK / CF::THREADS;  // elements per thread per stage
+struct ElemSlots {
+  static constexpr int PER = ROWS * CF::BK / CF::THREADS;  // elements per thread per stage
   static_assert(ROWS * CF::BK % CF::THREADS == 0, "loader shape");
-  const int lane = tid & 31, warp = tid >> 5;
-  const int lanes_e = 32 / lanes_k;
-  const int kslabs = CF::BK / lanes_k;  // slabs along k
-  const int lk = lane % lanes_k, le = lane / lanes_k;
+  static_assert(CF::BK * LD < 65536 && ROWS <= 256, "slot packing");
+  uint32_t slot[PER];
+  __device__ __forceinline__ void init(int tid, int lanes_k) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int lanes_e = 32 / lanes_k;
+    const int kslabs = CF::BK / lanes_k;
+    const int lk = lane % lanes_k, le = lane / lanes_k;
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int slab = warp * PER + j;
-    const int ks = slab % kslabs, esl = slab / kslabs;
-    const int kk = ks * lanes_k + lk;
-    const int el = esl * lanes_e + le;
-    const int64_t eo = s_off[el];
-    const uint32_t k = k0 + kk;
-    const bool ok = eo >= 0 && k < kend;
-    const int64_t ko = ok ? koff[k] : 0;
-    const typename CF::T* src = ok ? g + eo + ko : g;
-    cp_async_elem<CF::ES>(smem_u32(s_stage + kk * LD + el), src, ok);
+    for (int j = 0; j < PER; ++j) {
+      const int slab = warp * PER + j;
+      const int kk = (slab % kslabs) * lanes_k + lk;
+      const int el = (slab / kslabs) * lanes_e + le;
+      slot[j] = (uint32_t)(kk * LD + el) | ((uint32_t)kk << 16) | ((uint32_t)el << 24);
+    }
   }
-}
+  __device__ __forceinline__ void load(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
+                                       const int64_t* s_off, const int64_t* s_koff, uint32_t k0,
+                                       uint32_t kend) const {
+    const uint32_t sbase = smem_u32(s_stage);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const uint32_t sl = slot[j];
+      const int64_t eo = s_off[sl >> 24];
+      const uint32_t kk = (sl >> 16) & 0xffu;
+      const bool ok = eo >= 0 && k0 + kk < kend;
+      const typename CF::T* src = ok ? g + eo + s_koff[kk] : g;
+      cp_async_elem<CF::ES>(sbase + (sl & 0xffffu) * CF::ES, src, ok);
+    }
+  }
+};
 
 // --------------------------------------------------------------- kernel ----
 template <class CF>
@@ -168,7 +182,8 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
   int64_t* offc_m = offx_m + BM;
   int64_t* offy_n = offc_m + BM;
   int64_t* offc_n = offy_n + BN;
-  T* Xs = reinterpret_cast<T*>(offc_n + BN);
+  int64_t* kring = offc_n + BN;  // [KRING][2][BK]
+  T* Xs = reinterpret_cast<T*>(kring + CF::KRING * 2 * BK);
   T* Ys = Xs + STAGES * BK * LDX;
 
   const int tid = threadIdx.x;
@@ -185,21 +200,42 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
     else decode(p.N, n0 + (i - BM), p.Nflat, &offy_n[i - BM], &offc_n[i - BM]);
   }
+  // Contraction offsets of the first KRING stages, read directly.
+  for (int i = tid; i < CF::KRING * 2 * BK; i += CF::THREADS) {
+    const int st = i / (2 * BK), r = i % (2 * BK);
+    const uint32_t k = kbeg + st * BK + (r % BK);
+    kring[i] = k < kend ? (r < BK ? p.koff_x[k] : p.koff_y[k]) : 0;
+  }
   __syncthreads();
 
   const int nk = (int)((kend - kbeg + BK - 1) / BK);
+  ElemSlots<CF, BM, LDX> slots_x;
+  ElemSlots<CF, BN, LDY> slots_y;
+  if constexpr (!CF::VECX) slots_x.init(tid, p.lanes_k_x);
+  if constexpr (!CF::VECY) slots_y.init(tid, p.lanes_k_y);
   auto issue = [&](int it) {
     if (it < nk) {
       const int st = it % STAGES;
       const uint32_t k0 = kbeg + it * BK;
       T* xs = Xs + st * BK * LDX;
       T* ys = Ys + st * BK * LDY;
-      if constexpr (CF::VECX) load_stage_vec<CF, BM, LDX>(xs, X, offx_m, p.koff_x, k0, kend, tid);
-      else load_stage_elem<CF, BM, LDX>(xs, X, offx_m, p.koff_x, k0, kend, tid, p.lanes_k_x);
-      if constexpr (CF::VECY) load_stage_vec<CF, BN, LDY>(ys, Y, offy_n, p.koff_y, k0, kend, tid);
-      else load_stage_elem<CF, BN, LDY>(ys, Y, offy_n, p.koff_y, k0, kend, tid, p.lanes_k_y);
+      const int64_t* kx = kring + (it % CF::KRING) * 2 * BK;
+      if constexpr (CF::VECX) load_stage_vec<CF, BM, LDX>(xs, X, offx_m, kx, k0, kend, tid);
+      else slots_x.load(xs, X, offx_m, kx, k0, kend);
+      if constexpr (CF::VECY) load_stage_vec<CF, BN, LDY>(ys, Y, offy_n, kx + BK, k0, kend, tid);
+      else slots_y.load(ys, Y, offy_n, kx + BK, k0, kend);
     }
     cp_async_commit();
+  };
+  // Stage `it`'s data group also carries the offsets of stage it + KRING, into the
+  // ring slot whose last reader (the issue of stage `it`) is behind a barrier.
+  auto issue_koff = [&](int it) {
+    const int nx = it + CF::KRING;
+    if (tid < 2 * BK && nx < nk) {
+      const uint32_t k = kbeg + nx * BK + (tid % BK);
+      const int64_t* src = (tid < BK ? p.koff_x : p.koff_y) + (k < kend ? k : 0);
+      cp_async8(smem_u32(kring + (nx % CF::KRING) * 2 * BK + tid), src, k < kend);
+    }
   };
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) issue(s);
@@ -225,6 +261,7 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     for (int it = 0; it < nk; ++it) {
       cp_async_wait<STAGES - 2>();
       __syncthreads();
+      issue_koff(it);
       issue(it + STAGES - 1);
       const int st = it % STAGES;
       const T* xs = Xs + st * BK * LDX + wm0 + 2 * g;
@@ -351,6 +388,7 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     for (int it = 0; it < nk; ++it) {
       cp_async_wait<STAGES - 2>();
       __syncthreads();
+      issue_koff(it);
       issue(it + STAGES - 1);
       const int st = it % STAGES;
       const T* xs = Xs + st * BK * LDX + tx * VW;

@@ -250,6 +250,8 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   }
   c.bm = bm;
   c.bn = bn;
+  c.variant = p->opt.variant > 0 ? p->opt.variant - 1 : 0;
+  if (c.variant > 1 || (c.variant == 1 && !(c.math == TC_MATH_DMMA && bm == 128))) { *why = "requested kernel variant is not compiled in"; return TC_ERR_UNSUPPORTED; }
   a.tiles_m = (uint32_t)((mf + bm - 1) / bm);
   a.tiles_n = (uint32_t)((nf + bn - 1) / bn);
   const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
@@ -295,7 +297,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << tc_tile_bk(p.choice.dtype, p.choice.math)
-      << "],\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
+      << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"beta\":" << a.beta

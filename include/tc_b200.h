@@ -52,7 +52,8 @@ typedef struct tc_options {
   int tile_m;     /* 0 = planner's choice; otherwise force the CTA tile (must be one  */
   int tile_n;     /*     of the compiled shapes, see tc_plan_describe)                */
   int split_k;    /* 0 = planner's choice, 1 = never split, >1 = that many K slices   */
-  int reserved[4];
+  int variant;    /* 0 = planner's choice; otherwise 1-based warp layout of the tile  */
+  int reserved[3];
 } tc_options;
 
 typedef struct tc_plan tc_plan;
