@@ -26,17 +26,35 @@ def _newer(target, deps):
     return all(os.path.getmtime(d) <= t for d in deps)
 
 
+def _generate_kernel_units():
+    """One translation unit per line of csrc/tc_kernel_list.h (written only when its text changes)."""
+    import re
+    text = open(os.path.join(CSRC, "tc_kernel_list.h")).read()
+    units = []
+    for m in re.finditer(r"^\s*X\((\w+),\s*(\w+),\s*(\w+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", text, re.M):
+        name, t, math, bm, bn, wm, wn, st, minb, _variant = m.groups()
+        body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'
+                "TC_DEFINE_INST(tc_inst_%s, %s, %s, %s, %s, %s, %s, %s, %s)\n" % (name, t, math, bm, bn, wm, wn, st, minb))
+        path = os.path.join(OBJ, "gen_%s.cu" % name)
+        if not os.path.exists(path) or open(path).read() != body:
+            with open(path, "w") as f:
+                f.write(body)
+        units.append(path)
+    return units
+
+
 def build(force=False, verbose=False):
     os.makedirs(OBJ, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers.append(os.path.join(HERE, "..", "include", "tc_b200.h"))
-    sources = sorted(f for f in os.listdir(CSRC) if f.endswith((".cu", ".cpp")))
+    sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith((".cu", ".cpp"))]
+    sources += _generate_kernel_units()
     jobs = []
     objs = []
-    for src in sources:
+    for path in sources:
+        src = os.path.basename(path)
         obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
         objs.append(obj)
-        path = os.path.join(CSRC, src)
         if not force and _newer(obj, [path] + headers):
             continue
         cmd = [NVCC] + ARCH + COMMON + (["-Xptxas", "-v"] if verbose else []) + ["-x", "cu", "-c", path, "-o", obj]

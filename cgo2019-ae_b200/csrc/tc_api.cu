@@ -54,38 +54,67 @@ extern "C" int tc_expr_describe(const char* expr, char* buf, size_t cap) {
 }
 
 // -------------------------------------------------------- kernel dispatch ----
-extern "C" {
-int tc_inst_dmma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_dmma_128w16(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_dmma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_dfma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_dfma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_ffma_128(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
-int tc_inst_ffma_64(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+#include "tc_kernel_list.h"
+
+#define TC_DECLARE(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB, VARIANT) \
+  extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+TC_KERNEL_LIST(TC_DECLARE)
+#undef TC_DECLARE
+
+namespace {
+struct KernelEntry {
+  const char* name;
+  int dtype, math, bm, bn, variant;
+  tc_inst_fn fn;
+};
+template <typename T> constexpr int dtype_of() { return sizeof(T) == 8 ? TC_F64 : TC_F32; }
+#define TC_ENTRY(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB, VARIANT) {#NAME, dtype_of<T>(), MATH, BM, BN, VARIANT, tc_inst_##NAME},
+const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY)};
+#undef TC_ENTRY
+
+const KernelEntry* find_kernel(int dtype, int math, int bm, int bn, int variant) {
+  for (const KernelEntry& k : kKernels)
+    if (k.dtype == dtype && k.math == math && k.bm == bm && k.bn == bn && k.variant == variant) return &k;
+  return nullptr;
+}
+}  // namespace
+
+bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant) {
+  return find_kernel(dtype, math, bm, bn, variant) != nullptr;
 }
 
 static tc_inst_fn pick_inst(const TcKernelChoice& c) {
-  const bool big = c.bm == 128;
-  if (c.dtype == TC_F64 && c.math == TC_MATH_DMMA)
-    return big ? (c.variant == 1 ? tc_inst_dmma_128w16 : tc_inst_dmma_128) : tc_inst_dmma_64;
-  if (c.dtype == TC_F64) return big ? tc_inst_dfma_128 : tc_inst_dfma_64;
-  return big ? tc_inst_ffma_128 : tc_inst_ffma_64;
+  const KernelEntry* k = find_kernel(c.dtype, c.math, c.bm, c.bn, c.variant);
+  return k ? k->fn : nullptr;
 }
 
 int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk) {
-  if (bk) *bk = tc_tile_bk(c.dtype, c.math);
-  return pick_inst(c)(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
+  if (bk) *bk = TC_BK;
+  tc_inst_fn fn = pick_inst(c);
+  if (!fn) return TC_ERR_UNSUPPORTED;
+  return fn(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
 }
 
 int tc_kernels_prepare(const TcKernelChoice& c) {
   // Both loader variants of each operand: a misaligned base pointer at execute
   // time demotes 16-byte loads to element loads.
+  tc_inst_fn fn = pick_inst(c);
+  if (!fn) return TC_ERR_UNSUPPORTED;
   for (int vx = 0; vx <= (c.vec_x ? 1 : 0); ++vx)
     for (int vy = 0; vy <= (c.vec_y ? 1 : 0); ++vy) {
-      const int st = pick_inst(c)(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
+      const int st = fn(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
       if (st != TC_OK) return st;
     }
   return TC_OK;
+}
+
+// Resident CTAs of the chosen kernel on the whole device (0 on failure).
+static int resident_ctas(const TcKernelChoice& c) {
+  tc_inst_fn fn = pick_inst(c);
+  int per_sm = 0, dev = 0, sms = 0;
+  if (!fn || fn(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_OCCUPANCY, &per_sm, nullptr) != TC_OK) return 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return per_sm * sms;
 }
 
 int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, const void* X, const void* Y,
@@ -97,17 +126,15 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   const uintptr_t cu = reinterpret_cast<uintptr_t>(C);
   if ((cu & 15) != 0) a.vec_c = 1;
   const int vx = c.vec_x && x16, vy = c.vec_y && y16;
-  int st = pick_inst(c)(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
+  tc_inst_fn fn = pick_inst(c);
+  if (!fn) return TC_ERR_UNSUPPORTED;
+  int st = fn(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
   if (st != TC_OK) return st;
   if (a.ksplit > 1) {
     const unsigned grid = a.tiles_m * a.tiles_n;
-    if (p.dtype == TC_F64) {
-      if (c.bm == 128) tck::tc_combine_kernel<double, 128, 128><<<grid, 256, 0, stream>>>(a, static_cast<double*>(C));
-      else tck::tc_combine_kernel<double, 64, 64><<<grid, 256, 0, stream>>>(a, static_cast<double*>(C));
-    } else {
-      if (c.bm == 128) tck::tc_combine_kernel<float, 128, 128><<<grid, 256, 0, stream>>>(a, static_cast<float*>(C));
-      else tck::tc_combine_kernel<float, 64, 64><<<grid, 256, 0, stream>>>(a, static_cast<float*>(C));
-    }
+    const size_t smem = (size_t)(a.bm + a.bn) * sizeof(int64_t);
+    if (p.dtype == TC_F64) tck::tc_combine_kernel<double><<<grid, 256, smem, stream>>>(a, static_cast<double*>(C));
+    else tck::tc_combine_kernel<float><<<grid, 256, smem, stream>>>(a, static_cast<float*>(C));
     TC_CUDA_OK(cudaGetLastError());
   }
   return TC_OK;
@@ -175,6 +202,9 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   TC_CUDA_OK(cudaGetDevice(&dev));
   st = tc_kernels_prepare(p->choice);
   if (st != TC_OK) return st;
+  p->args.prefetch_dist = p->opt.l2_prefetch == 1 ? 0u : (uint32_t)resident_ctas(p->choice);
+  p->args.c_mode = p->opt.reserved[0] & 1;
+  p->args.c_stream = (p->opt.reserved[0] >> 1) & 1;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));
   TC_CUDA_OK(cudaMemcpy(p->d_koff, p->h_koff_x.data(), kb, cudaMemcpyHostToDevice));

@@ -1,4 +1,4 @@
-// Instantiation helper: one translation unit per (arithmetic, dtype, CTA tile)
+// Instantiation helper: one translation unit per line of tc_kernel_list.h
 // so the variants compile in parallel.  Each unit exports one dispatcher that
 // selects the loader variant (16-byte loads along the external index of X / Y
 // or element-wise loads) and either launches, prepares (opt-in shared memory)
@@ -6,7 +6,7 @@
 #pragma once
 #include "tc_kernels.cuh"
 
-enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2 };
+enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3 };
 
 typedef int (*tc_inst_fn)(int vec_x, int vec_y, const TcKernelArgs* args, void* C, const void* X, const void* Y,
                           cudaStream_t stream, int mode, int* threads, int* smem_bytes);
@@ -23,6 +23,12 @@ int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cu
     if (smem_bytes) *smem_bytes = CF::SMEM_BYTES;
     return TC_OK;
   }
+  if (mode == TC_INST_OCCUPANCY) {  // resident CTAs per SM -> *threads
+    int n = 0;
+    TC_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, CF::THREADS, CF::SMEM_BYTES));
+    if (threads) *threads = n;
+    return TC_OK;
+  }
   if (mode == TC_INST_PREPARE) {
     TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CF::SMEM_BYTES));
     return TC_OK;
@@ -36,11 +42,11 @@ int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cu
 
 }  // namespace tck
 
-#define TC_DEFINE_INST(NAME, T, MATH, BM, BN, WMN, WNN, STAGES)                                                  \
+#define TC_DEFINE_INST(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                                  \
   extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,              \
                       cudaStream_t s, int mode, int* threads, int* smem) {                                       \
-    if (vx && vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, true, true>>(a, C, X, Y, s, mode, threads, smem);   \
-    if (vx) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, true, false>>(a, C, X, Y, s, mode, threads, smem);        \
-    if (vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, false, true>>(a, C, X, Y, s, mode, threads, smem);        \
-    return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, false, false>>(a, C, X, Y, s, mode, threads, smem);               \
+    if (vx && vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, true, true>>(a, C, X, Y, s, mode, threads, smem);   \
+    if (vx) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, true, false>>(a, C, X, Y, s, mode, threads, smem);        \
+    if (vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, false, true>>(a, C, X, Y, s, mode, threads, smem);        \
+    return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, false, false>>(a, C, X, Y, s, mode, threads, smem);               \
   }

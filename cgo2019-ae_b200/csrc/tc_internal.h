@@ -62,6 +62,10 @@ struct TcKernelArgs {
   TcDims M, N;
   uint32_t Mflat, Nflat, Kflat;
   uint32_t tiles_m, tiles_n;
+  int32_t bm, bn;    // CTA tile of the chosen kernel
+  int32_t c_mode;    // 0: read-modify-write epilogue, 1: accumulators start from C
+  int32_t c_stream;  // cache-streaming hints on accesses to C
+  uint32_t prefetch_dist;  // blocks ahead whose output tile is prefetched into L2 (0 = off)
   uint32_t k_chunk;  // flattened contraction range per K slice (multiple of the K step)
   uint32_t ksplit;   // number of K slices (1 = the kernel applies the result to C itself)
   const int64_t* koff_x;  // [Kflat] offset of flattened contraction index k inside X
@@ -125,8 +129,8 @@ int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int*
 int tc_kernels_prepare(const TcKernelChoice& c);  // opt-in shared memory attribute
 #endif
 
-// Compiled CTA tiles.
-bool tc_tile_supported(int dtype, int math, int bm, int bn);
-int tc_tile_bk(int dtype, int math);
+// Compiled kernels (registry built from tc_kernel_list.h).
+bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant);
+constexpr int TC_BK = 16;  // contraction step of every kernel
 
 #endif  // TC_INTERNAL_H_

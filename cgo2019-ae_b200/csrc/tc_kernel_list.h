@@ -1,0 +1,28 @@
+// The compiled contraction kernels: one line per (arithmetic, dtype, CTA tile,
+// warp layout).  build.py turns every line into its own translation unit
+// (csrc/_obj/gen_<name>.cu) so they compile in parallel; tc_api.cu expands the
+// same list into the dispatch registry.
+//
+//   X(name, T, MATH, BM, BN, WARPS_M, WARPS_N, STAGES, MIN_CTAS_PER_SM, VARIANT)
+//
+// DMMA: WARPS_M x WARPS_N warps, warp tile (BM/WARPS_M) x (BN/WARPS_N), both
+// multiples of 16.  SIMT: (BM/8) x (BN/8) threads with 8 x 8 outputs each
+// (WARPS_* unused).  VARIANT distinguishes warp layouts of the same tile.
+#ifndef TC_KERNEL_LIST_H_
+#define TC_KERNEL_LIST_H_
+
+#define TC_KERNEL_LIST(X)                                                  \
+  X(dmma_128x128_w8, double, TC_MATH_DMMA, 128, 128, 2, 4, 4, 1, 0)        \
+  X(dmma_128x128_w16, double, TC_MATH_DMMA, 128, 128, 4, 4, 4, 1, 1)       \
+  X(dmma_128x64_w4, double, TC_MATH_DMMA, 128, 64, 2, 2, 3, 2, 0)          \
+  X(dmma_128x64_w8, double, TC_MATH_DMMA, 128, 64, 4, 2, 3, 2, 1)          \
+  X(dmma_128x96_w8, double, TC_MATH_DMMA, 128, 96, 4, 2, 3, 1, 0)          \
+  X(dmma_64x96_w4, double, TC_MATH_DMMA, 64, 96, 2, 2, 3, 3, 0)            \
+  X(dmma_64x64_w4, double, TC_MATH_DMMA, 64, 64, 2, 2, 3, 4, 0)            \
+  X(dfma_128x128, double, TC_MATH_SIMT, 128, 128, 1, 1, 3, 1, 0)           \
+  X(dfma_64x64, double, TC_MATH_SIMT, 64, 64, 1, 1, 4, 1, 0)               \
+  X(ffma_128x128, float, TC_MATH_SIMT, 128, 128, 1, 1, 4, 2, 0)            \
+  X(ffma_128x64, float, TC_MATH_SIMT, 128, 64, 1, 1, 4, 3, 0)              \
+  X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)
+
+#endif  // TC_KERNEL_LIST_H_

@@ -63,12 +63,13 @@ template <> struct Vec16<double> { using type = double2; static constexpr int W 
 template <> struct Vec16<float> { using type = float4; static constexpr int W = 4; };
 
 // ------------------------------------------------------------ configuration ----
-template <typename T_, int MATH_, int BM_, int BN_, int WARPS_M_, int WARPS_N_, int STAGES_, bool VECX_, bool VECY_>
+template <typename T_, int MATH_, int BM_, int BN_, int WARPS_M_, int WARPS_N_, int STAGES_, int MINB_, bool VECX_, bool VECY_>
 struct Cfg {
   using T = T_;
   static constexpr int MATH = MATH_;
   static constexpr int BM = BM_, BN = BN_, BK = 16;
   static constexpr int STAGES = STAGES_;
+  static constexpr int MIN_CTAS = MINB_;
   static constexpr bool VECX = VECX_, VECY = VECY_;
   static constexpr int ES = (int)sizeof(T);
   static constexpr int VW = 16 / ES;  // elements per 16 bytes
@@ -82,7 +83,8 @@ struct Cfg {
   // Contraction offsets of the stages in flight live in a shared ring (filled by
   // cp.async one pipeline depth ahead), so the loaders never wait on global memory.
   static constexpr int KRING = 2 * STAGES - 2;
-  static constexpr int TABLE_BYTES = (2 * BM + 2 * BN + KRING * 2 * BK) * 8;
+  // + output offsets of the tile whose C is prefetched into L2 (BM + BN entries)
+  static constexpr int TABLE_BYTES = (3 * BM + 3 * BN + KRING * 2 * BK) * 8;
   static constexpr int STAGE_ELEMS = BK * (LDX + LDY);
   static constexpr int SMEM_BYTES = TABLE_BYTES + STAGES * STAGE_ELEMS * ES;
 };
@@ -92,6 +94,11 @@ struct Cfg {
 // dimensions; -1 marks "outside the tensor".
 __device__ __forceinline__ void decode(const TcDims& d, uint32_t flat, uint32_t limit, int64_t* off_in, int64_t* off_out) {
   if (flat >= limit) { *off_in = -1; *off_out = -1; return; }
+  if (d.n == 1) {  // one fused dimension: the flattened index is the coordinate
+    *off_in = (int64_t)flat * d.s_in[0];
+    *off_out = (int64_t)flat * d.s_out[0];
+    return;
+  }
   int64_t oi = 0, oo = 0;
 #pragma unroll 1
   for (int i = 0; i < d.n; ++i) {
@@ -140,16 +147,18 @@ struct ElemSlots {
   static_assert(ROWS * CF::BK % CF::THREADS == 0, "loader shape");
   static_assert(CF::BK * LD < 65536 && ROWS <= 256, "slot packing");
   uint32_t slot[PER];
-  __device__ __forceinline__ void init(int tid, int lanes_k) {
+  // lg = log2(lanes walking k); BK and the warp size are powers of two, so the
+  // slab arithmetic is shifts and masks.
+  __device__ __forceinline__ void init(int tid, int lg) {
+    static_assert(CF::BK == 16, "slab arithmetic assumes BK = 16");
     const int lane = tid & 31, warp = tid >> 5;
-    const int lanes_e = 32 / lanes_k;
-    const int kslabs = CF::BK / lanes_k;
-    const int lk = lane % lanes_k, le = lane / lanes_k;
+    const int lk = lane & ((1 << lg) - 1), le = lane >> lg;
+    const int ks_bits = 4 - lg;  // log2(slabs along k)
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
       const int slab = warp * PER + j;
-      const int kk = (slab % kslabs) * lanes_k + lk;
-      const int el = (slab / kslabs) * lanes_e + le;
+      const int kk = ((slab & ((1 << ks_bits) - 1)) << lg) + lk;
+      const int el = ((slab >> ks_bits) << (5 - lg)) + le;
       slot[j] = (uint32_t)(kk * LD + el) | ((uint32_t)kk << 16) | ((uint32_t)el << 24);
     }
   }
@@ -171,7 +180,7 @@ struct ElemSlots {
 
 // --------------------------------------------------------------- kernel ----
 template <class CF>
-__global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_constant__ TcKernelArgs p,
+__global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(const __grid_constant__ TcKernelArgs p,
                                                                    typename CF::T* __restrict__ C,
                                                                    const typename CF::T* __restrict__ X,
                                                                    const typename CF::T* __restrict__ Y) {
@@ -183,7 +192,9 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
   int64_t* offy_n = offc_m + BM;
   int64_t* offc_n = offy_n + BN;
   int64_t* kring = offc_n + BN;  // [KRING][2][BK]
-  T* Xs = reinterpret_cast<T*>(kring + CF::KRING * 2 * BK);
+  int64_t* pf_m = kring + CF::KRING * 2 * BK;
+  int64_t* pf_n = pf_m + BM;
+  T* Xs = reinterpret_cast<T*>(pf_n + BN);
   T* Ys = Xs + STAGES * BK * LDX;
 
   const int tid = threadIdx.x;
@@ -211,8 +222,8 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
   const int nk = (int)((kend - kbeg + BK - 1) / BK);
   ElemSlots<CF, BM, LDX> slots_x;
   ElemSlots<CF, BN, LDY> slots_y;
-  if constexpr (!CF::VECX) slots_x.init(tid, p.lanes_k_x);
-  if constexpr (!CF::VECY) slots_y.init(tid, p.lanes_k_y);
+  if constexpr (!CF::VECX) slots_x.init(tid, p.lanes_k_x == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
+  if constexpr (!CF::VECY) slots_y.init(tid, p.lanes_k_y == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
   auto issue = [&](int it) {
     if (it < nk) {
       const int st = it % STAGES;
@@ -237,8 +248,40 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
       cp_async8(smem_u32(kring + (nx % CF::KRING) * 2 * BK + tid), src, k < kend);
     }
   };
-#pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) issue(s);
+  // How `+=` / `-=` reaches C when K is not split (p.c_mode):
+  //   0  read-modify-write in the epilogue; the CTA prefetches its own C tile into
+  //      L2 before the pipeline fills, so the epilogue loads wait on L2, not DRAM;
+  //   1  the accumulators START as alpha*C (alpha = +-1, exact), the epilogue only
+  //      stores alpha*acc; the C tile of a CTA one wave ahead is prefetched into L2.
+  const bool accumulate = p.ksplit == 1 && p.beta != 0;
+  const bool init_from_c = accumulate && p.c_mode == 1;
+  const bool rmw = accumulate && p.c_mode == 0;
+  const bool stream = p.c_stream != 0;  // cache-streaming hints on the accesses to C
+
+  auto prefetch_tile = [&](const int64_t* tm, const int64_t* tn) {
+    constexpr int SEC = 32 / CF::ES;  // elements per 32-byte sector
+    constexpr int SPR = BM / SEC;     // sectors per tile row
+    for (int i = tid; i < SPR * BN; i += CF::THREADS) {
+      const int64_t cm = tm[(i % SPR) * SEC], cn = tn[i / SPR];
+      if (cm >= 0 && cn >= 0) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(C + cn + cm));
+    }
+  };
+  auto prefetch_next = [&]() {
+    if (!accumulate || p.prefetch_dist == 0) return;
+    if (rmw) { prefetch_tile(offc_m, offc_n); return; }
+    const uint32_t nb = bid + p.prefetch_dist;
+    if (nb >= p.tiles_m * p.tiles_n) return;  // uniform across the CTA
+    const uint32_t pm0 = (nb % p.tiles_m) * BM, pn0 = (nb / p.tiles_m) * BN;
+    for (int i = tid; i < BM + BN; i += CF::THREADS) {
+      int64_t dummy;
+      if (i < BM) decode(p.M, pm0 + i, p.Mflat, &dummy, &pf_m[i]);
+      else decode(p.N, pn0 + (i - BM), p.Nflat, &dummy, &pf_n[i - BM]);
+    }
+    __syncthreads();
+    prefetch_tile(pf_m, pf_n);
+  };
+  auto ld_c2 = [&](const double2* q) { return stream ? __ldcs(q) : *q; };
+  auto st_c2 = [&](double2* q, double2 v) { if (stream) __stcs(q, v); else *q = v; };
 
   if constexpr (CF::MATH == TC_MATH_DMMA) {
     // ---------------- fp64 on the tensor pipe ----------------
@@ -247,16 +290,65 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     // MMA row/column r of block b is mapped to tile element 16*(b/2) + 2r + (b&1):
     // one 16-byte shared load feeds two blocks, and the four D values a thread
     // holds for a block pair are four CONSECUTIVE m.
+    // Thread holds, per n row (nb = 2j+h -> n = wn0 + 16j + 2g + h) and block
+    // pair i, the four m = wm0 + 16i + 4t + {0,1,2,3}:
+    //   acc[nb][2i][0], acc[nb][2i+1][0], acc[nb][2i][1], acc[nb][2i+1][1].
     constexpr int WM = CF::WM, WN = CF::WN;
     constexpr int MB2 = WM / 16, NB2 = WN / 16;
     const int warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int wm0 = (warp % CF::WARPS_M) * WM, wn0 = (warp / CF::WARPS_M) * WN;
+    const double alpha = p.alpha;
     double acc[2 * NB2][2 * MB2][2];
 #pragma unroll
     for (int j = 0; j < 2 * NB2; ++j)
 #pragma unroll
       for (int i = 0; i < 2 * MB2; ++i) { acc[j][i][0] = 0.0; acc[j][i][1] = 0.0; }
+
+    if (init_from_c) {
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
+        if (cn < 0) continue;
+        if (p.vec_c == 4) {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            const int64_t co = offc_m[wm0 + 16 * i + 4 * t];
+            if (co < 0) continue;
+            const double2* src = reinterpret_cast<const double2*>(C + cn + co);
+            const double2 v0 = ld_c2(src), v1 = ld_c2(src + 1);
+            acc[nb][2 * i][0] = alpha * v0.x;
+            acc[nb][2 * i + 1][0] = alpha * v0.y;
+            acc[nb][2 * i][1] = alpha * v1.x;
+            acc[nb][2 * i + 1][1] = alpha * v1.y;
+          }
+        } else if (p.vec_c == 2) {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + 2 * e];
+              if (co < 0) continue;
+              const double2 v = ld_c2(reinterpret_cast<const double2*>(C + cn + co));
+              acc[nb][2 * i][e] = alpha * v.x;
+              acc[nb][2 * i + 1][e] = alpha * v.y;
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
+              if (co < 0) continue;
+              acc[nb][2 * i + (q & 1)][q >> 1] = alpha * C[cn + co];
+            }
+        }
+      }
+    }
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    prefetch_next();
 
     for (int it = 0; it < nk; ++it) {
       cp_async_wait<STAGES - 2>();
@@ -291,11 +383,7 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     }
     cp_async_wait<0>();
 
-    // ---------------- epilogue ----------------
-    // Thread holds, per n row (nb = 2j+h -> n = wn0 + 16j + 2g + h) and block
-    // pair i, the four m = wm0 + 16i + 4t + {0,1,2,3}:
-    //   acc[nb][2i][0], acc[nb][2i+1][0], acc[nb][2i][1], acc[nb][2i+1][1].
-    const double alpha = p.alpha;
+    // ---------------- epilogue: stores only ----------------
     if (p.ksplit > 1) {
       double* ws = reinterpret_cast<double*>(p.ws) +
                    ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
@@ -312,39 +400,49 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
       }
       return;
     }
-    int64_t cm[MB2];
+    if (p.vec_c == 4) {
+      // Two n rows (the pair fed by one Y fragment) per batch: all their loads are
+      // issued before the first store, so a batch pays one L2 round trip.
+      int64_t co[MB2];
 #pragma unroll
-    for (int i = 0; i < MB2; ++i) cm[i] = offc_m[wm0 + 16 * i + 4 * t];
+      for (int i = 0; i < MB2; ++i) co[i] = offc_m[wm0 + 16 * i + 4 * t];
 #pragma unroll
-    for (int nb = 0; nb < 2 * NB2; ++nb) {
-      const int nl = wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1);
-      const int64_t cn = offc_n[nl];
-      if (cn < 0) continue;
-      if (p.vec_c == 4) {
-        double2 c0[MB2], c1[MB2];
-        if (p.beta) {
+      for (int j = 0; j < NB2; ++j) {
+        int64_t cn[2];
+        double2 c0[2][MB2], c1[2][MB2];
 #pragma unroll
-          for (int i = 0; i < MB2; ++i)
-            if (cm[i] >= 0) {
-              const double2* src = reinterpret_cast<const double2*>(C + cn + cm[i]);
-              c0[i] = src[0];
-              c1[i] = src[1];
+        for (int h = 0; h < 2; ++h) {
+          cn[h] = offc_n[wn0 + 16 * j + 2 * g + h];
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            c0[h][i] = make_double2(0.0, 0.0);
+            c1[h][i] = make_double2(0.0, 0.0);
+            if (rmw && cn[h] >= 0 && co[i] >= 0) {
+              const double2* src = reinterpret_cast<const double2*>(C + cn[h] + co[i]);
+              c0[h][i] = ld_c2(src);
+              c1[h][i] = ld_c2(src + 1);
             }
+          }
         }
 #pragma unroll
-        for (int i = 0; i < MB2; ++i)
-          if (cm[i] >= 0) {
-            double2 r0, r1;
-            r0.x = alpha * acc[nb][2 * i][0];
-            r0.y = alpha * acc[nb][2 * i + 1][0];
-            r1.x = alpha * acc[nb][2 * i][1];
-            r1.y = alpha * acc[nb][2 * i + 1][1];
-            if (p.beta) { r0.x += c0[i].x; r0.y += c0[i].y; r1.x += c1[i].x; r1.y += c1[i].y; }
-            double2* dst = reinterpret_cast<double2*>(C + cn + cm[i]);
-            dst[0] = r0;
-            dst[1] = r1;
+        for (int h = 0; h < 2; ++h) {
+          const int nb = 2 * j + h;
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            if (cn[h] < 0 || co[i] < 0) continue;
+            double2* dst = reinterpret_cast<double2*>(C + cn[h] + co[i]);
+            st_c2(dst, make_double2(fma(alpha, acc[nb][2 * i][0], c0[h][i].x), fma(alpha, acc[nb][2 * i + 1][0], c0[h][i].y)));
+            st_c2(dst + 1, make_double2(fma(alpha, acc[nb][2 * i][1], c1[h][i].x), fma(alpha, acc[nb][2 * i + 1][1], c1[h][i].y)));
           }
-      } else if (p.vec_c == 2) {
+        }
+      }
+      return;
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2 * NB2; ++nb) {
+      const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
+      if (cn < 0) continue;
+      if (p.vec_c == 2) {
 #pragma unroll
         for (int i = 0; i < MB2; ++i)
 #pragma unroll
@@ -352,11 +450,9 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
             const int64_t co = offc_m[wm0 + 16 * i + 4 * t + 2 * e];
             if (co < 0) continue;
             double2* dst = reinterpret_cast<double2*>(C + cn + co);
-            double2 r;
-            r.x = alpha * acc[nb][2 * i][e];
-            r.y = alpha * acc[nb][2 * i + 1][e];
-            if (p.beta) { const double2 c = *dst; r.x += c.x; r.y += c.y; }
-            *dst = r;
+            double2 c = make_double2(0.0, 0.0);
+            if (rmw) c = ld_c2(dst);
+            st_c2(dst, make_double2(fma(alpha, acc[nb][2 * i][e], c.x), fma(alpha, acc[nb][2 * i + 1][e], c.y)));
           }
       } else {
 #pragma unroll
@@ -365,25 +461,55 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
           for (int q = 0; q < 4; ++q) {
             const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
             if (co < 0) continue;
-            double r = alpha * acc[nb][2 * i + (q & 1)][q >> 1];
-            if (p.beta) r += C[cn + co];
-            C[cn + co] = r;
+            const double c = rmw ? C[cn + co] : 0.0;
+            C[cn + co] = fma(alpha, acc[nb][2 * i + (q & 1)][q >> 1], c);
           }
       }
     }
   } else {
     // ---------------- vector pipe (FFMA / DFMA) ----------------
     // (BM/8) x (BN/8) threads, 8 x 8 outputs each, as groups of VW contiguous
-    // elements: m(gq,e) = gq*TX*VW + tx*VW + e, same along n.
+    // elements: m(q,e) = q*TX*VW + tx*VW + e, same along n.
     using V = typename Vec16<T>::type;
     constexpr int VW = CF::VW, GR = 8 / VW;
     constexpr int TX = BM / 8, TY = BN / 8;
     const int tx = tid % TX, ty = tid / TX;
+    const T alpha = (T)p.alpha;
+    const bool vec_c = p.vec_c >= VW;
     T acc[8][8];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[j][i] = T(0);
+
+    if (init_from_c) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int64_t cn = offc_n[(j / VW) * TY * VW + ty * VW + (j % VW)];
+        if (cn < 0) continue;
+#pragma unroll
+        for (int q = 0; q < GR; ++q) {
+          if (vec_c) {
+            const int64_t co = offc_m[q * TX * VW + tx * VW];
+            if (co < 0) continue;
+            const V v = stream ? __ldcs(reinterpret_cast<const V*>(C + cn + co)) : *reinterpret_cast<const V*>(C + cn + co);
+            const T* vp = reinterpret_cast<const T*>(&v);
+#pragma unroll
+            for (int e = 0; e < VW; ++e) acc[j][q * VW + e] = alpha * vp[e];
+          } else {
+#pragma unroll
+            for (int e = 0; e < VW; ++e) {
+              const int64_t co = offc_m[q * TX * VW + tx * VW + e];
+              if (co >= 0) acc[j][q * VW + e] = alpha * C[cn + co];
+            }
+          }
+        }
+      }
+    }
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    prefetch_next();
 
     for (int it = 0; it < nk; ++it) {
       cp_async_wait<STAGES - 2>();
@@ -413,7 +539,7 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
     }
     cp_async_wait<0>();
 
-    const T alpha = (T)p.alpha;
+    // ---------------- epilogue: stores only ----------------
     if (p.ksplit > 1) {
       T* ws = reinterpret_cast<T*>(p.ws) +
               ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
@@ -428,34 +554,31 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
       }
       return;
     }
-    int64_t cm[GR];
-#pragma unroll
-    for (int q = 0; q < GR; ++q) cm[q] = offc_m[q * TX * VW + tx * VW];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int nl = (j / VW) * TY * VW + ty * VW + (j % VW);
-      const int64_t cn = offc_n[nl];
+      const int64_t cn = offc_n[(j / VW) * TY * VW + ty * VW + (j % VW)];
       if (cn < 0) continue;
-      if (p.vec_c >= VW) {
+      if (vec_c) {
+        int64_t co[GR];
         V cv[GR];
-        if (p.beta) {
 #pragma unroll
-          for (int q = 0; q < GR; ++q)
-            if (cm[q] >= 0) cv[q] = *reinterpret_cast<const V*>(C + cn + cm[q]);
+        for (int q = 0; q < GR; ++q) {
+          co[q] = offc_m[q * TX * VW + tx * VW];
+          if (rmw && co[q] >= 0) {
+            const V* src = reinterpret_cast<const V*>(C + cn + co[q]);
+            cv[q] = stream ? __ldcs(src) : *src;
+          }
         }
 #pragma unroll
-        for (int q = 0; q < GR; ++q)
-          if (cm[q] >= 0) {
-            T r[VW];
+        for (int q = 0; q < GR; ++q) {
+          if (co[q] < 0) continue;
+          T r[VW];
+          const T* cp = reinterpret_cast<const T*>(&cv[q]);
 #pragma unroll
-            for (int e = 0; e < VW; ++e) r[e] = alpha * acc[j][q * VW + e];
-            if (p.beta) {
-              const T* cp = reinterpret_cast<const T*>(&cv[q]);
-#pragma unroll
-              for (int e = 0; e < VW; ++e) r[e] += cp[e];
-            }
-            *reinterpret_cast<V*>(C + cn + cm[q]) = *reinterpret_cast<const V*>(r);
-          }
+          for (int e = 0; e < VW; ++e) r[e] = rmw ? fma(alpha, acc[j][q * VW + e], cp[e]) : alpha * acc[j][q * VW + e];
+          V* dst = reinterpret_cast<V*>(C + cn + co[q]);
+          if (stream) __stcs(dst, *reinterpret_cast<const V*>(r)); else *dst = *reinterpret_cast<const V*>(r);
+        }
       } else {
 #pragma unroll
         for (int q = 0; q < GR; ++q)
@@ -463,9 +586,8 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
           for (int e = 0; e < VW; ++e) {
             const int64_t co = offc_m[q * TX * VW + tx * VW + e];
             if (co < 0) continue;
-            T r = alpha * acc[j][q * VW + e];
-            if (p.beta) r += C[cn + co];
-            C[cn + co] = r;
+            const T c = rmw ? C[cn + co] : T(0);
+            C[cn + co] = fma(alpha, acc[j][q * VW + e], c);
           }
       }
     }
@@ -473,11 +595,14 @@ __global__ void __launch_bounds__(CF::THREADS) tc_contract_kernel(const __grid_c
 }
 
 // K-slice combine: C (op)= sum over slices of the partial tiles, slices in
-// ascending order (deterministic).
-template <typename T, int BM, int BN>
+// ascending order (deterministic).  One CTA per output tile; the tile shape is
+// the producing kernel's (args.bm x args.bn).
+template <typename T>
 __global__ void __launch_bounds__(256) tc_combine_kernel(const __grid_constant__ TcKernelArgs p, T* __restrict__ C) {
-  __shared__ int64_t offc_m[BM];
-  __shared__ int64_t offc_n[BN];
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int BM = p.bm, BN = p.bn;
+  int64_t* offc_m = reinterpret_cast<int64_t*>(smem_raw);
+  int64_t* offc_n = offc_m + BM;
   const uint32_t bid = blockIdx.x;
   const uint32_t tile_m = bid % p.tiles_m, tile_n = bid / p.tiles_m;
   const size_t tiles = (size_t)p.tiles_m * p.tiles_n;
@@ -487,14 +612,15 @@ __global__ void __launch_bounds__(256) tc_combine_kernel(const __grid_constant__
     else decode(p.N, tile_n * BN + (i - BM), p.Nflat, &dummy, &offc_n[i - BM]);
   }
   __syncthreads();
-  const T* ws = reinterpret_cast<const T*>(p.ws) + (size_t)bid * (BM * BN);
+  const size_t tile_elems = (size_t)BM * BN;
+  const T* ws = reinterpret_cast<const T*>(p.ws) + (size_t)bid * tile_elems;
   const T alpha = (T)p.alpha;
   for (int e = threadIdx.x; e < BM * BN; e += 256) {
     const int ml = e % BM, nl = e / BM;
     const int64_t cm = offc_m[ml], cn = offc_n[nl];
     if (cm < 0 || cn < 0) continue;
     T s = T(0);
-    for (uint32_t sl = 0; sl < p.ksplit; ++sl) s += ws[sl * tiles * (size_t)(BM * BN) + e];
+    for (uint32_t sl = 0; sl < p.ksplit; ++sl) s += ws[sl * tiles * tile_elems + e];
     T r = alpha * s;
     if (p.beta) r += C[cn + cm];
     C[cn + cm] = r;

@@ -86,14 +86,6 @@ int64_t span(const std::vector<int64_t>& ext, const std::vector<int64_t>& str) {
 
 }  // namespace
 
-bool tc_tile_supported(int dtype, int math, int bm, int bn) {
-  if (dtype == TC_F64 && math == TC_MATH_DMMA) return (bm == 128 && bn == 128) || (bm == 64 && bn == 64);
-  if (math == TC_MATH_SIMT) return (bm == 128 && bn == 128) || (bm == 64 && bn == 64);
-  return false;
-}
-
-int tc_tile_bk(int, int) { return 16; }
-
 int tc_plan_build(tc_plan* p, std::string* why) {
   std::string dummy;
   if (!why) why = &dummy;
@@ -238,24 +230,39 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   a.alpha = e.op < 0 ? -1.0 : 1.0;
   a.beta = e.op == 0 ? 0 : 1;
 
-  // CTA tile: the large tile unless it leaves most SMs idle.
-  int bm = 128, bn = 128;
+  // CTA tile and warp layout.  Rules distilled from tile sweeps on B200 over the
+  // benchmark configurations (they replace the reference's transaction-count
+  // cost model, cogent/src/algs/bases/cost_models.py:191-574):
+  //   * fp64 tensor pipe: the N tile that wastes least of Nflat among 64 / 96;
+  //     long contractions (compute bound) want the 64x32 warp tile of 128x64/4 warps,
+  //     short ones (output bound) more warps in flight: 128x64/8 warps;
+  //   * vector pipe: 128x128;
+  //   * anything that would leave most SMs without a tile: 64x64.
+  int bm = 128, bn = 128, variant = 0;
   if (p->opt.tile_m > 0 || p->opt.tile_n > 0) {
     bm = p->opt.tile_m;
     bn = p->opt.tile_n;
-    if (!tc_tile_supported(c.dtype, c.math, bm, bn)) { *why = "requested CTA tile is not compiled in"; return TC_ERR_UNSUPPORTED; }
+    variant = p->opt.variant > 0 ? p->opt.variant - 1 : 0;
   } else {
-    const int64_t big = ((mf + 127) / 128) * ((nf + 127) / 128);
-    if (big < 2 * 148) { bm = 64; bn = 64; }
+    auto waste = [&](int64_t n, int64_t b) { return (double)(((n + b - 1) / b) * b) / (double)n; };
+    if (c.math == TC_MATH_DMMA) {
+      if (waste(nf, 96) + 0.02 < waste(nf, 64)) { bm = 64; bn = 96; }
+      else { bm = 128; bn = 64; variant = kf >= 256 ? 0 : 1; }
+    }
+    const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
+    if (ctas < 2 * 148 && (bm > 64 || c.math == TC_MATH_SIMT)) { bm = 64; bn = 64; variant = 0; }
+    if (p->opt.variant > 0) variant = p->opt.variant - 1;
   }
   c.bm = bm;
   c.bn = bn;
-  c.variant = p->opt.variant > 0 ? p->opt.variant - 1 : 0;
-  if (c.variant > 1 || (c.variant == 1 && !(c.math == TC_MATH_DMMA && bm == 128))) { *why = "requested kernel variant is not compiled in"; return TC_ERR_UNSUPPORTED; }
+  c.variant = variant;
+  if (!tc_kernel_exists(c.dtype, c.math, bm, bn, c.variant)) { *why = "requested CTA tile / variant is not compiled in"; return TC_ERR_UNSUPPORTED; }
+  a.bm = bm;
+  a.bn = bn;
   a.tiles_m = (uint32_t)((mf + bm - 1) / bm);
   a.tiles_n = (uint32_t)((nf + bn - 1) / bn);
   const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
-  const int bk = tc_tile_bk(c.dtype, c.math);
+  const int bk = TC_BK;
 
   // K split: only when the tile count cannot fill the GPU and K is long.
   int64_t ksplit = 1;
@@ -280,6 +287,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
 
 std::string tc_plan_to_json(const tc_plan& p) {
   std::ostringstream o;
+  o.precision(17);
   const TcKernelArgs& a = p.args;
   auto dims = [&](const TcDims& d) {
     o << "[";
@@ -296,7 +304,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     dims(a.N);
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
-      << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << tc_tile_bk(p.choice.dtype, p.choice.math)
+      << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x

@@ -53,7 +53,8 @@ typedef struct tc_options {
   int tile_n;     /*     of the compiled shapes, see tc_plan_describe)                */
   int split_k;    /* 0 = planner's choice, 1 = never split, >1 = that many K slices   */
   int variant;    /* 0 = planner's choice; otherwise 1-based warp layout of the tile  */
-  int reserved[3];
+  int l2_prefetch; /* 0 = on (output tiles are prefetched into L2 one wave ahead), 1 = off */
+  int reserved[2];
 } tc_options;
 
 typedef struct tc_plan tc_plan;

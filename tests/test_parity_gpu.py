@@ -1,0 +1,352 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker.
+
+Gate everywhere: max|got - ref| / max|ref| <= 1e-12 (fp64) or 1e-5 (fp32),
+inputs uniform[-1,1) from the seeded generator.
+"""
+import random
+
+import numpy as np
+import pytest
+
+from conftest import CONFIGS, TOL
+from test_parser import _random_expr
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch_cuda():
+    import torch
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    torch.cuda.set_device(0)
+    return torch
+
+
+def _dt(pkg, dtype):
+    return pkg.F64 if np.dtype(dtype) == np.float64 else pkg.F32
+
+
+def _run(pkg, orc, torch, expr, dtype, seed, **kw):
+    """Executes on the GPU and returns (rel_err, plan description)."""
+    c0, a, b = orc.make_inputs(expr, seed, dtype)
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    plan = pkg.Plan(expr, _dt(pkg, dtype), **kw)
+    dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+    plan.execute(dc, da, db)
+    torch.cuda.synchronize()
+    desc = plan.describe()
+    plan.close()
+    return orc.rel_error(dc.cpu().numpy(), ref), desc
+
+
+def _scaled(expr, extent):
+    """Same expression with every extent replaced (a reduced copy of a benchmark configuration)."""
+    import re
+    return re.sub(r",(\d+)", lambda m: ",%d" % extent, expr)
+
+
+# ------------------------------------------------------------ generator ----
+def test_device_generator_matches_checker(pkg, orc, torch_cuda):
+    torch = torch_cuda
+    for tdt, ndt in ((torch.float64, np.float64), (torch.float32, np.float32)):
+        for seed, tid, first in ((0, 0, 0), (3, 1, 12345), (4, 2, (1 << 33) + 5)):
+            t = torch.empty(4099, dtype=tdt, device="cuda")
+            pkg.fill_uniform(t, seed, tid, first)
+            assert np.array_equal(t.cpu().numpy(), orc.uniform(seed, tid, 4099, ndt, first))
+
+
+# ------------------------------------------------- benchmark configurations ----
+def test_config1_full_size_all_paths(pkg, orc, torch_cuda):
+    expr, dt, seed = CONFIGS[0]
+    for kw in ({}, {"path": pkg.PATH_DFMA}, {"tile": (128, 128)}, {"tile": (128, 64), "variant": 2},
+               {"tile": (64, 96)}, {"tile": (64, 64), "split_k": 2}):
+        err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
+        assert err <= TOL[dt], (kw, err)
+
+
+@pytest.mark.parametrize("idx,extent", [(1, 24), (2, 16), (3, 8), (4, 10)])
+def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
+    expr, dt, seed = CONFIGS[idx]
+    expr = _scaled(expr, extent)
+    if idx == 3:
+        expr = expr.replace("sum(l,8)", "sum(l,24)")
+    if idx == 4:
+        expr = expr.replace("sum(g,10)", "sum(g,40)")
+    tiles = [None, (128, 128), (64, 64)] + ([(128, 64), (128, 96), (64, 96)] if dt == "float64" else [(128, 64)])
+    for tile in tiles:
+        err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, **({"tile": tile} if tile else {}))
+        assert err <= TOL[dt], (expr, tile, err)
+    if dt == "float64":
+        for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 128), "variant": 2}, {"tile": (128, 64), "variant": 2},
+                   {"l2_prefetch": 1}, {"tuning": 1}, {"tuning": 3}):
+            err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
+            assert err <= TOL[dt], (expr, kw, err)
+
+
+def _slab_check(pkg, orc, torch, expr, dtype, seed, fixes, device_inputs=False):
+    """Full-size run; the checker recomputes only slabs (some output indices fixed)."""
+    p = orc.parse(expr)
+    ext = dict(zip(p["out_idx"] + p["sum_idx"], p["out_ext"] + p["sum_ext"]))
+    nc, na, nb = orc.sizes(expr)
+    tdt = torch.float64 if np.dtype(dtype) == np.float64 else torch.float32
+    dc = torch.empty(nc, dtype=tdt, device="cuda")
+    da = torch.empty(na, dtype=tdt, device="cuda")
+    db = torch.empty(nb, dtype=tdt, device="cuda")
+    pkg.fill_uniform(dc, seed, 0)
+    pkg.fill_uniform(da, seed, 1)
+    pkg.fill_uniform(db, seed, 2)
+    plan = pkg.Plan(expr, _dt(pkg, dtype))
+    plan.execute(dc, da, db)
+    torch.cuda.synchronize()
+    a, b = orc.uniform(seed, 1, na, dtype), orc.uniform(seed, 2, nb, dtype)
+
+    def strides(idx):
+        s, acc = [], 1
+        for i in idx:
+            s.append(acc)
+            acc *= ext[i]
+        return s
+
+    sc, sa, sb = strides(p["out_idx"]), strides(p["left_idx"]), strides(p["right_idx"])
+    worst = 0.0
+    for fix in fixes:
+        sub = orc.with_extents(expr, {i: 1 for i in fix})
+        off = lambda idx, st: sum(fix.get(i, 0) * s for i, s in zip(idx, st))
+        oc = off(p["out_idx"], sc)
+        # the slab of C spans [oc, oc + span); regenerate just that range of the initial output
+        span = 1 + sum((1 if i in fix else ext[i]) * s - s for i, s in zip(p["out_idx"], sc))
+        c_ref = orc.uniform(seed, 0, span, dtype, first=oc)
+        c_init = c_ref.copy()
+        orc.contract(sub, c_ref, a[off(p["left_idx"], sa):], b[off(p["right_idx"], sb):],
+                     threads=orc.max_threads(), strides={0: sc, 1: sa, 2: sb})
+        got = dc[oc:oc + span].cpu().numpy()
+        touched = c_ref != c_init
+        assert touched.any()
+        # elements outside the slab inside the span must not be compared against the slab's reference
+        worst = max(worst, orc.rel_error(got[touched], c_ref[touched]))
+    plan.close()
+    del dc, da, db
+    torch.cuda.empty_cache()
+    return worst
+
+
+def test_config2_full_size_slabs(pkg, orc, torch_cuda):
+    expr, dt, seed = CONFIGS[1]
+    err = _slab_check(pkg, orc, torch_cuda, expr, dt, seed, [{"d": 0, "c": 0}, {"d": 95, "c": 95}, {"d": 41, "b": 7}])
+    assert err <= TOL[dt]
+
+
+def test_config3_full_size_slabs(pkg, orc, torch_cuda):
+    expr, dt, seed = CONFIGS[2]
+    err = _slab_check(pkg, orc, torch_cuda, expr, dt, seed, [{"c": 0, "d": 0}, {"c": 63, "d": 63}, {"a": 17, "b": 33}])
+    assert err <= TOL[dt]
+
+
+def test_config4_full_size_slabs(pkg, orc, torch_cuda):
+    expr, dt, seed = CONFIGS[3]
+    err = _slab_check(pkg, orc, torch_cuda, expr, dt, seed,
+                      [{"i": 0, "j": 0, "k": 0}, {"i": 23, "j": 23, "k": 23}, {"b": 5, "c": 11, "k": 2}])
+    assert err <= TOL[dt]
+
+
+def test_config5_one_eighth_slabs(pkg, orc, torch_cuda):
+    # the shard one GPU owns when the large configuration is split 8 ways along f (4.1 GB of output)
+    expr, dt, seed = CONFIGS[4]
+    expr = expr.replace("f,40", "f,5")
+    err = _slab_check(pkg, orc, torch_cuda, expr, dt, seed,
+                      [{"d": 0, "e": 0, "f": 0}, {"d": 39, "e": 39, "f": 4}, {"a": 3, "b": 1, "f": 2, "e": 7}])
+    assert err <= TOL[dt]
+
+
+# ------------------------------------------------------- random expressions ----
+@pytest.mark.parametrize("path", ["dmma", "dfma", "ffma"])
+def test_random_contractions(pkg, orc, torch_cuda, path):
+    rng = random.Random({"dmma": 11, "dfma": 12, "ffma": 13}[path])
+    dt = "float32" if path == "ffma" else "float64"
+    kw = {"path": pkg.PATH_DFMA} if path == "dfma" else {}
+    for n in range(40):
+        expr = _random_expr(rng, max_out=5, max_sum=3, multi_char=(n % 4 == 0))
+        err, d = _run(pkg, orc, torch_cuda, expr, dt, 100 + n, **kw)
+        assert err <= TOL[dt], (expr, err, d)
+
+
+EDGE = [
+    "C [a,1,b,1] += sum(c,1) * A [c,a] * B [b,c];",                         # everything is a scalar
+    "C [a,5] += sum(b,7) * A [b,a] * B [b];",                               # right operand has no external index
+    "C [a,5] -= sum(b,7) * A [b] * B [a,b];",                               # left operand has no external index
+    "C [a,13,b,11] += sum(c,1) * A [a,c] * B [c,b];",                       # outer product
+    "C [a,127,b,129] += sum(c,17) * A [c,a] * B [c,b];",                    # one off the tile sizes, K just over a step
+    "C [a,2,b,3,c,5,d,7,e,2,f,3] += sum(g,11,h,2) * A [h,f,d,b,g] * B [g,a,c,h,e];",  # 6-D output, prime extents
+    "C [a,31,b,37] = sum(c,4099) * A [c,a] * B [b,c];",                     # long prime contraction, overwrite
+    "C [a,64,b,64] -= sum(c,64) * A [a,c] * B [b,c];",                      # both operands external-contiguous
+    "C [a,64,b,64] += sum(c,64) * A [c,a] * B [c,b];",                      # both operands contraction-contiguous
+]
+
+
+@pytest.mark.parametrize("expr", EDGE)
+def test_edge_shapes(pkg, orc, torch_cuda, expr):
+    for dt in ("float64", "float32"):
+        err, d = _run(pkg, orc, torch_cuda, expr, dt, 42)
+        assert err <= TOL[dt], (expr, dt, err, d)
+    err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, path=pkg.PATH_DFMA)
+    assert err <= TOL["float64"]
+
+
+def test_overwrite_ignores_initial_output_even_nan(pkg, orc, torch_cuda):
+    torch = torch_cuda
+    expr = "C [a,40,b,24] = sum(c,33) * A [c,a] * B [b,c];"
+    c0, a, b = orc.make_inputs(expr, 9)
+    ref = orc.contract(expr, c0.copy(), a, b)
+    for kw in ({}, {"split_k": 2}):
+        dc = torch.full((c0.size,), float("nan"), dtype=torch.float64, device="cuda")
+        plan = pkg.Plan(expr, **kw)
+        plan.execute(dc, torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda())
+        torch.cuda.synchronize()
+        got = dc.cpu().numpy()
+        assert np.isfinite(got).all() and orc.rel_error(got, ref) <= 1e-12
+
+
+# ------------------------------------------------------- views / alignment ----
+def test_strided_slab_of_a_larger_problem(pkg, orc, torch_cuda):
+    """One rank's share when an external index is split: strides of the full tensors, shifted bases."""
+    torch = torch_cuda
+    full = "C [a,24,b,10,c,12] += sum(d,20) * A [d,c,a] * B [b,d];"
+    c0, a, b = orc.make_inputs(full, 21)
+    ref = orc.contract(full, c0.copy(), a, b)
+    dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+    # split b (middle index of C, fastest of B) into [0,4) and [4,10); run both slabs
+    for start, count in ((0, 4), (4, 6)):
+        plan = pkg.Plan(orc.with_extents(full, {"b": count}))
+        plan.set_strides(pkg.TENSOR_OUT, [1, 24, 240]).set_strides(pkg.TENSOR_RIGHT, [1, 10])
+        plan.execute(dc[24 * start:], da, db[start:])
+        plan.close()
+    torch.cuda.synchronize()
+    assert orc.rel_error(dc.cpu().numpy(), ref) <= 1e-12
+
+
+def test_contraction_slab_accumulates(pkg, orc, torch_cuda):
+    """Splitting the contraction index: two executes over halves of d accumulate to the full sum."""
+    torch = torch_cuda
+    full = "C [a,24,b,10,c,12] += sum(d,20) * A [d,c,a] * B [b,d];"
+    c0, a, b = orc.make_inputs(full, 22)
+    ref = orc.contract(full, c0.copy(), a, b)
+    dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+    for start, count in ((0, 12), (12, 8)):
+        plan = pkg.Plan(orc.with_extents(full, {"d": count}))
+        plan.set_strides(pkg.TENSOR_LEFT, [1, 20, 240]).set_strides(pkg.TENSOR_RIGHT, [1, 10])
+        plan.execute(dc, da[start:], db[10 * start:])
+        plan.close()
+    torch.cuda.synchronize()
+    assert orc.rel_error(dc.cpu().numpy(), ref) <= 1e-12
+
+
+def test_pointers_off_16_byte_alignment(pkg, orc, torch_cuda):
+    torch = torch_cuda
+    for dt, tdt in (("float64", torch.float64), ("float32", torch.float32)):
+        expr = "C [a,32,b,20] += sum(c,24) * A [a,c] * B [c,b];"
+        c0, a, b = orc.make_inputs(expr, 5, dt)
+        ref = orc.contract(expr, c0.copy(), a, b)
+        pad = lambda x: torch.cat([torch.zeros(1, dtype=tdt), torch.from_numpy(x)]).cuda()
+        dc, da, db = pad(c0), pad(a), pad(b)
+        plan = pkg.Plan(expr, _dt(pkg, dt))
+        assert plan.describe()["vec_x"] and plan.describe()["vec_c"] == 4
+        plan.execute(dc[1:], da[1:], db[1:])  # every base is one element off a 16-byte boundary
+        torch.cuda.synchronize()
+        assert orc.rel_error(dc[1:].cpu().numpy(), ref) <= TOL[dt]
+        assert dc[0].item() == 0.0
+        plan.close()
+    # a pointer off the element size is an error, not a fault
+    plan = pkg.Plan("C [a,4,b,4] += sum(c,4) * A [a,c] * B [c,b];")
+    buf = torch.zeros(64, dtype=torch.float64, device="cuda")
+    with pytest.raises(pkg.TcError) as e:
+        plan.execute(buf.data_ptr() + 4, buf.data_ptr() + 128, buf.data_ptr() + 256)
+    assert e.value.status == 6
+
+
+# ------------------------------------------------------ K split / workspace ----
+def test_k_split_and_caller_workspace(pkg, orc, torch_cuda):
+    torch = torch_cuda
+    expr = "C [a,33,b,17] += sum(c,1000,d,9) * A [a,c,d] * B [d,b,c];"
+    c0, a, b = orc.make_inputs(expr, 7)
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    for dt in ("float64",):
+        plan = pkg.Plan(expr)
+        plan.commit()
+        assert plan.describe()["ksplit"] > 1 and plan.launches == 2
+        need = plan.workspace_bytes()
+        assert need > 0
+        da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        dc = torch.from_numpy(c0).cuda()
+        plan.execute(dc, da, db)  # plan-owned workspace
+        dc2 = torch.from_numpy(c0).cuda()
+        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        plan.execute(dc2, da, db, workspace=ws)  # caller's workspace
+        torch.cuda.synchronize()
+        assert orc.rel_error(dc.cpu().numpy(), ref) <= 1e-12
+        assert np.array_equal(dc.cpu().numpy(), dc2.cpu().numpy())  # slices are combined in a fixed order
+        small = torch.empty(need - 16, dtype=torch.uint8, device="cuda")
+        with pytest.raises(pkg.TcError) as e:
+            plan.execute(dc2, da, db, workspace=small)
+        assert e.value.status == 8
+        plan.close()
+
+
+# ----------------------------------------------------------- host pointers ----
+def test_host_pointer_execute(pkg, orc, torch_cuda):
+    for dt in ("float64", "float32"):
+        expr = "t3 [a,20,b,6,c,14] += sum(d,18) * t2 [d,c,a] * v2 [b,d];"
+        c0, a, b = orc.make_inputs(expr, 31, dt)
+        ref = orc.contract(expr, c0.copy(), a, b)
+        c = c0.copy()
+        plan = pkg.Plan(expr, _dt(pkg, dt))
+        plan.execute_host(c, a, b)
+        assert orc.rel_error(c, ref) <= TOL[dt]
+        plan.close()
+
+
+def test_extents_overridden_at_run_time(pkg, orc, torch_cuda):
+    """The sizes written in the expression are only representative, as in the reference drivers."""
+    torch = torch_cuda
+    written = "t3 [a,16,b,16,c,16] += sum(d,16) * t2 [d,c,a] * v2 [b,d];"
+    ext = {"a": 40, "b": 9, "c": 21, "d": 33}
+    actual = orc.with_extents(written, ext)
+    c0, a, b = orc.make_inputs(actual, 3)
+    ref = orc.contract(actual, c0.copy(), a, b)
+    plan = pkg.Plan(written, extents=ext)
+    dc = torch.from_numpy(c0).cuda()
+    plan.execute(dc, torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda())
+    torch.cuda.synchronize()
+    assert orc.rel_error(dc.cpu().numpy(), ref) <= 1e-12
+    with pytest.raises(pkg.TcError) as e:
+        plan.set_extents({"a": 2})  # committed plans are immutable
+    assert e.value.status == 7
+
+
+# ------------------------------------------------------------- properties ----
+def test_two_streams_and_repeated_accumulation(pkg, orc, torch_cuda):
+    """Linearity at a size the checker would not finish: C2 - C1 == C1 - C0, on two streams at once."""
+    torch = torch_cuda
+    expr = CONFIGS[1][0].replace("96", "48")
+    nc, na, nb = orc.sizes(expr)
+    outs = []
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    plan = pkg.Plan(expr).commit()
+    bufs = []
+    for s, seed in zip(streams, (1, 2)):
+        with torch.cuda.stream(s):
+            dc = torch.empty(nc, dtype=torch.float64, device="cuda")
+            da = torch.empty(na, dtype=torch.float64, device="cuda")
+            db = torch.empty(nb, dtype=torch.float64, device="cuda")
+            for t, tid in ((dc, 0), (da, 1), (db, 2)):
+                pkg.fill_uniform(t, seed, tid, stream=s.cuda_stream)
+            c0 = dc.clone()
+            plan.execute(dc, da, db, stream=s.cuda_stream)
+            c1 = dc.clone()
+            plan.execute(dc, da, db, stream=s.cuda_stream)
+            bufs.append((c0, c1, dc, da, db))
+    torch.cuda.synchronize()
+    for c0, c1, c2, da, db in bufs:
+        d1, d2 = (c1 - c0), (c2 - c1)
+        scale = d1.abs().max().item()
+        assert scale > 1.0 and (d1 - d2).abs().max().item() <= 1e-12 * scale
+    plan.close()

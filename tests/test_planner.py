@@ -1,0 +1,108 @@
+"""Host-side planner (no GPU): index classes, fusion, loaders, tiles, costs, errors."""
+import pytest
+
+from conftest import CONFIGS
+
+
+def _plan(pkg, expr, dtype="float64", **kw):
+    return pkg.Plan(expr, pkg.F64 if dtype == "float64" else pkg.F32, **kw)
+
+
+def test_algorithmic_costs_of_the_benchmark_configurations(pkg):
+    # flops = 2 * prod(extents); bytes = elemsize * (2|C| + |A| + |B|)
+    want = [(7864320, 2243584), (16307453952, 2038505472), (137438953472, 536870912),
+            (9172942848, 1531478016), (327680000000, 65576960000)]
+    for (expr, dt, _), (fl, by) in zip(CONFIGS, want):
+        f, b = _plan(pkg, expr, dt).cost()
+        assert (f, b) == (fl, by)
+
+
+def test_index_classes_and_fusion(pkg):
+    d = [_plan(pkg, e, dt).describe() for e, dt, _ in CONFIGS]
+    # cfg1: M = {i,k} (left operand), N = {j}, K = {l}
+    assert [x["extent"] for x in d[0]["M"]] == [64, 32] and [x["extent"] for x in d[0]["N"]] == [48]
+    assert d[0]["Kflat"] == 40 and not d[0]["swapped"]
+    # cfg2: nothing fuses (b,d adjacent in A but not in C)
+    assert [x["extent"] for x in d[1]["M"]] == [96, 96, 96] and d[1]["Nflat"] == 96
+    # cfg3: two contraction indices flatten to 4096
+    assert d[2]["Mflat"] == d[2]["Nflat"] == d[2]["Kflat"] == 4096
+    # cfg4: (i,j) and (b,c) fuse: adjacent in the output and in their operand
+    assert [x["extent"] for x in d[3]["M"]] == [24, 576] and [x["extent"] for x in d[3]["N"]] == [576, 24]
+    # cfg5: becomes a plain 64000 x 64000 x 40 product
+    assert [x["extent"] for x in d[4]["M"]] == [64000] and [x["extent"] for x in d[4]["N"]] == [64000]
+    assert d[4]["M"][0]["s_in"] == 40 and d[4]["M"][0]["s_out"] == 1
+
+
+def test_operands_swap_when_output_fastest_index_is_in_the_right_operand(pkg):
+    d = _plan(pkg, "C [a,8,b,8] += sum(c,8) * A [c,b] * B [a,c];").describe()
+    assert d["swapped"] and d["M"][0]["s_out"] == 1 and d["vec_c"] == 4
+
+
+def test_loader_and_vector_choices(pkg):
+    d2 = _plan(pkg, CONFIGS[1][0]).describe()
+    assert d2["vec_x"] and not d2["vec_y"] and d2["lanes_k_y"] == 4 and d2["vec_c"] == 4
+    d4 = _plan(pkg, CONFIGS[3][0], "float32").describe()
+    assert not d4["vec_x"] and d4["lanes_k_x"] == 8 and d4["vec_y"] and d4["vec_c"] == 4
+    odd = _plan(pkg, "C [a,7,b,5] += sum(c,3) * A [a,c] * B [c,b];").describe()
+    assert not odd["vec_x"] and odd["vec_c"] == 1
+    even = _plan(pkg, "C [a,6,b,5] += sum(c,3) * A [a,c] * B [c,b];").describe()
+    assert even["vec_x"] and even["vec_c"] == 2
+
+
+def test_tile_choices(pkg):
+    d = [_plan(pkg, e, dt).describe() for e, dt, _ in CONFIGS]
+    assert d[1]["tile"][:2] == [64, 96] and d[1]["tiles"] == [13824, 1]      # N = 96 exactly one tile wide
+    assert d[2]["tile"][:2] == [128, 64] and d[2]["variant"] == 0          # long contraction
+    assert d[4]["tile"][:2] == [128, 64] and d[4]["variant"] == 1          # short contraction, output bound
+    assert d[3]["math"] == "ffma" and d[3]["tile"][:2] == [128, 128]
+    assert d[0]["tile"][:2] == [64, 64]                                     # tiny problem
+
+
+def test_k_split_plans(pkg):
+    p = _plan(pkg, "C [a,33,b,17] += sum(c,1000,d,9) * A [a,c,d] * B [d,b,c];")
+    d = p.describe()
+    assert d["ksplit"] > 1 and d["launches"] == 2 and d["workspace_bytes"] == d["ksplit"] * 64 * 64 * 8
+    assert d["k_chunk"] % 16 == 0 and d["k_chunk"] * d["ksplit"] >= 9000
+    assert _plan(pkg, "C [a,33,b,17] += sum(c,1000,d,9) * A [a,c,d] * B [d,b,c];", split_k=1).describe()["ksplit"] == 1
+    assert _plan(pkg, CONFIGS[1][0]).describe()["ksplit"] == 1
+
+
+def test_extent_override_and_errors(pkg):
+    p = _plan(pkg, "t3 [a,16,b,16,c,16] += sum(d,16) * t2 [d,c,a] * v2 [b,d];")
+    p.set_extents({"a": 312, "b": 24, "c": 296, "d": 312})
+    assert p.cost()[0] == 2.0 * 312 * 24 * 296 * 312
+    with pytest.raises(pkg.TcError) as e:
+        p.set_extents({"z": 3})
+    assert e.value.status == 2
+    with pytest.raises(pkg.TcError) as e:
+        p.set_extents({"a": 0})
+    assert e.value.status == 4
+    with pytest.raises(pkg.TcError) as e:
+        _plan(pkg, CONFIGS[0][0], tile=(48, 48)).describe()
+    assert e.value.status == 3
+    with pytest.raises(pkg.TcError) as e:
+        _plan(pkg, CONFIGS[0][0], path=pkg.PATH_FFMA).describe()
+    assert e.value.status == 2
+    with pytest.raises(pkg.TcError) as e:
+        _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_3XTF32).describe()
+    assert e.value.status == 3
+
+
+def test_strided_views(pkg):
+    p = _plan(pkg, "C [a,4,b,3] += sum(c,5) * A [c,a] * B [b,c];")
+    p.set_strides(pkg.TENSOR_OUT, [1, 4]).set_strides(pkg.TENSOR_RIGHT, [1, 7])
+    d = p.describe()
+    assert d["N"][0]["s_in"] == 1 and d["N"][0]["s_out"] == 4
+    with pytest.raises(pkg.TcError) as e:
+        _plan(pkg, "C [a,4,b,3] += sum(c,5) * A [c,a] * B [b,c];").set_strides(pkg.TENSOR_OUT, [1, 2]).describe()
+    assert e.value.status == 4  # output elements would alias
+    with pytest.raises(pkg.TcError) as e:
+        p.set_strides(pkg.TENSOR_OUT, [1])
+    assert e.value.status == 2
+
+
+def test_sizes_beyond_32_bit(pkg):
+    # 4.096e9 output elements: offsets are 64-bit (the reference's int arithmetic cannot address this)
+    d = _plan(pkg, CONFIGS[4][0]).describe()
+    assert d["tiles"][0] * d["tiles"][1] == 500 * 1000
+    assert d["N"][0]["s_out"] == 64000
