@@ -56,6 +56,7 @@ _SIGNATURES = {
     "tc_plan_cost": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_double),
                                     ctypes.POINTER(ctypes.c_double)]),
     "tc_plan_launches": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_plan_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
     "tc_plan_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "tc_execute": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                   ctypes.c_void_p]),
@@ -179,6 +180,12 @@ class Plan:
     @property
     def launches(self):
         return lib().tc_plan_launches(self._h)
+
+    def status(self):
+        """Device status word (synchronises): 0 unless a bounded wait in a persistent kernel gave up."""
+        v = ctypes.c_int()
+        _check(lib().tc_plan_status(self._h, ctypes.byref(v)), "tc_plan_status")
+        return v.value
 
     def workspace_bytes(self):
         n = ctypes.c_size_t()

@@ -60,6 +60,10 @@ extern "C" int tc_expr_describe(const char* expr, char* buf, size_t cap) {
   extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 TC_KERNEL_LIST(TC_DECLARE)
 #undef TC_DECLARE
+#define TC_DECLARE_WS(NAME, BM, BN, STAGES, VARIANT) \
+  extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+TC_WS_KERNEL_LIST(TC_DECLARE_WS)
+#undef TC_DECLARE_WS
 
 namespace {
 struct KernelEntry {
@@ -69,8 +73,10 @@ struct KernelEntry {
 };
 template <typename T> constexpr int dtype_of() { return sizeof(T) == 8 ? TC_F64 : TC_F32; }
 #define TC_ENTRY(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB, VARIANT) {#NAME, dtype_of<T>(), MATH, BM, BN, VARIANT, tc_inst_##NAME},
-const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY)};
+#define TC_WS_ENTRY(NAME, BM, BN, STAGES, VARIANT) {#NAME, TC_F64, TC_MATH_DMMA, BM, BN, VARIANT, tc_inst_##NAME},
+const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY) TC_WS_KERNEL_LIST(TC_WS_ENTRY)};
 #undef TC_ENTRY
+#undef TC_WS_ENTRY
 
 const KernelEntry* find_kernel(int dtype, int math, int bm, int bn, int variant) {
   for (const KernelEntry& k : kKernels)
@@ -88,11 +94,13 @@ static tc_inst_fn pick_inst(const TcKernelChoice& c) {
   return k ? k->fn : nullptr;
 }
 
+static int mode_of(bool ext_vec, bool k_vec) { return ext_vec ? 1 : k_vec ? 2 : 0; }
+
 int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk) {
   if (bk) *bk = TC_BK;
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
-  return fn(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
+  return fn(mode_of(c.vec_x, c.kvec_x), mode_of(c.vec_y, c.kvec_y), nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
 }
 
 int tc_kernels_prepare(const TcKernelChoice& c) {
@@ -100,8 +108,9 @@ int tc_kernels_prepare(const TcKernelChoice& c) {
   // time demotes 16-byte loads to element loads.
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
-  for (int vx = 0; vx <= (c.vec_x ? 1 : 0); ++vx)
-    for (int vy = 0; vy <= (c.vec_y ? 1 : 0); ++vy) {
+  const int mx = mode_of(c.vec_x, c.kvec_x), my = mode_of(c.vec_y, c.kvec_y);
+  for (int vx = 0; vx <= mx; vx += (mx ? mx : 1))
+    for (int vy = 0; vy <= my; vy += (my ? my : 1)) {
       const int st = fn(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
       if (st != TC_OK) return st;
     }
@@ -112,7 +121,7 @@ int tc_kernels_prepare(const TcKernelChoice& c) {
 static int resident_ctas(const TcKernelChoice& c) {
   tc_inst_fn fn = pick_inst(c);
   int per_sm = 0, dev = 0, sms = 0;
-  if (!fn || fn(c.vec_x, c.vec_y, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_OCCUPANCY, &per_sm, nullptr) != TC_OK) return 0;
+  if (!fn || fn(mode_of(c.vec_x, c.kvec_x), mode_of(c.vec_y, c.kvec_y), nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_OCCUPANCY, &per_sm, nullptr) != TC_OK) return 0;
   if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
   return per_sm * sms;
 }
@@ -125,7 +134,7 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   const bool x16 = (reinterpret_cast<uintptr_t>(X) & 15) == 0, y16 = (reinterpret_cast<uintptr_t>(Y) & 15) == 0;
   const uintptr_t cu = reinterpret_cast<uintptr_t>(C);
   if ((cu & 15) != 0) a.vec_c = 1;
-  const int vx = c.vec_x && x16, vy = c.vec_y && y16;
+  const int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
   int st = fn(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
@@ -212,6 +221,9 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   p->args.koff_x = static_cast<const int64_t*>(p->d_koff);
   p->args.koff_y = p->args.koff_x + p->h_koff_x.size();
   if (p->ws_bytes) TC_CUDA_OK(cudaMalloc(&p->d_ws, p->ws_bytes));
+  TC_CUDA_OK(cudaMalloc(&p->d_status, sizeof(int)));
+  TC_CUDA_OK(cudaMemset(p->d_status, 0, sizeof(int)));
+  p->args.status = p->d_status;
   p->device = dev;
   p->committed = true;
   return TC_OK;
@@ -221,6 +233,7 @@ extern "C" void tc_plan_destroy(tc_plan* p) {
   if (!p) return;
   if (p->d_koff) cudaFree(p->d_koff);
   if (p->d_ws) cudaFree(p->d_ws);
+  if (p->d_status) cudaFree(p->d_status);
   delete p;
 }
 
@@ -249,6 +262,13 @@ extern "C" int tc_plan_cost(const tc_plan* p, double* flops, double* bytes) {
   }
   if (flops) *flops = tmp.flops;
   if (bytes) *bytes = tmp.bytes;
+  return TC_OK;
+}
+
+extern "C" int tc_plan_status(tc_plan* p, int* device_status) {
+  if (!p || !device_status) return TC_ERR_INVALID_ARG;
+  if (!p->committed) return TC_ERR_STATE;
+  TC_CUDA_OK(cudaMemcpy(device_status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
   return TC_OK;
 }
 

@@ -5,10 +5,13 @@
 // or reports the launch shape.
 #pragma once
 #include "tc_kernels.cuh"
+#include "tc_ws_kernel.cuh"
 
 enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3 };
 
-typedef int (*tc_inst_fn)(int vec_x, int vec_y, const TcKernelArgs* args, void* C, const void* X, const void* Y,
+// mode_x / mode_y: 0 element loads, 1 16-byte loads along the external index, 2 16-byte loads along the
+// contraction index (kernels without a contraction-major image treat 2 as 0).
+typedef int (*tc_inst_fn)(int mode_x, int mode_y, const TcKernelArgs* args, void* C, const void* X, const void* Y,
                           cudaStream_t stream, int mode, int* threads, int* smem_bytes);
 
 namespace tck {
@@ -40,11 +43,51 @@ int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cu
   return TC_OK;
 }
 
+template <class CF>
+int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
+                   int* threads, int* smem_bytes) {
+  auto kern = tc_ws_dmma_kernel<CF>;
+  if (mode == TC_INST_QUERY) {
+    if (threads) *threads = CF::CTA_THREADS;
+    if (smem_bytes) *smem_bytes = CF::SMEM_BYTES;
+    return TC_OK;
+  }
+  if (mode == TC_INST_OCCUPANCY) {
+    if (threads) *threads = 1;
+    return TC_OK;
+  }
+  if (mode == TC_INST_PREPARE) {
+    TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CF::SMEM_BYTES));
+    return TC_OK;
+  }
+  int dev = 0, sms = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const unsigned tiles = a->tiles_m * a->tiles_n;
+  const unsigned grid = (tiles + 1) / 2 < (unsigned)sms ? (tiles + 1) / 2 : (unsigned)sms;  // one persistent CTA per SM
+  kern<<<grid, CF::CTA_THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<double*>(C), static_cast<const double*>(X),
+                                                           static_cast<const double*>(Y));
+  TC_CUDA_OK(cudaGetLastError());
+  return TC_OK;
+}
+
 }  // namespace tck
+
+#define TC_WS_CASE(MX, MY, BM, BN, STAGES) \
+  if (vx == MX && vy == MY) return tck::run_ws_variant<tck::WsCfg<BM, BN, STAGES, MX, MY>>(a, C, X, Y, s, mode, threads, smem);
+#define TC_DEFINE_WS_INST(NAME, BM, BN, STAGES)                                                              \
+  extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,         \
+                      cudaStream_t s, int mode, int* threads, int* smem) {                                  \
+    TC_WS_CASE(0, 0, BM, BN, STAGES) TC_WS_CASE(0, 1, BM, BN, STAGES) TC_WS_CASE(0, 2, BM, BN, STAGES)      \
+    TC_WS_CASE(1, 0, BM, BN, STAGES) TC_WS_CASE(1, 1, BM, BN, STAGES) TC_WS_CASE(1, 2, BM, BN, STAGES)      \
+    TC_WS_CASE(2, 0, BM, BN, STAGES) TC_WS_CASE(2, 1, BM, BN, STAGES) TC_WS_CASE(2, 2, BM, BN, STAGES)      \
+    return TC_ERR_INVALID_ARG;                                                                              \
+  }
 
 #define TC_DEFINE_INST(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                                  \
   extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,              \
                       cudaStream_t s, int mode, int* threads, int* smem) {                                       \
+    vx = vx == 1; vy = vy == 1;                                                                                  \
     if (vx && vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, true, true>>(a, C, X, Y, s, mode, threads, smem);   \
     if (vx) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, true, false>>(a, C, X, Y, s, mode, threads, smem);        \
     if (vy) return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, false, true>>(a, C, X, Y, s, mode, threads, smem);        \

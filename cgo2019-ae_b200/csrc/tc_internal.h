@@ -76,6 +76,7 @@ struct TcKernelArgs {
   int32_t beta;      // 1: C is read and accumulated into; 0: C is overwritten
   double alpha;      // +1 or -1
   void* ws;          // K-slice partials: [ksplit][tiles][BN][BM]
+  int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
 enum TcMath { TC_MATH_DMMA = 0, TC_MATH_SIMT = 1 };
@@ -85,7 +86,8 @@ struct TcKernelChoice {
   int math;       // TcMath
   int bm, bn;     // CTA tile
   int variant;    // warp layout of the tile (0-based)
-  bool vec_x, vec_y;  // 16-byte loads along the external index of X / Y
+  bool vec_x, vec_y;    // 16-byte loads along the external index of X / Y are legal
+  bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
 };
 
 // Host-side plan.
@@ -108,6 +110,7 @@ struct tc_plan {
   std::vector<int64_t> h_koff_x, h_koff_y;
   void* d_koff = nullptr;      // device copy of both tables
   void* d_ws = nullptr;        // plan-owned K-slice workspace
+  int* d_status = nullptr;     // device status word
   size_t ws_bytes = 0;
   int64_t size_c = 0, size_a = 0, size_b = 0;  // elements spanned (max offset + 1)
   int64_t count_c = 0, count_a = 0, count_b = 0;  // logical element counts

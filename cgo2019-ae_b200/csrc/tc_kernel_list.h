@@ -25,4 +25,13 @@
   X(ffma_128x64, float, TC_MATH_SIMT, 128, 64, 1, 1, 4, 3, 0)              \
   X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)
 
+// Persistent warp-specialised fp64 kernels (tc_ws_kernel.cuh): two consumer groups of 2 x 2 warps,
+// each on its own BM x BN tile, plus four producer warps.
+//   X(name, BM, BN, STAGES, VARIANT)
+#define TC_WS_KERNEL_LIST(X) \
+  X(dmma_ws_128x64, 128, 64, 3, 2)     \
+  X(dmma_ws_128x64_s4, 128, 64, 4, 3)  \
+  X(dmma_ws_64x96, 64, 96, 3, 2)       \
+  X(dmma_ws_64x64, 64, 64, 4, 2)
+
 #endif  // TC_KERNEL_LIST_H_

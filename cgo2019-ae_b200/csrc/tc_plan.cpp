@@ -202,20 +202,26 @@ int tc_plan_build(tc_plan* p, std::string* why) {
 
   // Loader per operand.
   const int V = 16 / es;
-  auto loader = [&](const TcDims& ext, bool k_is_in, bool* vec, int32_t* lanes_k) {
+  auto loader = [&](const TcDims& ext, bool k_is_in, bool* vec, bool* kvec, int32_t* lanes_k) {
     *vec = false;
+    *kvec = false;
     *lanes_k = 1;
+    auto ks = [&](int d) { return k_is_in ? kd.s_in[d] : kd.s_out[d]; };
     if (ext.n > 0 && ext.s_in[0] == 1) {
       bool ok = ext.extent[0] % V == 0;
       for (int d = 1; d < ext.n; ++d) ok = ok && ext.s_in[d] % V == 0;
-      for (int d = 0; d < kd.n; ++d) ok = ok && (k_is_in ? kd.s_in[d] : kd.s_out[d]) % V == 0;
+      for (int d = 0; d < kd.n; ++d) ok = ok && ks(d) % V == 0;
       *vec = ok;
-    } else if (kd.n > 0 && (k_is_in ? kd.s_in[0] : kd.s_out[0]) == 1) {
+    } else if (kd.n > 0 && ks(0) == 1) {
       *lanes_k = 32 / es;
+      bool ok = kd.extent[0] % V == 0;
+      for (int d = 1; d < kd.n; ++d) ok = ok && ks(d) % V == 0;
+      for (int d = 0; d < ext.n; ++d) ok = ok && ext.s_in[d] % V == 0;
+      *kvec = ok;
     }
   };
-  loader(a.M, true, &c.vec_x, &a.lanes_k_x);
-  loader(a.N, false, &c.vec_y, &a.lanes_k_y);
+  loader(a.M, true, &c.vec_x, &c.kvec_x, &a.lanes_k_x);
+  loader(a.N, false, &c.vec_y, &c.kvec_y, &a.lanes_k_y);
 
   // Contiguous output elements per thread access.
   a.vec_c = 1;
@@ -307,7 +313,8 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
-      << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
+      << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
+      << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches
       << ",\"flops\":" << p.flops << ",\"bytes\":" << p.bytes;

@@ -1,0 +1,419 @@
+// Persistent, warp-specialised fp64 contraction kernel for sm_100a.
+//
+// Same tiling, address scheme, shared-memory image and DMMA fragment mapping as
+// tc_contract_kernel (tc_kernels.cuh); what changes is WHO does what and WHEN:
+//
+//   * one CTA per SM lives for the whole contraction and walks a strided list of
+//     output tiles;
+//   * warps 0-3 and 4-7 are two CONSUMER groups, each owning its own tile
+//     (BM x BN, 2 x 2 warps) and its own stage ring: shared loads, DMMA and the
+//     read-modify-write of C, nothing else;
+//   * warps 8-9 / 10-11 are the PRODUCERS of group 0 / 1: they decode the tile's
+//     offset tables, prefetch its C tile into L2 and issue every cp.async of its
+//     stages, running ahead of the consumers by the depth of the ring -- across
+//     tile boundaries, so the set-up and load latency of tile i+1 and the DRAM
+//     fetch of its C hide behind the products of tile i, and one group's
+//     epilogue overlaps the other group's products;
+//   * stages and tables are handed over through mbarriers in shared memory
+//     (cp.async.mbarrier.arrive makes a stage "full" when its copies land);
+//   * registers follow the roles (setmaxnreg): producers shrink, consumers grow.
+//
+// Every mbarrier wait is bounded: a wait that does not complete within
+// kSpinLimit polls records an error code in *args.status and the thread leaves
+// the kernel; its partners then run out of polls the same way, so the kernel
+// always terminates.  The host reads the status word after synchronising.
+#pragma once
+#include "tc_kernels.cuh"
+
+namespace tck {
+
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// Arrival that fires when all cp.async issued so far by this thread have landed.
+__device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *status = code) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicMax(status, code);
+  return false;
+}
+__device__ __forceinline__ void group_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+}
+template <int R> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(R)); }
+template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(R)); }
+
+// Loader / shared-image mode of one operand.
+//   LM_ELEM     element copies, external-major image  [k][ext], pitch ROWS+4
+//   LM_EXT_VEC  16-byte copies along the external index, same image
+//   LM_K_VEC    16-byte copies along the contraction index, contraction-major image [ext][k], pitch 18
+enum { LM_ELEM = 0, LM_EXT_VEC = 1, LM_K_VEC = 2 };
+
+template <int BM_, int BN_, int STAGES_, int MODEX_, int MODEY_>
+struct WsCfg {
+  using T = double;
+  static constexpr int BM = BM_, BN = BN_, BK = 16, STAGES = STAGES_;
+  static constexpr int MODEX = MODEX_, MODEY = MODEY_;
+  static constexpr int ES = 8, VW = 2;
+  static constexpr int GROUPS = 2;
+  static constexpr int CONSUMER_THREADS = 128;  // per group: 2 x 2 warps
+  static constexpr int THREADS = 64;            // producer threads per group
+  static constexpr int CTA_THREADS = GROUPS * (CONSUMER_THREADS + THREADS);
+  static constexpr int WM = BM / 2, WN = BN / 2;
+  static constexpr int LDK = BK + 2;            // pitch of a contraction-major image (18 = 2 mod 16: conflict-free)
+  static constexpr int LDX = MODEX == LM_K_VEC ? LDK : BM + 4;
+  static constexpr int LDY = MODEY == LM_K_VEC ? LDK : BN + 4;
+  static constexpr int XIMG = MODEX == LM_K_VEC ? BM * LDK : BK * (BM + 4);
+  static constexpr int YIMG = MODEY == LM_K_VEC ? BN * LDK : BK * (BN + 4);
+  static constexpr int STAGE_ELEMS = XIMG + YIMG;
+  static constexpr int TABLE_ELEMS = 2 * BM + 2 * BN;            // offx_m, offc_m, offy_n, offc_n
+  static constexpr int NBARS = GROUPS * (2 * STAGES + 4);
+  static constexpr int SMEM_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8;
+  static constexpr int PRODUCER_REGS = 56, CONSUMER_REGS = 224;
+};
+
+// Producer loaders.  A producer thread keeps what does not change inside a stage in
+// registers (its external offsets or its contraction offsets), so that one element
+// costs an add, a predicate and the copy.
+
+// 16 bytes along the external index, external-major image.
+template <class CF, int ROWS>
+__device__ __forceinline__ void ws_load_ext_vec(double* img, const double* __restrict__ g, const int64_t* s_off,
+                                                const int64_t* __restrict__ koff, uint32_t k0, uint32_t kend, int ptid) {
+  constexpr int LD = ROWS + 4, VPR = ROWS / 2, T = CF::THREADS;
+  const uint32_t sbase = smem_u32(img);
+  if constexpr (VPR >= T && VPR % T == 0) {
+#pragma unroll
+    for (int c = 0; c < VPR / T; ++c) {
+      const int ev = ptid + c * T;
+      const int64_t eo = s_off[ev * 2];
+#pragma unroll 8
+      for (int kk = 0; kk < CF::BK; ++kk) {
+        const bool ok = eo >= 0 && k0 + kk < kend;
+        const double* src = ok ? g + eo + koff[k0 + kk] : g;
+        cp_async16(sbase + (uint32_t)(kk * LD + ev * 2) * 8u, src, ok);
+      }
+    }
+  } else if constexpr (T % VPR == 0) {
+    const int ev = ptid % VPR;
+    const int64_t eo = s_off[ev * 2];
+#pragma unroll 8
+    for (int kk = ptid / VPR; kk < CF::BK; kk += T / VPR) {
+      const bool ok = eo >= 0 && k0 + kk < kend;
+      const double* src = ok ? g + eo + koff[k0 + kk] : g;
+      cp_async16(sbase + (uint32_t)(kk * LD + ev * 2) * 8u, src, ok);
+    }
+  } else {  // tile widths that neither divide nor are divided by the producer count
+    static_assert(VPR * CF::BK % T == 0, "loader shape");
+#pragma unroll 4
+    for (int sl = ptid; sl < VPR * CF::BK; sl += T) {
+      const int ev = sl % VPR, kk = sl / VPR;
+      const int64_t eo = s_off[ev * 2];
+      const bool ok = eo >= 0 && k0 + kk < kend;
+      const double* src = ok ? g + eo + koff[k0 + kk] : g;
+      cp_async16(sbase + (uint32_t)(kk * LD + ev * 2) * 8u, src, ok);
+    }
+  }
+}
+
+// 16 bytes along the contraction index, contraction-major image.
+template <class CF, int ROWS>
+__device__ __forceinline__ void ws_load_k_vec(double* img, const double* __restrict__ g, const int64_t* s_off,
+                                              const int64_t* __restrict__ koff, uint32_t k0, uint32_t kend, int ptid) {
+  constexpr int KV = CF::BK / 2, T = CF::THREADS;
+  static_assert(T % KV == 0 && ROWS % (T / KV) == 0, "loader shape");
+  const int kv = ptid % KV;
+  const uint32_t k = k0 + kv * 2;
+  const bool kok = k < kend;
+  const int64_t ko = kok ? koff[k] : 0;
+  const uint32_t sbase = smem_u32(img) + (uint32_t)(kv * 2) * 8u;
+#pragma unroll 8
+  for (int r = ptid / KV; r < ROWS; r += T / KV) {
+    const int64_t eo = s_off[r];
+    const bool ok = kok && eo >= 0;
+    const double* src = ok ? g + eo + ko : g;
+    cp_async16(sbase + (uint32_t)(r * CF::LDK) * 8u, src, ok);
+  }
+}
+
+// Element copies, external-major image.  lg = log2(lanes walking k): a warp covers 2^lg consecutive k
+// by 32 >> lg consecutive externals (whole 32-byte sectors along the operand's fastest index).
+template <class CF, int ROWS>
+__device__ __forceinline__ void ws_load_elem(double* img, const double* __restrict__ g, const int64_t* s_off,
+                                             const int64_t* __restrict__ koff, uint32_t k0, uint32_t kend, int ptid,
+                                             int lg) {
+  constexpr int LD = ROWS + 4, WARPS = CF::THREADS / 32;
+  const int lane = ptid & 31, warp = ptid >> 5;
+  const uint32_t sbase = smem_u32(img);
+  if (lg == 0) {  // lanes walk the external index: few externals, all 16 k per thread
+    constexpr int EG = ROWS / 32;  // groups of 32 externals
+#pragma unroll
+    for (int eg = warp; eg < EG; eg += WARPS) {
+      const int el = eg * 32 + lane;
+      const int64_t eo = s_off[el];
+#pragma unroll 8
+      for (int kk = 0; kk < CF::BK; ++kk) {
+        const bool ok = eo >= 0 && k0 + kk < kend;
+        const double* src = ok ? g + eo + koff[k0 + kk] : g;
+        cp_async8(sbase + (uint32_t)(kk * LD + el) * 8u, src, ok);
+      }
+    }
+  } else {  // 4 lanes walk k, 8 lanes walk the external index: 4 contraction offsets live in registers
+    const int lk = lane & 3, le = lane >> 2;
+    int64_t ko[4];
+    bool kok[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t k = k0 + q * 4 + lk;
+      kok[q] = k < kend;
+      ko[q] = kok[q] ? koff[k] : 0;
+    }
+#pragma unroll 4
+    for (int eg = warp; eg < ROWS / 8; eg += WARPS) {
+      const int el = eg * 8 + le;
+      const int64_t eo = s_off[el];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const bool ok = kok[q] && eo >= 0;
+        const double* src = ok ? g + eo + ko[q] : g;
+        cp_async8(sbase + (uint32_t)((q * 4 + lk) * LD + el) * 8u, src, ok);
+      }
+    }
+  }
+}
+
+template <class CF, int ROWS, int MODE>
+__device__ __forceinline__ void ws_load(double* img, const double* __restrict__ g, const int64_t* s_off,
+                                        const int64_t* __restrict__ koff, uint32_t k0, uint32_t kend, int ptid, int lg) {
+  if constexpr (MODE == LM_EXT_VEC) ws_load_ext_vec<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid);
+  else if constexpr (MODE == LM_K_VEC) ws_load_k_vec<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid);
+  else ws_load_elem<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid, lg);
+}
+
+// Fragment pair of the DMMA mapping: tile elements (e, e+1) at contraction index k.
+template <int MODE, int LD>
+__device__ __forceinline__ double2 ws_frag(const double* img, int e, int k) {
+  if constexpr (MODE == LM_K_VEC) return make_double2(img[e * LD + k], img[(e + 1) * LD + k]);
+  else return *reinterpret_cast<const double2*>(img + k * LD + e);
+}
+
+template <class CF>
+__global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __grid_constant__ TcKernelArgs p,
+                                                                         double* __restrict__ C,
+                                                                         const double* __restrict__ X,
+                                                                         const double* __restrict__ Y) {
+  constexpr int BM = CF::BM, BN = CF::BN, BK = CF::BK, LDX = CF::LDX, LDY = CF::LDY, STAGES = CF::STAGES;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  int64_t* tables = reinterpret_cast<int64_t*>(bars + CF::NBARS);
+  double* stages = reinterpret_cast<double*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const bool is_producer = warp >= 8;
+  const int gi = is_producer ? (warp - 8) >> 1 : warp >> 2;  // group served
+  uint64_t* full = bars + gi * (2 * STAGES + 4);             // [STAGES]
+  uint64_t* empty = full + STAGES;                           // [STAGES]
+  uint64_t* tab_full = empty + STAGES;                       // [2]
+  uint64_t* tab_empty = tab_full + 2;                        // [2]
+  int64_t* gtab = tables + gi * 2 * CF::TABLE_ELEMS;         // two table sets, alternating per tile
+  double* gstage = stages + gi * STAGES * CF::STAGE_ELEMS;
+
+  if (tid == 0) {
+    for (int q = 0; q < CF::GROUPS; ++q) {
+      uint64_t* b = bars + q * (2 * STAGES + 4);
+      for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::THREADS); mbar_init(b + STAGES + s, 4); }
+      for (int s = 0; s < 2; ++s) { mbar_init(b + 2 * STAGES + s, CF::THREADS); mbar_init(b + 2 * STAGES + 2 + s, 4); }
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  const uint32_t total = p.tiles_m * p.tiles_n;
+  const uint32_t first = 2u * blockIdx.x + gi, step = 2u * gridDim.x;
+  const int nk = (int)((p.Kflat + BK - 1) / BK);
+  const uint32_t kend = p.Kflat;
+  const bool accumulate = p.beta != 0;
+
+  if (is_producer) {
+    // ------------------------------------------------------------ producer ----
+    reg_dec<CF::PRODUCER_REGS>();
+    const int ptid = tid - 256 - gi * CF::THREADS;
+    const int lgx = p.lanes_k_x == 1 ? 0 : 2, lgy = p.lanes_k_y == 1 ? 0 : 2;
+    uint32_t it = 0, titer = 0;
+    for (uint32_t tile = first; tile < total; tile += step, ++titer) {
+      const uint32_t par = titer & 1;
+      int64_t* offx_m = gtab + par * CF::TABLE_ELEMS;
+      int64_t* offc_m = offx_m + BM;
+      int64_t* offy_n = offc_m + BM;
+      int64_t* offc_n = offy_n + BN;
+      if (!mbar_wait(&tab_empty[par], ((titer >> 1) & 1) ^ 1, p.status, 1)) return;
+      const uint32_t m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+      for (int i = ptid; i < BM + BN; i += CF::THREADS) {
+        if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
+        else decode(p.N, n0 + (i - BM), p.Nflat, &offy_n[i - BM], &offc_n[i - BM]);
+      }
+      mbar_arrive(&tab_full[par]);            // consumers may read the tables once all 64 have arrived
+      group_bar_sync(1 + gi, CF::THREADS);    // ... and so may this group's producers
+      if (accumulate && p.prefetch_dist != 0) {
+        constexpr int SEC = 4;                // doubles per 32-byte sector
+        constexpr int SPR = BM / SEC;
+        for (int i = ptid; i < SPR * BN; i += CF::THREADS) {
+          const int64_t cm = offc_m[(i % SPR) * SEC], cn = offc_n[i / SPR];
+          if (cm >= 0 && cn >= 0) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(C + cn + cm));
+        }
+      }
+      for (int ks = 0; ks < nk; ++ks, ++it) {
+        const uint32_t s = it % STAGES;
+        if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, 2)) return;
+        double* xs = gstage + s * CF::STAGE_ELEMS;
+        double* ys = xs + CF::XIMG;
+        const uint32_t k0 = (uint32_t)ks * BK;
+        ws_load<CF, BM, CF::MODEX>(xs, X, offx_m, p.koff_x, k0, kend, ptid, lgx);
+        ws_load<CF, BN, CF::MODEY>(ys, Y, offy_n, p.koff_y, k0, kend, ptid, lgy);
+        mbar_arrive_on_copies(&full[s]);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------- consumer ----
+  reg_inc<CF::CONSUMER_REGS>();
+  constexpr int WM = CF::WM, WN = CF::WN;
+  constexpr int MB2 = WM / 16, NB2 = WN / 16;
+  const int lane = tid & 31, cw = warp & 3;
+  const int g = lane >> 2, t = lane & 3;
+  const int wm0 = (cw & 1) * WM, wn0 = (cw >> 1) * WN;
+  const double alpha = p.alpha;
+  uint32_t it = 0, titer = 0;
+  for (uint32_t tile = first; tile < total; tile += step, ++titer) {
+    double acc[2 * NB2][2 * MB2][2];
+#pragma unroll
+    for (int j = 0; j < 2 * NB2; ++j)
+#pragma unroll
+      for (int i = 0; i < 2 * MB2; ++i) { acc[j][i][0] = 0.0; acc[j][i][1] = 0.0; }
+
+    for (int ks = 0; ks < nk; ++ks, ++it) {
+      const uint32_t s = it % STAGES;
+      if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, 3)) return;
+      const double* xs = gstage + s * CF::STAGE_ELEMS;
+      const double* ys = xs + CF::XIMG;
+      const int kleft = (int)kend - ks * BK;
+      const int nks = kleft >= BK ? BK / 4 : (kleft + 3) / 4;
+#pragma unroll
+      for (int kq = 0; kq < BK / 4; ++kq) {
+        if (kq < nks) {
+          const int k = kq * 4 + t;
+          double2 xf[MB2], yf[NB2];
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) xf[i] = ws_frag<CF::MODEX, LDX>(xs, wm0 + 2 * g + i * 16, k);
+#pragma unroll
+          for (int j = 0; j < NB2; ++j) yf[j] = ws_frag<CF::MODEY, LDY>(ys, wn0 + 2 * g + j * 16, k);
+#pragma unroll
+          for (int j = 0; j < NB2; ++j)
+#pragma unroll
+            for (int i = 0; i < MB2; ++i) {
+              dmma884(acc[2 * j][2 * i][0], acc[2 * j][2 * i][1], yf[j].x, xf[i].x);
+              dmma884(acc[2 * j][2 * i + 1][0], acc[2 * j][2 * i + 1][1], yf[j].x, xf[i].y);
+              dmma884(acc[2 * j + 1][2 * i][0], acc[2 * j + 1][2 * i][1], yf[j].y, xf[i].x);
+              dmma884(acc[2 * j + 1][2 * i + 1][0], acc[2 * j + 1][2 * i + 1][1], yf[j].y, xf[i].y);
+            }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);  // this warp no longer reads the stage
+    }
+
+    // ---- epilogue: read-modify-write of C (the tile was prefetched into L2 by the producers) ----
+    const uint32_t par = titer & 1;
+    if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4)) return;
+    const int64_t* offc_m = gtab + par * CF::TABLE_ELEMS + BM;
+    const int64_t* offc_n = offc_m + BM + BN;
+    if (p.vec_c == 4) {
+      int64_t co[MB2];
+#pragma unroll
+      for (int i = 0; i < MB2; ++i) co[i] = offc_m[wm0 + 16 * i + 4 * t];
+#pragma unroll
+      for (int j = 0; j < NB2; ++j) {
+        int64_t cn[2];
+        double2 c0[2][MB2], c1[2][MB2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          cn[h] = offc_n[wn0 + 16 * j + 2 * g + h];
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            c0[h][i] = make_double2(0.0, 0.0);
+            c1[h][i] = make_double2(0.0, 0.0);
+            if (accumulate && cn[h] >= 0 && co[i] >= 0) {
+              const double2* src = reinterpret_cast<const double2*>(C + cn[h] + co[i]);
+              c0[h][i] = src[0];
+              c1[h][i] = src[1];
+            }
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int nb = 2 * j + h;
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            if (cn[h] < 0 || co[i] < 0) continue;
+            double2* dst = reinterpret_cast<double2*>(C + cn[h] + co[i]);
+            dst[0] = make_double2(fma(alpha, acc[nb][2 * i][0], c0[h][i].x), fma(alpha, acc[nb][2 * i + 1][0], c0[h][i].y));
+            dst[1] = make_double2(fma(alpha, acc[nb][2 * i][1], c1[h][i].x), fma(alpha, acc[nb][2 * i + 1][1], c1[h][i].y));
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
+        if (cn < 0) continue;
+        if (p.vec_c == 2) {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + 2 * e];
+              if (co < 0) continue;
+              double2* dst = reinterpret_cast<double2*>(C + cn + co);
+              double2 c = make_double2(0.0, 0.0);
+              if (accumulate) c = *dst;
+              *dst = make_double2(fma(alpha, acc[nb][2 * i][e], c.x), fma(alpha, acc[nb][2 * i + 1][e], c.y));
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < MB2; ++i)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
+              if (co < 0) continue;
+              const double c = accumulate ? C[cn + co] : 0.0;
+              C[cn + co] = fma(alpha, acc[nb][2 * i + (q & 1)][q >> 1], c);
+            }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&tab_empty[par]);  // the producers may overwrite this table set
+  }
+}
+
+}  // namespace tck

@@ -100,6 +100,10 @@ int tc_plan_describe(const tc_plan* plan, char* buf, size_t cap);
 int tc_plan_cost(const tc_plan* plan, double* flops, double* bytes);
 /* Kernel launches one tc_execute enqueues. */
 int tc_plan_launches(const tc_plan* plan);
+/* Blocks until the device is idle for this plan's status word and reads it: 0 = every kernel of the
+ * plan ran to completion; non-zero = a bounded wait inside a persistent kernel gave up (the output
+ * of that execute is invalid).  No counterpart in the reference. */
+int tc_plan_status(tc_plan* plan, int* device_status);
 /* Bytes of caller-provided workspace tc_execute_ws needs (0 when the plan does not split K). */
 int tc_plan_workspace_bytes(const tc_plan* plan, size_t* bytes);
 
