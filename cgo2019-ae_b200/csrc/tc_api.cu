@@ -89,6 +89,11 @@ bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant) {
   return find_kernel(dtype, math, bm, bn, variant) != nullptr;
 }
 
+const char* tc_kernel_name(const TcKernelChoice& c) {
+  const KernelEntry* k = find_kernel(c.dtype, c.math, c.bm, c.bn, c.variant);
+  return k ? k->name : "?";
+}
+
 static tc_inst_fn pick_inst(const TcKernelChoice& c) {
   const KernelEntry* k = find_kernel(c.dtype, c.math, c.bm, c.bn, c.variant);
   return k ? k->fn : nullptr;
@@ -212,8 +217,8 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   st = tc_kernels_prepare(p->choice);
   if (st != TC_OK) return st;
   p->args.prefetch_dist = p->opt.l2_prefetch == 1 ? 0u : (uint32_t)resident_ctas(p->choice);
-  p->args.c_mode = p->opt.reserved[0] & 1;
-  p->args.c_stream = (p->opt.reserved[0] >> 1) & 1;
+  p->args.c_mode = p->opt.reserved[0] & 3;
+  p->args.c_stream = (p->opt.reserved[0] >> 2) & 1;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));
   TC_CUDA_OK(cudaMemcpy(p->d_koff, p->h_koff_x.data(), kb, cudaMemcpyHostToDevice));

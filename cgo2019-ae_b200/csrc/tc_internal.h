@@ -63,7 +63,8 @@ struct TcKernelArgs {
   uint32_t Mflat, Nflat, Kflat;
   uint32_t tiles_m, tiles_n;
   int32_t bm, bn;    // CTA tile of the chosen kernel
-  int32_t c_mode;    // 0: read-modify-write epilogue, 1: accumulators start from C
+  int32_t c_mode;    // 0: read-modify-write epilogue, 1: accumulators start from C,
+                     // 2: bulk asynchronous reduce-add from shared memory (persistent kernels)
   int32_t c_stream;  // cache-streaming hints on accesses to C
   uint32_t prefetch_dist;  // blocks ahead whose output tile is prefetched into L2 (0 = off)
   uint32_t k_chunk;  // flattened contraction range per K slice (multiple of the K step)
@@ -134,6 +135,7 @@ int tc_kernels_prepare(const TcKernelChoice& c);  // opt-in shared memory attrib
 
 // Compiled kernels (registry built from tc_kernel_list.h).
 bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant);
+const char* tc_kernel_name(const TcKernelChoice& c);  // registry name, "?" if absent
 constexpr int TC_BK = 16;  // contraction step of every kernel
 
 #endif  // TC_INTERNAL_H_

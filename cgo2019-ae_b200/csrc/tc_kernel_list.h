@@ -30,7 +30,6 @@
 //   X(name, BM, BN, STAGES, VARIANT)
 #define TC_WS_KERNEL_LIST(X) \
   X(dmma_ws_128x64, 128, 64, 3, 2)     \
-  X(dmma_ws_128x64_s4, 128, 64, 4, 3)  \
   X(dmma_ws_64x96, 64, 96, 3, 2)       \
   X(dmma_ws_64x64, 64, 64, 4, 2)
 

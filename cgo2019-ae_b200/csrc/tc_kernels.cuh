@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
   //      stores alpha*acc; the C tile of a CTA one wave ahead is prefetched into L2.
   const bool accumulate = p.ksplit == 1 && p.beta != 0;
   const bool init_from_c = accumulate && p.c_mode == 1;
-  const bool rmw = accumulate && p.c_mode == 0;
+  const bool rmw = accumulate && p.c_mode != 1;
   const bool stream = p.c_stream != 0;  // cache-streaming hints on the accesses to C
 
   auto prefetch_tile = [&](const int64_t* tm, const int64_t* tn) {

@@ -236,14 +236,13 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   a.alpha = e.op < 0 ? -1.0 : 1.0;
   a.beta = e.op == 0 ? 0 : 1;
 
-  // CTA tile and warp layout.  Rules distilled from tile sweeps on B200 over the
+  // CTA tile and kernel variant.  Rules distilled from tile sweeps on B200 over the
   // benchmark configurations (they replace the reference's transaction-count
   // cost model, cogent/src/algs/bases/cost_models.py:191-574):
-  //   * fp64 tensor pipe: the N tile that wastes least of Nflat among 64 / 96;
-  //     long contractions (compute bound) want the 64x32 warp tile of 128x64/4 warps,
-  //     short ones (output bound) more warps in flight: 128x64/8 warps;
-  //   * vector pipe: 128x128;
-  //   * anything that would leave most SMs without a tile: 64x64.
+  //   * fp64 tensor pipe: the persistent warp-specialised kernel (variant 2), N tile
+  //     64 or 96, whichever wastes less of Nflat (128 x 64 or 64 x 96 per consumer group);
+  //   * vector pipe: 128 x 128;
+  //   * anything that would leave most SMs without a tile: 64 x 64, one CTA per tile.
   int bm = 128, bn = 128, variant = 0;
   if (p->opt.tile_m > 0 || p->opt.tile_n > 0) {
     bm = p->opt.tile_m;
@@ -253,10 +252,11 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     auto waste = [&](int64_t n, int64_t b) { return (double)(((n + b - 1) / b) * b) / (double)n; };
     if (c.math == TC_MATH_DMMA) {
       if (waste(nf, 96) + 0.02 < waste(nf, 64)) { bm = 64; bn = 96; }
-      else { bm = 128; bn = 64; variant = kf >= 256 ? 0 : 1; }
+      else { bm = 128; bn = 64; }
+      variant = 2;
     }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
-    if (ctas < 2 * 148 && (bm > 64 || c.math == TC_MATH_SIMT)) { bm = 64; bn = 64; variant = 0; }
+    if (ctas < 2 * 148) { bm = 64; bn = 64; variant = 0; }
     if (p->opt.variant > 0) variant = p->opt.variant - 1;
   }
   c.bm = bm;
@@ -273,7 +273,9 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // K split: only when the tile count cannot fill the GPU and K is long.
   int64_t ksplit = 1;
   const int64_t ksteps = (kf + bk - 1) / bk;
-  if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
+  const bool persistent = c.math == TC_MATH_DMMA && c.variant >= 2;  // these kernels do not split K
+  if (persistent) ksplit = 1;
+  else if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
   else if (p->opt.split_k == 0 && tiles * 2 <= 148 && ksteps >= 16)
     ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * 148) / tiles, ksteps / 8));
   int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
@@ -310,7 +312,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     dims(a.N);
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
-      << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
+      << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")

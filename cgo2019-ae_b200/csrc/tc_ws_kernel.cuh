@@ -86,7 +86,12 @@ struct WsCfg {
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
   static constexpr int TABLE_ELEMS = 2 * BM + 2 * BN;            // offx_m, offc_m, offy_n, offc_n
   static constexpr int NBARS = GROUPS * (2 * STAGES + 4);
-  static constexpr int SMEM_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8;
+  // Epilogue staging for the bulk reduce: per consumer warp 8 rows of WM outputs, pitch WM+2
+  // (16-byte aligned rows, conflict-free 16-byte writes).
+  static constexpr int CPITCH = WM + 2;
+  static constexpr int CSTAGE_ELEMS = 8 * CPITCH;
+  static constexpr int SMEM_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8 +
+                                    GROUPS * 4 * CSTAGE_ELEMS * 8;
   static constexpr int PRODUCER_REGS = 56, CONSUMER_REGS = 224;
 };
 
@@ -225,6 +230,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
   int64_t* tables = reinterpret_cast<int64_t*>(bars + CF::NBARS);
   double* stages = reinterpret_cast<double*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
+  double* cstages = stages + CF::GROUPS * CF::STAGES * CF::STAGE_ELEMS;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -273,14 +279,16 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       }
       mbar_arrive(&tab_full[par]);            // consumers may read the tables once all 64 have arrived
       group_bar_sync(1 + gi, CF::THREADS);    // ... and so may this group's producers
-      if (accumulate && p.prefetch_dist != 0) {
+      auto prefetch_c = [&]() {
         constexpr int SEC = 4;                // doubles per 32-byte sector
         constexpr int SPR = BM / SEC;
         for (int i = ptid; i < SPR * BN; i += CF::THREADS) {
           const int64_t cm = offc_m[(i % SPR) * SEC], cn = offc_n[i / SPR];
           if (cm >= 0 && cn >= 0) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(C + cn + cm));
         }
-      }
+      };
+      const bool pf = accumulate && p.prefetch_dist != 0;
+      if (pf && !p.c_stream) prefetch_c();
       for (int ks = 0; ks < nk; ++ks, ++it) {
         const uint32_t s = it % STAGES;
         if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, 2)) return;
@@ -291,6 +299,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         ws_load<CF, BN, CF::MODEY>(ys, Y, offy_n, p.koff_y, k0, kend, ptid, lgy);
         mbar_arrive_on_copies(&full[s]);
       }
+      if (pf && p.c_stream) prefetch_c();
     }
     return;
   }
@@ -305,11 +314,36 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const double alpha = p.alpha;
   uint32_t it = 0, titer = 0;
   for (uint32_t tile = first; tile < total; tile += step, ++titer) {
+    const uint32_t par = titer & 1;
+    const int64_t* offc_m = gtab + par * CF::TABLE_ELEMS + BM;
+    const int64_t* offc_n = offc_m + BM + BN;
     double acc[2 * NB2][2 * MB2][2];
 #pragma unroll
     for (int j = 0; j < 2 * NB2; ++j)
 #pragma unroll
       for (int i = 0; i < 2 * MB2; ++i) { acc[j][i][0] = 0.0; acc[j][i][1] = 0.0; }
+    // Optional (c_mode 1, 32-byte-contiguous output): the accumulators start as alpha*C.  The producers
+    // prefetched this tile's C into L2 a whole tile ago, all loads go out at once and overlap the wait for
+    // the first stage; the epilogue is then stores only.
+    const bool from_c = accumulate && p.c_mode == 1 && p.vec_c == 4;
+    if (from_c) {
+      if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 5)) return;
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          const int64_t co = offc_m[wm0 + 16 * i + 4 * t];
+          if (cn < 0 || co < 0) continue;
+          const double2* src = reinterpret_cast<const double2*>(C + cn + co);
+          const double2 v0 = src[0], v1 = src[1];
+          acc[nb][2 * i][0] = alpha * v0.x;
+          acc[nb][2 * i + 1][0] = alpha * v0.y;
+          acc[nb][2 * i][1] = alpha * v1.x;
+          acc[nb][2 * i + 1][1] = alpha * v1.y;
+        }
+      }
+    }
 
     for (int ks = 0; ks < nk; ++ks, ++it) {
       const uint32_t s = it % STAGES;
@@ -343,11 +377,50 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     }
 
     // ---- epilogue: read-modify-write of C (the tile was prefetched into L2 by the producers) ----
-    const uint32_t par = titer & 1;
-    if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4)) return;
-    const int64_t* offc_m = gtab + par * CF::TABLE_ELEMS + BM;
-    const int64_t* offc_n = offc_m + BM + BN;
-    if (p.vec_c == 4) {
+    if (!from_c && !mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4)) return;
+    const bool rmw = accumulate && !from_c;
+    // c_mode 2: the warp's tile leaves through shared memory as bulk asynchronous copies, one per output
+    // row (WM contiguous elements): `+=`/`-=` become reduce-adds performed by the memory system, so the SM
+    // neither loads C nor waits for it.  Needs the warp's WM outputs of a row to be contiguous in C.
+    bool bulk = false;
+    if (p.c_mode == 2 && p.vec_c == 4 && !from_c) {
+      const int64_t c_lo = offc_m[wm0], c_hi = offc_m[wm0 + WM - 1];
+      bulk = c_lo >= 0 && c_hi == c_lo + WM - 1;  // uniform across the warp
+    }
+    if (bulk) {
+      double* cst = cstages + (gi * 4 + cw) * CF::CSTAGE_ELEMS;
+      const int64_t c_lo = offc_m[wm0];
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        // the previous batch must have been read out of the staging rows
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          double2* dst = reinterpret_cast<double2*>(cst + g * CF::CPITCH + 16 * i + 4 * t);
+          dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
+          dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncwarp();
+        if (lane < 8) {
+          const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * lane + (nb & 1)];
+          if (cn >= 0) {
+            const uint32_t src = smem_u32(cst + lane * CF::CPITCH);
+            double* dstg = C + cn + c_lo;
+            if (accumulate)
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;\n" ::"l"(dstg),
+                           "r"(src), "n"(WM * 8)
+                           : "memory");
+            else
+              asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dstg), "r"(src),
+                           "n"(WM * 8)
+                           : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        }
+      }
+    } else if (p.vec_c == 4) {
       int64_t co[MB2];
 #pragma unroll
       for (int i = 0; i < MB2; ++i) co[i] = offc_m[wm0 + 16 * i + 4 * t];
@@ -362,7 +435,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
           for (int i = 0; i < MB2; ++i) {
             c0[h][i] = make_double2(0.0, 0.0);
             c1[h][i] = make_double2(0.0, 0.0);
-            if (accumulate && cn[h] >= 0 && co[i] >= 0) {
+            if (rmw && cn[h] >= 0 && co[i] >= 0) {
               const double2* src = reinterpret_cast<const double2*>(C + cn[h] + co[i]);
               c0[h][i] = src[0];
               c1[h][i] = src[1];
@@ -414,6 +487,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     __syncwarp();
     if (lane == 0) mbar_arrive(&tab_empty[par]);  // the producers may overwrite this table set
   }
+  asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // outstanding bulk copies of this thread
 }
 
 }  // namespace tck

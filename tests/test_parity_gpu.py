@@ -35,6 +35,7 @@ def _run(pkg, orc, torch, expr, dtype, seed, **kw):
     plan.execute(dc, da, db)
     torch.cuda.synchronize()
     desc = plan.describe()
+    assert plan.status() == 0, "a bounded wait inside a persistent kernel gave up"
     plan.close()
     return orc.rel_error(dc.cpu().numpy(), ref), desc
 
@@ -59,7 +60,9 @@ def test_device_generator_matches_checker(pkg, orc, torch_cuda):
 def test_config1_full_size_all_paths(pkg, orc, torch_cuda):
     expr, dt, seed = CONFIGS[0]
     for kw in ({}, {"path": pkg.PATH_DFMA}, {"tile": (128, 128)}, {"tile": (128, 64), "variant": 2},
-               {"tile": (64, 96)}, {"tile": (64, 64), "split_k": 2}):
+               {"tile": (64, 96)}, {"tile": (64, 64), "split_k": 2}, {"tile": (128, 64), "variant": 3},
+               {"tile": (64, 96), "variant": 3}, {"tile": (64, 64), "variant": 3},
+               {"tile": (128, 64), "variant": 3, "tuning": 2}):
         err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
         assert err <= TOL[dt], (kw, err)
 
@@ -78,7 +81,10 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
         assert err <= TOL[dt], (expr, tile, err)
     if dt == "float64":
         for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 128), "variant": 2}, {"tile": (128, 64), "variant": 2},
-                   {"l2_prefetch": 1}, {"tuning": 1}, {"tuning": 3}):
+                   {"l2_prefetch": 1}, {"tuning": 1}, {"tuning": 2}, {"tile": (128, 64), "variant": 3},
+                   {"tile": (64, 96), "variant": 3}, {"tile": (64, 64), "variant": 3, "tuning": 1},
+                   {"tile": (128, 64), "variant": 3, "tuning": 2}, {"tile": (64, 96), "variant": 3, "tuning": 2},
+                   {"tile": (128, 64), "path": pkg.PATH_DMMA}):
             err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
             assert err <= TOL[dt], (expr, kw, err)
 
@@ -159,11 +165,13 @@ def test_config5_one_eighth_slabs(pkg, orc, torch_cuda):
 
 
 # ------------------------------------------------------- random expressions ----
-@pytest.mark.parametrize("path", ["dmma", "dfma", "ffma"])
+@pytest.mark.parametrize("path", ["dmma", "dfma", "ffma", "persistent", "persistent_bulk"])
 def test_random_contractions(pkg, orc, torch_cuda, path):
-    rng = random.Random({"dmma": 11, "dfma": 12, "ffma": 13}[path])
+    rng = random.Random({"dmma": 11, "dfma": 12, "ffma": 13, "persistent": 14, "persistent_bulk": 15}[path])
     dt = "float32" if path == "ffma" else "float64"
     kw = {"path": pkg.PATH_DFMA} if path == "dfma" else {}
+    if path.startswith("persistent"):  # small problems would not pick the persistent kernel by themselves
+        kw = {"tile": (128, 64), "variant": 3, "tuning": 2 if path.endswith("bulk") else 0}
     for n in range(40):
         expr = _random_expr(rng, max_out=5, max_sum=3, multi_char=(n % 4 == 0))
         err, d = _run(pkg, orc, torch_cuda, expr, dt, 100 + n, **kw)
@@ -188,8 +196,9 @@ def test_edge_shapes(pkg, orc, torch_cuda, expr):
     for dt in ("float64", "float32"):
         err, d = _run(pkg, orc, torch_cuda, expr, dt, 42)
         assert err <= TOL[dt], (expr, dt, err, d)
-    err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, path=pkg.PATH_DFMA)
-    assert err <= TOL["float64"]
+    for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "tuning": 2}):
+        err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, **kw)
+        assert err <= TOL["float64"], (expr, kw, err)
 
 
 def test_overwrite_ignores_initial_output_even_nan(pkg, orc, torch_cuda):

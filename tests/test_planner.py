@@ -51,11 +51,18 @@ def test_loader_and_vector_choices(pkg):
 
 def test_tile_choices(pkg):
     d = [_plan(pkg, e, dt).describe() for e, dt, _ in CONFIGS]
-    assert d[1]["tile"][:2] == [64, 96] and d[1]["tiles"] == [13824, 1]      # N = 96 exactly one tile wide
-    assert d[2]["tile"][:2] == [128, 64] and d[2]["variant"] == 0          # long contraction
-    assert d[4]["tile"][:2] == [128, 64] and d[4]["variant"] == 1          # short contraction, output bound
-    assert d[3]["math"] == "ffma" and d[3]["tile"][:2] == [128, 128]
-    assert d[0]["tile"][:2] == [64, 64]                                     # tiny problem
+    # fp64 with enough tiles: the persistent warp-specialised kernel (variant 2)
+    assert d[1]["kernel"] == "dmma_ws_64x96" and d[1]["tiles"] == [13824, 1]   # N = 96 is exactly one tile wide
+    assert d[2]["kernel"] == "dmma_ws_128x64" and d[2]["tiles"] == [32, 64]
+    assert d[4]["kernel"] == "dmma_ws_128x64" and d[4]["tiles"] == [500, 1000]
+    assert d[3]["math"] == "ffma" and d[3]["kernel"] == "ffma_128x128"
+    assert d[0]["kernel"] == "dmma_64x64_w4"                                    # tiny problem: one CTA per tile
+    # operands whose fastest index is contracted are staged contraction-major with 16-byte copies
+    assert d[4]["kvec_x"] and d[4]["vec_y"] and not d[4]["vec_x"]
+    assert d[2]["kvec_x"] and d[2]["vec_y"]
+    # forcing a persistent kernel disables the K split
+    forced = _plan(pkg, "C [a,33,b,17] += sum(c,1000,d,9) * A [a,c,d] * B [d,b,c];", tile=(128, 64), variant=3).describe()
+    assert forced["ksplit"] == 1 and forced["kernel"] == "dmma_ws_128x64"
 
 
 def test_k_split_plans(pkg):
