@@ -216,9 +216,15 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   TC_CUDA_OK(cudaGetDevice(&dev));
   st = tc_kernels_prepare(p->choice);
   if (st != TC_OK) return st;
-  p->args.prefetch_dist = p->opt.l2_prefetch == 1 ? 0u : (uint32_t)resident_ctas(p->choice);
-  p->args.c_mode = p->opt.reserved[0] & 3;
-  p->args.c_stream = (p->opt.reserved[0] >> 2) & 1;
+  // How the result reaches C (tc_options.c_path) and whether output tiles are prefetched into L2.
+  // Defaults follow the B200 measurements: persistent kernels hand their tiles to the memory system as
+  // bulk reduce-adds and need no prefetch; the one-CTA-per-tile kernels read-modify-write behind a prefetch.
+  const bool persistent = p->choice.math == TC_MATH_DMMA && p->choice.variant >= 2;
+  const int c_path = p->opt.c_path;
+  p->args.c_mode = c_path > 0 ? c_path - 1 : (persistent ? 2 : 0);
+  p->args.c_stream = 0;
+  const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !(persistent && p->args.c_mode == 2));
+  p->args.prefetch_dist = prefetch ? (uint32_t)resident_ctas(p->choice) : 0u;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));
   TC_CUDA_OK(cudaMemcpy(p->d_koff, p->h_koff_x.data(), kb, cudaMemcpyHostToDevice));

@@ -53,8 +53,13 @@ typedef struct tc_options {
   int tile_n;     /*     of the compiled shapes, see tc_plan_describe)                */
   int split_k;    /* 0 = planner's choice, 1 = never split, >1 = that many K slices   */
   int variant;    /* 0 = planner's choice; otherwise 1-based warp layout of the tile  */
-  int l2_prefetch; /* 0 = on (output tiles are prefetched into L2 one wave ahead), 1 = off */
-  int reserved[2];
+  int l2_prefetch; /* output tiles are prefetched into L2 ahead of their read-modify-write:  */
+                   /*   0 = planner's choice, 1 = off, 2 = on                                */
+  int c_path;      /* how `+=`/`-=` reach the output: 0 = planner's choice, 1 = read-modify- */
+                   /*   write in the epilogue, 2 = accumulators start from the output,       */
+                   /*   3 = bulk asynchronous reduce-add from shared memory (persistent      */
+                   /*   kernels, rows contiguous in the output; falls back to 1 elsewhere)   */
+  int reserved[1];
 } tc_options;
 
 typedef struct tc_plan tc_plan;

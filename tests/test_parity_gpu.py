@@ -62,7 +62,7 @@ def test_config1_full_size_all_paths(pkg, orc, torch_cuda):
     for kw in ({}, {"path": pkg.PATH_DFMA}, {"tile": (128, 128)}, {"tile": (128, 64), "variant": 2},
                {"tile": (64, 96)}, {"tile": (64, 64), "split_k": 2}, {"tile": (128, 64), "variant": 3},
                {"tile": (64, 96), "variant": 3}, {"tile": (64, 64), "variant": 3},
-               {"tile": (128, 64), "variant": 3, "tuning": 2}):
+               {"tile": (128, 64), "variant": 3, "c_path": 1}):
         err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
         assert err <= TOL[dt], (kw, err)
 
@@ -81,10 +81,10 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
         assert err <= TOL[dt], (expr, tile, err)
     if dt == "float64":
         for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 128), "variant": 2}, {"tile": (128, 64), "variant": 2},
-                   {"l2_prefetch": 1}, {"tuning": 1}, {"tuning": 2}, {"tile": (128, 64), "variant": 3},
-                   {"tile": (64, 96), "variant": 3}, {"tile": (64, 64), "variant": 3, "tuning": 1},
-                   {"tile": (128, 64), "variant": 3, "tuning": 2}, {"tile": (64, 96), "variant": 3, "tuning": 2},
-                   {"tile": (128, 64), "path": pkg.PATH_DMMA}):
+                   {"tile": (64, 64), "l2_prefetch": 1}, {"tile": (64, 64), "c_path": 2},
+                   {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3},
+                   {"tile": (64, 64), "variant": 3, "c_path": 2}, {"tile": (128, 64), "variant": 3, "c_path": 1},
+                   {"tile": (64, 96), "variant": 3, "c_path": 1, "l2_prefetch": 2}):
             err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
             assert err <= TOL[dt], (expr, kw, err)
 
@@ -171,7 +171,7 @@ def test_random_contractions(pkg, orc, torch_cuda, path):
     dt = "float32" if path == "ffma" else "float64"
     kw = {"path": pkg.PATH_DFMA} if path == "dfma" else {}
     if path.startswith("persistent"):  # small problems would not pick the persistent kernel by themselves
-        kw = {"tile": (128, 64), "variant": 3, "tuning": 2 if path.endswith("bulk") else 0}
+        kw = {"tile": (128, 64), "variant": 3, "c_path": 3 if path.endswith("bulk") else 1}
     for n in range(40):
         expr = _random_expr(rng, max_out=5, max_sum=3, multi_char=(n % 4 == 0))
         err, d = _run(pkg, orc, torch_cuda, expr, dt, 100 + n, **kw)
@@ -196,7 +196,7 @@ def test_edge_shapes(pkg, orc, torch_cuda, expr):
     for dt in ("float64", "float32"):
         err, d = _run(pkg, orc, torch_cuda, expr, dt, 42)
         assert err <= TOL[dt], (expr, dt, err, d)
-    for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "tuning": 2}):
+    for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "c_path": 1}):
         err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, **kw)
         assert err <= TOL["float64"], (expr, kw, err)
 
