@@ -62,6 +62,8 @@ _SIGNATURES = {
                                   ctypes.c_void_p]),
     "tc_execute_ws": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "tc_execute_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_void_p]),
     "tc_execute_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tc_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "tc_last_cuda_error": (ctypes.c_char_p, []),
@@ -200,6 +202,12 @@ class Plan:
         else:
             nbytes = workspace.numel() * workspace.element_size()
             _check(lib().tc_execute_ws(self._h, _ptr(C), _ptr(A), _ptr(B), _ptr(workspace), nbytes, s), "tc_execute_ws")
+
+    def execute_noalloc(self, C, A, B, stream=None):
+        """tc_execute that takes K-slice scratch from the library's fixed array instead of allocated memory
+        (for callers that cannot allocate); the plan must be committed and the scratch need must fit."""
+        s = ctypes.c_void_p(stream) if stream else None
+        _check(lib().tc_execute_noalloc(self._h, _ptr(C), _ptr(A), _ptr(B), s), "tc_execute_noalloc")
 
     def execute_host(self, C, A, B):
         """Blocking call on host arrays (numpy, C-contiguous 1-D storage in column-major element order)."""

@@ -327,6 +327,52 @@ extern "C" int tc_execute_ws(tc_plan* p, void* C, const void* A, const void* B, 
   return execute_impl(p, C, A, B, ws, ws_bytes, stream);
 }
 
+// ---------------------------------------------------- execute without allocating ----
+// K-slice scratch that lives in the library image instead of in allocated memory.  Every GPU that
+// loads the library carries these 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_tc_static_ws[TC_NOALLOC_MAX_WORKSPACE_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_tc_static_ws per device.  In host code the array's name is only a handle for
+// the runtime, not an address a kernel can use; the real address comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+void* g_static_ws_addr[kMaxDevices] = {};
+}  // namespace
+
+// For callers that must not allocate device memory at call time and have none to lend: an application
+// whose own pool already owns the whole device (the reference's competitors pre-claim memory this way,
+// nwchem-tccg/memory.cu:74-163), or a latency-critical loop where cudaMalloc's implicit device-wide
+// synchronisation is not acceptable.  Same work as tc_execute on a committed plan; a plan that slices
+// the contraction takes its slice scratch from the static array above.
+//   * The plan must already be committed (committing uploads tables, which allocates): TC_ERR_STATE otherwise.
+//   * Plans that need more than TC_NOALLOC_MAX_WORKSPACE_BYTES of scratch are refused with TC_ERR_WORKSPACE.
+//   * The first call on each device looks up the array's device address; make that call before any
+//     stream capture begins.
+//   * All calls on a device share the one array and it keeps whatever the last call left in it.  Nothing
+//     in it has to start at zero: every slice overwrites its whole partial tile before the combine step
+//     reads it.  Two calls whose kernels overlap on the GPU (different streams) race on it: serialise them.
+extern "C" int tc_execute_noalloc(tc_plan* p, void* C, const void* A, const void* B, void* stream) {
+  if (!p || !C || !A || !B) return TC_ERR_INVALID_ARG;
+  if (!p->committed) return TC_ERR_STATE;
+  if (p->ws_bytes > (size_t)TC_NOALLOC_MAX_WORKSPACE_BYTES) return TC_ERR_WORKSPACE;
+  int dev = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev != p->device || dev < 0 || dev >= kMaxDevices) return TC_ERR_STATE;
+  void* ws = nullptr;
+  if (p->ws_bytes) {
+    ws = __atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE);
+    if (!ws) {
+      void* addr = nullptr;
+      TC_CUDA_OK(cudaGetSymbolAddress(&addr, g_tc_static_ws));
+      if (!addr) return TC_ERR_CUDA;
+      __atomic_store_n(&g_static_ws_addr[dev], addr, __ATOMIC_RELEASE);  // same value from every thread
+      ws = addr;
+    }
+  }
+  return execute_impl(p, C, A, B, ws, (size_t)TC_NOALLOC_MAX_WORKSPACE_BYTES, stream);
+}
+
 extern "C" int tc_execute_host(tc_plan* p, void* C, const void* A, const void* B) {
   if (!p || !C || !A || !B) return TC_ERR_INVALID_ARG;
   if (!p->committed) {

@@ -127,6 +127,18 @@ int tc_execute(tc_plan* plan, void* C, const void* A, const void* B, void* strea
 int tc_execute_ws(tc_plan* plan, void* C, const void* A, const void* B, void* workspace,
                   size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  tc_execute for callers that can neither allocate device memory
+ * when they call nor spare any for a workspace: programs whose own memory pool already owns the
+ * device, and latency-critical loops that cannot take cudaMalloc's device-wide synchronisation.
+ * The scratch of K-sliced plans comes from a fixed array inside the library image
+ * (TC_NOALLOC_MAX_WORKSPACE_BYTES, held by every GPU that loads the library until exit); the call
+ * itself never allocates or frees.  The plan must already be committed (TC_ERR_STATE otherwise);
+ * plans needing more scratch than the array return TC_ERR_WORKSPACE.  The first call on a device
+ * resolves the array's device address: issue it before any stream capture.  Calls on one device
+ * share the array, so calls whose kernels may overlap on the GPU must be serialised by the caller. */
+#define TC_NOALLOC_MAX_WORKSPACE_BYTES (8u << 20)
+int tc_execute_noalloc(tc_plan* plan, void* C, const void* A, const void* B, void* stream);
+
 /* Blocking convenience over HOST pointers: allocate, copy in (C too), run,
  * copy C back, free -- what the reference's sd_t_d2_fusion does around its
  * kernel (cogent/src/codes/others/tc_pre_CUDA_Malloc.py:6-47,
