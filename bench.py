@@ -41,11 +41,13 @@ WORKLOADS = {
     "cfg3": ("C [a,64,b,64,c,64,d,64] += sum(e,64,f,64) * A [e,c,a,f] * B [b,f,d,e];", "f64", 2),
     "cfg4": ("C [a,24,b,24,c,24,i,24,j,24,k,24] += sum(l,24) * A [l,a,i,j] * B [b,c,k,l];", "f32", 3),
     "cfg5": ("C [a,40,b,40,c,40,d,40,e,40,f,40] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];", "f64", 4),
+    # what one GPU runs when cfg5 is cut 8 ways along f (4.1 GB of output): small enough to profile
+    "cfg5_shard8": ("C [a,40,b,40,c,40,d,40,e,40,f,5] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];", "f64", 4),
 }
 METRIC = "GFLOP/s per contraction"
-# DRAM bytes one launch of the cfg2 kernel moves (dram__bytes_read.sum + dram__bytes_write.sum, one ncu
-# capture, profiles/dmma_64x96_cfg2.md); None until captured for the current kernel.
-NCU_TRAFFIC_BYTES = {"cfg2": 1988625664}
+# DRAM bytes one launch of the workload's kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of one
+# ncu capture, summarised under profiles/); cfg5 is 8 x the captured one-eighth slab.
+NCU_TRAFFIC_BYTES = {"cfg2": 1988028160, "cfg5_shard8": 8380523776, "cfg5": 8 * 8380523776}
 
 
 def measured_peaks():
@@ -148,7 +150,7 @@ def quick_config(pkg, orc, torch, name, steps=5):
     del dc, da, db
     torch.cuda.empty_cache()
     return {"workload": name, "dtype": dtype, "gflops": flops * steps / sec * 1e-9, "ms": sec / steps * 1e3,
-            "algorithmic_gbs": nbytes * steps / sec * 1e-9, "kernel": "%s_%dx%d" % (d["math"], d["tile"][0], d["tile"][1])}
+            "algorithmic_gbs": nbytes * steps / sec * 1e-9, "kernel": d["kernel"]}
 
 
 def run_ours(args):
@@ -265,7 +267,7 @@ def run_ours(args):
                 "peak_source": "MEASURED_PEAKS.json hbm_gbs (of %s)" % hbm_src}
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof["traffic"] = NCU_TRAFFIC_BYTES.get(name) if world == 1 else None
-    roof["kernel"] = "tc_contract_kernel<%s %dx%d variant %d>" % (desc["math"], desc["tile"][0], desc["tile"][1], desc["variant"])
+    roof["kernel"] = desc["kernel"]
     roof["algorithmic_bytes_per_launch"] = shard_bytes
     roof["algorithmic_flops_per_launch"] = shard_flops
     roof["hbm"] = {"achieved": shard_bytes / launch_s * 1e-9, "peak": hbm_peak, "unit": "GB/s",
@@ -279,7 +281,7 @@ def run_ours(args):
                    "sharding": "output index %s cut into %d contiguous slabs, no communication" % (g.index, world)
                    if world > 1 else "none",
                    "l2": "inputs larger than L2 (%.0f MB touched per pass per GPU)" % (shard_bytes / 2 ** 20),
-                   "plan": {k: desc[k] for k in ("math", "tile", "variant", "tiles", "ksplit", "vec_c")}},
+                   "plan": {k: desc[k] for k in ("kernel", "math", "tile", "tiles", "ksplit", "vec_c")}},
         "roofline": roof,
         "e2e": {"value": e2e_value, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": slab_bytes,
                 "steps": e2e_steps, "call": "tc_execute_host (allocate, H2D of C, A, B from pinned host memory, "

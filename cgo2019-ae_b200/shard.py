@@ -88,7 +88,7 @@ class ShardGeometry:
                         for t, s in zip(tensors, self.strides)]
         self.full_sizes = [_prod(full[i] for i in t) for t in tensors]
         # The slab of C is one contiguous block iff the cut index is C's slowest (or C is not cut at all).
-        self.c_slab_contiguous = self.kind == "external" and p["out_idx"][-1] == index
+        self.c_slab_contiguous = self.kind == "external" and (p["out_idx"][-1] == index or world == 1)
         self.c_slab_elems = _prod(local[i] for i in p["out_idx"])
 
     def make_plan(self, dtype=F64, **kw):
