@@ -219,11 +219,12 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   // How the result reaches C (tc_options.c_path) and whether output tiles are prefetched into L2.
   // Defaults follow the B200 measurements: persistent kernels hand their tiles to the memory system as
   // bulk reduce-adds and need no prefetch; the one-CTA-per-tile kernels read-modify-write behind a prefetch.
-  const bool persistent = p->choice.math == TC_MATH_DMMA && p->choice.variant >= 2;
+  const bool persistent = tc_kernel_is_persistent(p->choice);
   const int c_path = p->opt.c_path;
-  p->args.c_mode = c_path > 0 ? c_path - 1 : (persistent ? 2 : 0);
+  p->args.c_mode = c_path > 0 ? c_path - 1 : ((persistent || p->choice.math == TC_MATH_SIMT) ? 2 : 0);
   p->args.c_stream = 0;
-  const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !(persistent && p->args.c_mode == 2));
+  const bool bulk_out = p->args.c_mode == 2 && (persistent || p->args.epi_run > 0);
+  const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !bulk_out);
   p->args.prefetch_dist = prefetch ? (uint32_t)resident_ctas(p->choice) : 0u;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));

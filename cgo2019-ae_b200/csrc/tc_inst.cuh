@@ -34,6 +34,8 @@ int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cu
   }
   if (mode == TC_INST_PREPARE) {
     TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, CF::SMEM_BYTES));
+    // as much of the unified L1/shared array as shared memory as the device allows: residency is bounded by it
+    TC_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     return TC_OK;
   }
   const unsigned grid = a->tiles_m * a->tiles_n * a->ksplit;
@@ -43,10 +45,10 @@ int run_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cu
   return TC_OK;
 }
 
-template <class CF>
-int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
-                   int* threads, int* smem_bytes) {
-  auto kern = tc_ws_dmma_kernel<CF>;
+template <class CF, class Kern>
+int run_persistent(Kern kern, const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream,
+                   int mode, int* threads, int* smem_bytes) {
+  using T = typename CF::T;
   if (mode == TC_INST_QUERY) {
     if (threads) *threads = CF::CTA_THREADS;
     if (smem_bytes) *smem_bytes = CF::SMEM_BYTES;
@@ -65,12 +67,17 @@ int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
   TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const unsigned tiles = a->tiles_m * a->tiles_n;
   const unsigned grid = (tiles + 1) / 2 < (unsigned)sms ? (tiles + 1) / 2 : (unsigned)sms;  // one persistent CTA per SM
-  kern<<<grid, CF::CTA_THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<double*>(C), static_cast<const double*>(X),
-                                                           static_cast<const double*>(Y));
+  kern<<<grid, CF::CTA_THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<T*>(C), static_cast<const T*>(X),
+                                                           static_cast<const T*>(Y));
   TC_CUDA_OK(cudaGetLastError());
   return TC_OK;
 }
 
+template <class CF>
+int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
+                   int* threads, int* smem_bytes) {
+  return run_persistent<CF>(tc_ws_dmma_kernel<CF>, a, C, X, Y, stream, mode, threads, smem_bytes);
+}
 }  // namespace tck
 
 #define TC_WS_CASE(MX, MY, BM, BN, STAGES) \

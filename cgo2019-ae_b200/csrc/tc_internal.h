@@ -77,6 +77,8 @@ struct TcKernelArgs {
   int32_t beta;      // 1: C is read and accumulated into; 0: C is overwritten
   double alpha;      // +1 or -1
   void* ws;          // K-slice partials: [ksplit][tiles][BN][BM]
+  int32_t epi_run;       // staged bulk epilogue: run length E0 in elements (0 = not available)
+  int32_t epi_n_span;    // ... F0 > 0: consecutive n are adjacent in the output within blocks of F0 (0: never)
   int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
@@ -135,7 +137,10 @@ int tc_kernels_prepare(const TcKernelChoice& c);  // opt-in shared memory attrib
 
 // Compiled kernels (registry built from tc_kernel_list.h).
 bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant);
-const char* tc_kernel_name(const TcKernelChoice& c);  // registry name, "?" if absent
+const char* tc_kernel_name(const TcKernelChoice& c);
+inline bool tc_kernel_is_persistent(const TcKernelChoice& c) {
+  return c.math == TC_MATH_DMMA && c.variant >= 2;
+}  // registry name, "?" if absent
 constexpr int TC_BK = 16;  // contraction step of every kernel
 
 #endif  // TC_INTERNAL_H_

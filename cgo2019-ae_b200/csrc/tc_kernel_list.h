@@ -23,6 +23,8 @@
   X(dfma_64x64, double, TC_MATH_SIMT, 64, 64, 1, 1, 4, 1, 0)               \
   X(ffma_128x128, float, TC_MATH_SIMT, 128, 128, 1, 1, 4, 2, 0)            \
   X(ffma_128x64, float, TC_MATH_SIMT, 128, 64, 1, 1, 4, 3, 0)              \
+  X(ffma_96x128, float, TC_MATH_SIMT, 96, 128, 1, 1, 4, 3, 0)              \
+  X(ffma_96x64, float, TC_MATH_SIMT, 96, 64, 1, 1, 4, 5, 0)                \
   X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)
 
 // Persistent warp-specialised fp64 kernels (tc_ws_kernel.cuh): two consumer groups of 2 x 2 warps,

@@ -120,7 +120,6 @@ __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const ty
                                                uint32_t k0, uint32_t kend, int tid) {
   constexpr int VPR = ROWS / CF::VW;            // vectors per k row
   constexpr int SLOTS = VPR * CF::BK;
-  static_assert(SLOTS % CF::THREADS == 0 || SLOTS < CF::THREADS, "loader shape");
   constexpr int PER = (SLOTS + CF::THREADS - 1) / CF::THREADS;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
@@ -143,8 +142,9 @@ __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const ty
 //   bits 0-15 element offset inside the stage image, 16-23 k, 24-31 external.
 template <class CF, int ROWS, int LD>
 struct ElemSlots {
-  static constexpr int PER = ROWS * CF::BK / CF::THREADS;  // elements per thread per stage
-  static_assert(ROWS * CF::BK % CF::THREADS == 0, "loader shape");
+  static constexpr int SLABS = ROWS * CF::BK / 32;                      // warp-wide groups of 32 elements
+  static constexpr int PER = (SLABS + CF::WARPS - 1) / CF::WARPS;      // slabs (= elements per thread) per stage
+  static constexpr uint32_t kNoSlot = 0xffffffffu;
   static_assert(CF::BK * LD < 65536 && ROWS <= 256, "slot packing");
   uint32_t slot[PER];
   // lg = log2(lanes walking k); BK and the warp size are powers of two, so the
@@ -159,7 +159,7 @@ struct ElemSlots {
       const int slab = warp * PER + j;
       const int kk = ((slab & ((1 << ks_bits) - 1)) << lg) + lk;
       const int el = ((slab >> ks_bits) << (5 - lg)) + le;
-      slot[j] = (uint32_t)(kk * LD + el) | ((uint32_t)kk << 16) | ((uint32_t)el << 24);
+      slot[j] = slab < SLABS ? ((uint32_t)(kk * LD + el) | ((uint32_t)kk << 16) | ((uint32_t)el << 24)) : kNoSlot;
     }
   }
   __device__ __forceinline__ void load(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
@@ -169,6 +169,7 @@ struct ElemSlots {
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
       const uint32_t sl = slot[j];
+      if (SLABS % CF::WARPS != 0 && sl == kNoSlot) continue;
       const int64_t eo = s_off[sl >> 24];
       const uint32_t kk = (sl >> 16) & 0xffu;
       const bool ok = eo >= 0 && k0 + kk < kend;
@@ -553,6 +554,65 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
         }
       }
       return;
+    }
+    // Staged bulk epilogue (c_mode 2, plans with args.epi_run = E0 > 0, tiles wholly inside the tensor).
+    // The tile is laid out in the freed stage buffers in the ORDER IT HAS IN THE OUTPUT and leaves as bulk
+    // asynchronous copies (reduce-add for `+=`/`-=`, plain copy for `=`): the SM never loads C.  The BM rows
+    // split into BM/E0 runs of E0 elements contiguous in C; staging index of (m, n) is
+    //   (m / E0) * (E0 * BN) + n * E0 + (m % E0).
+    // If consecutive n are adjacent in C inside blocks of F0 (args.epi_n_span: the output's second index
+    // belongs to the other operand), a run is one chunk per such block (at most two per tile), otherwise
+    // one chunk per (run, n).
+    if constexpr (STAGES * CF::STAGE_ELEMS >= BM * BN) {
+      const int E0 = p.epi_run;
+      if (p.c_mode == 2 && E0 > 0 && p.vec_c >= VW && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
+        __syncthreads();  // every warp is done with the stage buffers
+        T* ctile = Xs;
+        const int run_elems = E0 * BN;
+#pragma unroll
+        for (int q = 0; q < GR; ++q) {
+          const int m = q * TX * VW + tx * VW;
+          T* col = ctile + (m / E0) * run_elems + (m % E0);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int n = (j / VW) * TY * VW + ty * VW + (j % VW);
+            T r[VW];
+#pragma unroll
+            for (int e = 0; e < VW; ++e) r[e] = alpha * acc[j][q * VW + e];
+            *reinterpret_cast<V*>(col + n * E0) = *reinterpret_cast<const V*>(r);
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncthreads();
+        const int runs = BM / E0;
+        // n segments: [0, nb) and [nb, BN) when adjacency holds within blocks of F0, else single n's
+        const int F0 = p.epi_n_span;
+        int nb = BN, nseg = BN;
+        if (F0 > 0) {
+          const int left = F0 - (int)(n0 % (uint32_t)F0);
+          nb = left < BN ? left : BN;
+          nseg = nb < BN ? 2 : 1;
+        }
+        for (int c = tid; c < runs * nseg; c += CF::THREADS) {
+          const int r = c / nseg, sgi = c % nseg;
+          const int n = F0 > 0 ? (sgi == 0 ? 0 : nb) : sgi;
+          const int len = F0 > 0 ? (sgi == 0 ? nb : BN - nb) : 1;
+          T* dstg = C + offc_m[r * E0] + offc_n[n];
+          const uint32_t src = smem_u32(ctile + r * run_elems + n * E0);
+          const uint32_t bytes = (uint32_t)(E0 * len) * CF::ES;
+          if (p.beta) {
+            if constexpr (CF::ES == 4)
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+            else
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+          } else {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+          }
+        }
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // shared memory is released at exit
+        return;
+      }
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {

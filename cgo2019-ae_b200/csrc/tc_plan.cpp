@@ -255,6 +255,12 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       else { bm = 128; bn = 64; }
       variant = 2;
     }
+    if (c.math == TC_MATH_SIMT && c.dtype == TC_F32) {
+      // fp32: 96 rows instead of 128 when that makes the tile a whole number of the output's contiguous
+      // runs (e.g. a fastest output index of extent 24), which the bulk epilogue wants.
+      const int64_t e0 = (a.M.n > 0 && a.M.s_out[0] == 1) ? a.M.extent[0] : 0;
+      if (e0 > 0 && e0 % 128 != 0 && 128 % e0 != 0 && (96 % e0 == 0 || e0 % 96 == 0)) bm = 96;
+    }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
     if (ctas < 2 * 148) { bm = 64; bn = 64; variant = 0; }
     if (p->opt.variant > 0) variant = p->opt.variant - 1;
@@ -273,7 +279,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // K split: only when the tile count cannot fill the GPU and K is long.
   int64_t ksplit = 1;
   const int64_t ksteps = (kf + bk - 1) / bk;
-  const bool persistent = c.math == TC_MATH_DMMA && c.variant >= 2;  // these kernels do not split K
+  const bool persistent = tc_kernel_is_persistent(c);  // these kernels do not split K
   if (persistent) ksplit = 1;
   else if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
   else if (p->opt.split_k == 0 && tiles * 2 <= 148 && ksteps >= 16)
@@ -285,6 +291,24 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   if (tiles * ksplit >= (int64_t(1) << 31)) { *why = "too many tiles"; return TC_ERR_UNSUPPORTED; }
   p->ws_bytes = ksplit > 1 ? (size_t)(ksplit * tiles * bm * bn) * es : 0;
   p->launches = ksplit > 1 ? 2 : 1;
+
+  // Staged bulk epilogue of the vector-pipe kernels: the tile's rows split into runs of E0 elements
+  // contiguous in the output; if the output's next index belongs to the other operand (its stride equals
+  // the extent of the fastest one), consecutive n are adjacent too within blocks of that index's extent.
+  a.epi_run = 0;
+  a.epi_n_span = 0;
+  if (c.math == TC_MATH_SIMT && ksplit == 1 && a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= V) {
+    const int64_t e = a.M.extent[0];
+    int64_t e0 = e % bm == 0 ? bm : (bm % e == 0 ? e : std::gcd<int64_t>(bm, e));
+    if (e0 % V == 0 && e0 >= V) {
+      const bool n_adjacent = e0 == e && a.N.n > 0 && a.N.s_out[0] == e && (int64_t)a.N.extent[0] >= bn;
+      // bulk copies pay off from a few hundred bytes per chunk; shorter runs keep the read-modify-write
+      if (n_adjacent || e0 * es >= 256) {
+        a.epi_run = (int32_t)e0;
+        if (n_adjacent) a.epi_n_span = (int32_t)a.N.extent[0];
+      }
+    }
+  }
 
   double prod = 1.0;
   for (int64_t x : p->idx_extent) prod *= (double)x;
@@ -317,7 +341,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
-      << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"beta\":" << a.beta
+      << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"epi_run\":" << a.epi_run << ",\"epi_n_span\":" << a.epi_n_span << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches
       << ",\"flops\":" << p.flops << ",\"bytes\":" << p.bytes;
   }

@@ -55,7 +55,9 @@ def test_tile_choices(pkg):
     assert d[1]["kernel"] == "dmma_ws_64x96" and d[1]["tiles"] == [13824, 1]   # N = 96 is exactly one tile wide
     assert d[2]["kernel"] == "dmma_ws_128x64" and d[2]["tiles"] == [32, 64]
     assert d[4]["kernel"] == "dmma_ws_128x64" and d[4]["tiles"] == [500, 1000]
-    assert d[3]["math"] == "ffma" and d[3]["kernel"] == "ffma_128x128"
+    # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
+    assert d[3]["math"] == "ffma" and d[3]["kernel"] == "ffma_96x128"
+    assert d[3]["epi_run"] == 24 and d[3]["epi_n_span"] == 576
     assert d[0]["kernel"] == "dmma_64x64_w4"                                    # tiny problem: one CTA per tile
     # operands whose fastest index is contracted are staged contraction-major with 16-byte copies
     assert d[4]["kvec_x"] and d[4]["vec_y"] and not d[4]["vec_x"]
