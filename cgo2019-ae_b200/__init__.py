@@ -48,6 +48,9 @@ _SIGNATURES = {
                                       ctypes.POINTER(ctypes.c_void_p)]),
     "tc_plan_set_extents": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
                                            ctypes.POINTER(ctypes.c_int64)]),
+    "tc_plan_set_extents_ordered": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
+    "tc_sd_t_d2_fusion": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tc_plan_set_strides": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                            ctypes.POINTER(ctypes.c_int64)]),
     "tc_plan_commit": (ctypes.c_int, [ctypes.c_void_p]),
@@ -223,6 +226,12 @@ class Plan:
             self.close()
         except Exception:
             pass
+
+
+def sd_t_d2_fusion(expr, sizes, t3, t2, v2, dtype=F64):
+    """The reference's generated entry for one expression: sizes in output-then-contraction order, numpy host arrays."""
+    arr = (ctypes.c_int * len(sizes))(*[int(x) for x in sizes])
+    _check(lib().tc_sd_t_d2_fusion(expr.encode(), dtype, len(sizes), arr, _ptr(t3), _ptr(t2), _ptr(v2)), "tc_sd_t_d2_fusion")
 
 
 def fill_uniform(t, seed, tensor_id, first_index=0, stream=None):

@@ -195,6 +195,16 @@ extern "C" int tc_plan_set_extents(tc_plan* p, int n, const char* const* names, 
   return TC_OK;
 }
 
+extern "C" int tc_plan_set_extents_ordered(tc_plan* p, int n, const int64_t* extents) {
+  if (!p || n < 0 || (n > 0 && !extents)) return TC_ERR_INVALID_ARG;
+  if (p->committed) return TC_ERR_STATE;
+  if ((size_t)n != p->idx_names.size()) return TC_ERR_INVALID_ARG;
+  for (int i = 0; i < n; ++i)
+    if (extents[i] <= 0) return TC_ERR_EXTENT;
+  p->idx_extent.assign(extents, extents + n);
+  return TC_OK;
+}
+
 extern "C" int tc_plan_set_strides(tc_plan* p, int tensor, int n, const int64_t* strides) {
   if (!p || tensor < 0 || tensor > 2 || n < 0 || (n > 0 && !strides)) return TC_ERR_INVALID_ARG;
   if (p->committed) return TC_ERR_STATE;
@@ -412,6 +422,36 @@ extern "C" int tc_execute_host(tc_plan* p, void* C, const void* A, const void* B
 #undef TC_HOST_OK
   cleanup();
   return TC_OK;
+}
+
+// ------------------------------------------- drop-in for sd_t_d2_fusion_ ----
+#include <map>
+#include <mutex>
+extern "C" int tc_sd_t_d2_fusion(const char* expr, int dtype, int n_sizes, const int* sizes, void* t3, const void* t2,
+                                 const void* v2) {
+  if (!expr || !sizes || !t3 || !t2 || !v2 || n_sizes < 0) return TC_ERR_INVALID_ARG;
+  static std::mutex mu;
+  static std::map<std::string, tc_plan*> cache;  // plans live for the process, like the generated code's statics
+  std::string key = std::string(expr) + "|" + std::to_string(dtype);
+  for (int i = 0; i < n_sizes; ++i) key += "," + std::to_string(sizes[i]);
+  tc_plan* plan = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) plan = it->second;
+  }
+  if (!plan) {
+    int st = tc_plan_create(expr, dtype, nullptr, &plan);
+    if (st != TC_OK) return st;
+    std::vector<int64_t> ext(sizes, sizes + n_sizes);
+    st = tc_plan_set_extents_ordered(plan, n_sizes, ext.data());
+    if (st == TC_OK) st = tc_plan_commit(plan);
+    if (st != TC_OK) { tc_plan_destroy(plan); return st; }
+    std::lock_guard<std::mutex> lock(mu);
+    auto ins = cache.emplace(key, plan);
+    if (!ins.second) { tc_plan_destroy(plan); plan = ins.first->second; }
+  }
+  return tc_execute_host(plan, t3, t2, v2);
 }
 
 // -------------------------------------------------------- seeded inputs ----

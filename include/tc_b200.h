@@ -84,6 +84,11 @@ int tc_expr_describe(const char* expr, char* buf, size_t cap);
 int tc_plan_create(const char* expr, int dtype, const tc_options* options, tc_plan** out);
 int tc_plan_set_extents(tc_plan* plan, int n, const char* const* index_names, const int64_t* extents);
 
+/* Extents by position: output indices in written order, then the contraction indices in sum(...)
+ * order -- the order of the size arguments of the reference entry sd_t_d2_fusion_
+ * (cogent/src/codes/kernels/tc_interface.py:1451-1516). */
+int tc_plan_set_extents_ordered(tc_plan* plan, int n, const int64_t* extents);
+
 /* Optional strided views.  tensor: 0 = output, 1 = left input, 2 = right input.
  * strides[i] is the element stride of the tensor's i-th index as written in the
  * expression.  Default: compact column-major from the current extents.  Used to
@@ -144,6 +149,14 @@ int tc_execute_noalloc(tc_plan* plan, void* C, const void* A, const void* B, voi
  * kernel (cogent/src/codes/others/tc_pre_CUDA_Malloc.py:6-47,
  * cogent/src/codes/kernels/tc_interface.py:1368-1388). */
 int tc_execute_host(tc_plan* plan, void* C, const void* A, const void* B);
+
+/* ---- drop-in for the reference's generated entry ------------------------------------
+ * What the generated sd_t_d2_fusion_ does for ONE expression (cogent/src/codes/kernels/tc_interface.py:
+ * 1444-1598 -> 10-101): sizes in the order above, host pointers t3 (in/out), t2, v2; allocate, copy in,
+ * contract, copy t3 back.  Plans are cached per (expression, dtype, sizes).  include/tc_b200_shim.h
+ * wraps this into a symbol with the reference's exact name and argument list. */
+int tc_sd_t_d2_fusion(const char* expr, int dtype, int n_sizes, const int* sizes, void* t3, const void* t2,
+                      const void* v2);
 
 /* ---- diagnostics ------------------------------------------------------------ */
 const char* tc_status_string(int status);
