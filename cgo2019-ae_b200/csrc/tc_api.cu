@@ -231,7 +231,7 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   // bulk reduce-adds and need no prefetch; the one-CTA-per-tile kernels read-modify-write behind a prefetch.
   const bool persistent = tc_kernel_is_persistent(p->choice);
   const int c_path = p->opt.c_path;
-  p->args.c_mode = c_path > 0 ? c_path - 1 : ((persistent || p->choice.math == TC_MATH_SIMT) ? 2 : 0);
+  p->args.c_mode = c_path > 0 ? c_path - 1 : ((persistent || p->choice.math != TC_MATH_DMMA) ? 2 : 0);
   p->args.c_stream = 0;
   const bool bulk_out = p->args.c_mode == 2 && (persistent || p->args.epi_run > 0);
   const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !bulk_out);

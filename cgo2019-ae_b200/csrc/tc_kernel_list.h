@@ -5,7 +5,7 @@
 //
 //   X(name, T, MATH, BM, BN, WARPS_M, WARPS_N, STAGES, MIN_CTAS_PER_SM, VARIANT)
 //
-// DMMA: WARPS_M x WARPS_N warps, warp tile (BM/WARPS_M) x (BN/WARPS_N), both
+// DMMA / TF32X3: WARPS_M x WARPS_N warps, warp tile (BM/WARPS_M) x (BN/WARPS_N), both
 // multiples of 16.  SIMT: (BM/8) x (BN/8) threads with 8 x 8 outputs each
 // (WARPS_* unused).  VARIANT distinguishes warp layouts of the same tile.
 #ifndef TC_KERNEL_LIST_H_
@@ -25,7 +25,10 @@
   X(ffma_128x64, float, TC_MATH_SIMT, 128, 64, 1, 1, 4, 3, 0)              \
   X(ffma_96x128, float, TC_MATH_SIMT, 96, 128, 1, 1, 4, 3, 0)              \
   X(ffma_96x64, float, TC_MATH_SIMT, 96, 64, 1, 1, 4, 5, 0)                \
-  X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)
+  X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)               \
+  X(tf32_128x128, float, TC_MATH_TF32X3, 128, 128, 2, 4, 4, 2, 0)          \
+  X(tf32_96x128, float, TC_MATH_TF32X3, 96, 128, 2, 4, 4, 2, 0)            \
+  X(tf32_64x64, float, TC_MATH_TF32X3, 64, 64, 2, 2, 4, 4, 0)
 
 // Persistent warp-specialised fp64 kernels (tc_ws_kernel.cuh): two consumer groups of 2 x 2 warps,
 // each on its own BM x BN tile, plus four producer warps.

@@ -52,6 +52,20 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// D(16x8) += A(16x8) * B(8x8), TF32 inputs, fp32 accumulate.
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// v = hi + lo with hi, lo representable in TF32 (10-bit mantissa): hi*hi' + hi*lo' + lo*hi' recovers the
+// fp32 product to about 2^-21 relative.
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(hi) : "f"(v));
+  const float r = v - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(lo) : "f"(r));
+}
+
 __device__ __forceinline__ void dmma884(double& d0, double& d1, double a, double b) {
   asm("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};\n"
       : "+d"(d0), "+d"(d1)
@@ -75,11 +89,13 @@ struct Cfg {
   static constexpr int VW = 16 / ES;  // elements per 16 bytes
   // DMMA: WARPS_M x WARPS_N warps, each a (BM/WARPS_M) x (BN/WARPS_N) tile.
   // SIMT: (BM/8) x (BN/8) threads, each an 8 x 8 tile.
-  static constexpr int THREADS = MATH == TC_MATH_DMMA ? 32 * WARPS_M_ * WARPS_N_ : (BM / 8) * (BN / 8);
+  static constexpr int THREADS = MATH == TC_MATH_SIMT ? (BM / 8) * (BN / 8) : 32 * WARPS_M_ * WARPS_N_;
   static constexpr int WARPS = THREADS / 32;
   static constexpr int WM = BM / WARPS_M_, WN = BN / WARPS_N_;
   static constexpr int WARPS_M = WARPS_M_, WARPS_N = WARPS_N_;
-  static constexpr int LDX = BM + 4, LDY = BN + 4;
+  // row pitch: +4 words keeps the fp64 / vector-pipe reads conflict-free, the TF32 fragment reads want +8
+  static constexpr int PAD = MATH == TC_MATH_TF32X3 ? 8 : 4;
+  static constexpr int LDX = BM + PAD, LDY = BN + PAD;
   // Contraction offsets of the stages in flight live in a shared ring (filled by
   // cp.async one pipeline depth ahead), so the loaders never wait on global memory.
   static constexpr int KRING = 2 * STAGES - 2;
@@ -178,6 +194,43 @@ struct ElemSlots {
     }
   }
 };
+
+// Issues the bulk asynchronous copies of a staged output tile (layout: see the staged epilogue) and
+// waits until they have read shared memory.  Chunks: per run of E0 rows either one per n, or -- when
+// consecutive n are adjacent in the output inside blocks of F0 -- one per such block (at most two per tile).
+template <class CF>
+__device__ __forceinline__ void bulk_out_tile(const TcKernelArgs& p, typename CF::T* __restrict__ C,
+                                              const typename CF::T* ctile, const int64_t* offc_m,
+                                              const int64_t* offc_n, uint32_t n0, int tid) {
+  using T = typename CF::T;
+  constexpr int BM = CF::BM, BN = CF::BN;
+  const int E0 = p.epi_run, run_elems = E0 * BN, runs = BM / E0;
+  const int F0 = p.epi_n_span;
+  int nb = BN, nseg = BN;
+  if (F0 > 0) {
+    const int left = F0 - (int)(n0 % (uint32_t)F0);
+    nb = left < BN ? left : BN;
+    nseg = nb < BN ? 2 : 1;
+  }
+  for (int c = tid; c < runs * nseg; c += CF::THREADS) {
+    const int r = c / nseg, sgi = c % nseg;
+    const int n = F0 > 0 ? (sgi == 0 ? 0 : nb) : sgi;
+    const int len = F0 > 0 ? (sgi == 0 ? nb : BN - nb) : 1;
+    T* dstg = C + offc_m[r * E0] + offc_n[n];
+    const uint32_t src = smem_u32(ctile + r * run_elems + n * E0);
+    const uint32_t bytes = (uint32_t)(E0 * len) * CF::ES;
+    if (p.beta) {
+      if constexpr (CF::ES == 4)
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+      else
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+    } else {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
+    }
+  }
+  asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // shared memory is released at exit
+}
 
 // --------------------------------------------------------------- kernel ----
 template <class CF>
@@ -467,6 +520,145 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
           }
       }
     }
+  } else if constexpr (CF::MATH == TC_MATH_TF32X3) {
+    // ---------------- fp32 as three TF32 tensor-core products ----------------
+    // mma.sync m16n8k8: D rows (16) = n, D columns (8) = m; column c of m-block 2i+h is tile element
+    // 16i + 2c + h, so one 8-byte shared load feeds two blocks and a thread's D values of a block pair are
+    // four consecutive m (16 bytes of the output).  Every operand value is split v = hi + lo (both TF32)
+    // and the product is hi*hi + hi*lo + lo*hi accumulated in fp32.
+    constexpr int WM = CF::WM, WN = CF::WN;
+    constexpr int MB2 = WM / 16, NB = WN / 16;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int wm0 = (warp % CF::WARPS_M) * WM, wn0 = (warp / CF::WARPS_M) * WN;
+    const float alpha = (float)p.alpha;
+    float acc[NB][2 * MB2][4];
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int i = 0; i < 2 * MB2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][i][e] = 0.f;
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    prefetch_next();
+
+    for (int it = 0; it < nk; ++it) {
+      cp_async_wait<STAGES - 2>();
+      __syncthreads();
+      issue_koff(it);
+      issue(it + STAGES - 1);
+      const int st = it % STAGES;
+      const float* xs = Xs + st * BK * LDX + wm0 + 2 * g;
+      const float* ys = Ys + st * BK * LDY + wn0 + g;
+      const int kleft = (int)(kend - (kbeg + it * BK));
+      const int nk8 = kleft >= BK ? BK / 8 : (kleft + 7) / 8;
+#pragma unroll
+      for (int k8 = 0; k8 < BK / 8; ++k8) {
+        if (k8 < nk8) {
+          const int k = k8 * 8 + t;
+          uint32_t ahi[NB][4], alo[NB][4];
+#pragma unroll
+          for (int j = 0; j < NB; ++j) {
+            split_tf32(ys[k * LDY + 16 * j], ahi[j][0], alo[j][0]);
+            split_tf32(ys[k * LDY + 16 * j + 8], ahi[j][1], alo[j][1]);
+            split_tf32(ys[(k + 4) * LDY + 16 * j], ahi[j][2], alo[j][2]);
+            split_tf32(ys[(k + 4) * LDY + 16 * j + 8], ahi[j][3], alo[j][3]);
+          }
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            const float2 x0 = *reinterpret_cast<const float2*>(xs + k * LDX + 16 * i);
+            const float2 x1 = *reinterpret_cast<const float2*>(xs + (k + 4) * LDX + 16 * i);
+            uint32_t bhi[2][2], blo[2][2];
+            split_tf32(x0.x, bhi[0][0], blo[0][0]);
+            split_tf32(x1.x, bhi[0][1], blo[0][1]);
+            split_tf32(x0.y, bhi[1][0], blo[1][0]);
+            split_tf32(x1.y, bhi[1][1], blo[1][1]);
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int j = 0; j < NB; ++j) {
+                mma_tf32(acc[j][2 * i + h], alo[j], bhi[h]);
+                mma_tf32(acc[j][2 * i + h], ahi[j], blo[h]);
+                mma_tf32(acc[j][2 * i + h], ahi[j], bhi[h]);
+              }
+          }
+        }
+      }
+    }
+    cp_async_wait<0>();
+
+    // Thread holds, for n = wn0 + 16j + g + 8r (r = 0, 1) and block pair i, the four
+    // m = wm0 + 16i + 4t + q:  acc[j][2i + (q & 1)][2r + (q >> 1)].
+    if (p.ksplit > 1) {
+      float* ws = reinterpret_cast<float*>(p.ws) +
+                  ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
+#pragma unroll
+      for (int j = 0; j < NB; ++j)
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int i = 0; i < MB2; ++i) {
+            const int nl = wn0 + 16 * j + g + 8 * r, ml = wm0 + 16 * i + 4 * t;
+            *reinterpret_cast<float4*>(ws + (size_t)nl * BM + ml) =
+                make_float4(acc[j][2 * i][2 * r], acc[j][2 * i + 1][2 * r], acc[j][2 * i][2 * r + 1], acc[j][2 * i + 1][2 * r + 1]);
+          }
+      return;
+    }
+    if constexpr (STAGES * CF::STAGE_ELEMS >= BM * BN) {
+      const int E0 = p.epi_run;
+      if (p.c_mode == 2 && E0 > 0 && p.vec_c >= 4 && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
+        __syncthreads();
+        float* ctile = Xs;
+        const int run_elems = E0 * BN;
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          const int m = wm0 + 16 * i + 4 * t;
+          float* col = ctile + (m / E0) * run_elems + (m % E0);
+#pragma unroll
+          for (int j = 0; j < NB; ++j)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const int n = wn0 + 16 * j + g + 8 * r;
+              *reinterpret_cast<float4*>(col + n * E0) =
+                  make_float4(alpha * acc[j][2 * i][2 * r], alpha * acc[j][2 * i + 1][2 * r],
+                              alpha * acc[j][2 * i][2 * r + 1], alpha * acc[j][2 * i + 1][2 * r + 1]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        __syncthreads();
+        bulk_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
+        return;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int64_t cn = offc_n[wn0 + 16 * j + g + 8 * r];
+        if (cn < 0) continue;
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          if (p.vec_c == 4) {
+            const int64_t co = offc_m[wm0 + 16 * i + 4 * t];
+            if (co < 0) continue;
+            float4* dst = reinterpret_cast<float4*>(C + cn + co);
+            float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (rmw) c = *dst;
+            *dst = make_float4(fmaf(alpha, acc[j][2 * i][2 * r], c.x), fmaf(alpha, acc[j][2 * i + 1][2 * r], c.y),
+                               fmaf(alpha, acc[j][2 * i][2 * r + 1], c.z), fmaf(alpha, acc[j][2 * i + 1][2 * r + 1], c.w));
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
+              if (co < 0) continue;
+              const float c = rmw ? C[cn + co] : 0.f;
+              C[cn + co] = fmaf(alpha, acc[j][2 * i + (q & 1)][2 * r + (q >> 1)], c);
+            }
+          }
+        }
+      }
   } else {
     // ---------------- vector pipe (FFMA / DFMA) ----------------
     // (BM/8) x (BN/8) threads, 8 x 8 outputs each, as groups of VW contiguous
@@ -584,33 +776,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         __syncthreads();
-        const int runs = BM / E0;
-        // n segments: [0, nb) and [nb, BN) when adjacency holds within blocks of F0, else single n's
-        const int F0 = p.epi_n_span;
-        int nb = BN, nseg = BN;
-        if (F0 > 0) {
-          const int left = F0 - (int)(n0 % (uint32_t)F0);
-          nb = left < BN ? left : BN;
-          nseg = nb < BN ? 2 : 1;
-        }
-        for (int c = tid; c < runs * nseg; c += CF::THREADS) {
-          const int r = c / nseg, sgi = c % nseg;
-          const int n = F0 > 0 ? (sgi == 0 ? 0 : nb) : sgi;
-          const int len = F0 > 0 ? (sgi == 0 ? nb : BN - nb) : 1;
-          T* dstg = C + offc_m[r * E0] + offc_n[n];
-          const uint32_t src = smem_u32(ctile + r * run_elems + n * E0);
-          const uint32_t bytes = (uint32_t)(E0 * len) * CF::ES;
-          if (p.beta) {
-            if constexpr (CF::ES == 4)
-              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
-            else
-              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
-          } else {
-            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dstg), "r"(src), "r"(bytes) : "memory");
-          }
-        }
-        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // shared memory is released at exit
+        bulk_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
         return;
       }
     }

@@ -196,8 +196,9 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     c.math = path == TC_PATH_DFMA ? TC_MATH_SIMT : TC_MATH_DMMA;
   } else {
     if (path == TC_PATH_DMMA || path == TC_PATH_DFMA) { *why = "fp64 path requested for an fp32 plan"; return TC_ERR_INVALID_ARG; }
-    if (path == TC_PATH_3XTF32) { *why = "the 3xTF32 path is not built into this library"; return TC_ERR_UNSUPPORTED; }
-    c.math = TC_MATH_SIMT;
+    // AUTO: three TF32 tensor-core products per fp32 product measured faster than FFMA on B200 (the
+    // vector-pipe kernel is issue-bound on short contractions) at the same observed error (~3e-7).
+    c.math = path == TC_PATH_FFMA ? TC_MATH_SIMT : TC_MATH_TF32X3;
   }
 
   // Loader per operand.
@@ -255,7 +256,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       else { bm = 128; bn = 64; }
       variant = 2;
     }
-    if (c.math == TC_MATH_SIMT && c.dtype == TC_F32) {
+    if (c.math != TC_MATH_DMMA && c.dtype == TC_F32) {
       // fp32: 96 rows instead of 128 when that makes the tile a whole number of the output's contiguous
       // runs (e.g. a fastest output index of extent 24), which the bulk epilogue wants.
       const int64_t e0 = (a.M.n > 0 && a.M.s_out[0] == 1) ? a.M.extent[0] : 0;
@@ -297,7 +298,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // the extent of the fastest one), consecutive n are adjacent too within blocks of that index's extent.
   a.epi_run = 0;
   a.epi_n_span = 0;
-  if (c.math == TC_MATH_SIMT && ksplit == 1 && a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= V) {
+  if (c.math != TC_MATH_DMMA && ksplit == 1 && a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= V) {
     const int64_t e = a.M.extent[0];
     int64_t e0 = e % bm == 0 ? bm : (bm % e == 0 ? e : std::gcd<int64_t>(bm, e));
     if (e0 % V == 0 && e0 >= V) {
@@ -335,7 +336,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     o << ",\"N\":";
     dims(a.N);
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
-      << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
+      << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")

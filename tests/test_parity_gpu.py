@@ -75,10 +75,17 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
         expr = expr.replace("sum(l,8)", "sum(l,24)")
     if idx == 4:
         expr = expr.replace("sum(g,10)", "sum(g,40)")
-    tiles = [None, (128, 128), (64, 64)] + ([(128, 64), (128, 96), (64, 96)] if dt == "float64" else [(128, 64)])
+    tiles = [None, (128, 128), (64, 64)] + ([(128, 64), (128, 96), (64, 96)] if dt == "float64" else [(96, 128)])
     for tile in tiles:
         err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, **({"tile": tile} if tile else {}))
         assert err <= TOL[dt], (expr, tile, err)
+    if dt == "float32":  # both fp32 arithmetic paths, both ways of reaching the output
+        for path in (pkg.PATH_FFMA, pkg.PATH_3XTF32):
+            for kw in ({}, {"tile": (96, 128), "c_path": 1}, {"tile": (128, 128), "c_path": 3}, {"tile": (64, 64), "split_k": 2}):
+                err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, path=path, **kw)
+                assert err <= TOL[dt], (expr, path, kw, err)
+        err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, path=pkg.PATH_FFMA, tile=(128, 64))
+        assert err <= TOL[dt]
     if dt == "float64":
         for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 128), "variant": 2}, {"tile": (128, 64), "variant": 2},
                    {"tile": (64, 64), "l2_prefetch": 1}, {"tile": (64, 64), "c_path": 2},
@@ -165,11 +172,11 @@ def test_config5_one_eighth_slabs(pkg, orc, torch_cuda):
 
 
 # ------------------------------------------------------- random expressions ----
-@pytest.mark.parametrize("path", ["dmma", "dfma", "ffma", "persistent", "persistent_bulk"])
+@pytest.mark.parametrize("path", ["dmma", "dfma", "ffma", "tf32x3", "persistent", "persistent_bulk"])
 def test_random_contractions(pkg, orc, torch_cuda, path):
-    rng = random.Random({"dmma": 11, "dfma": 12, "ffma": 13, "persistent": 14, "persistent_bulk": 15}[path])
-    dt = "float32" if path == "ffma" else "float64"
-    kw = {"path": pkg.PATH_DFMA} if path == "dfma" else {}
+    rng = random.Random({"dmma": 11, "dfma": 12, "ffma": 13, "tf32x3": 16, "persistent": 14, "persistent_bulk": 15}[path])
+    dt = "float32" if path in ("ffma", "tf32x3") else "float64"
+    kw = {"path": {"dfma": pkg.PATH_DFMA, "ffma": pkg.PATH_FFMA, "tf32x3": pkg.PATH_3XTF32}.get(path, pkg.PATH_AUTO)}
     if path.startswith("persistent"):  # small problems would not pick the persistent kernel by themselves
         kw = {"tile": (128, 64), "variant": 3, "c_path": 3 if path.endswith("bulk") else 1}
     for n in range(40):
@@ -196,6 +203,8 @@ def test_edge_shapes(pkg, orc, torch_cuda, expr):
     for dt in ("float64", "float32"):
         err, d = _run(pkg, orc, torch_cuda, expr, dt, 42)
         assert err <= TOL[dt], (expr, dt, err, d)
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 42, path=pkg.PATH_FFMA)
+    assert err <= TOL["float32"], (expr, err, d)
     for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "c_path": 1}):
         err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, **kw)
         assert err <= TOL["float64"], (expr, kw, err)

@@ -56,7 +56,9 @@ def test_tile_choices(pkg):
     assert d[2]["kernel"] == "dmma_ws_128x64" and d[2]["tiles"] == [32, 64]
     assert d[4]["kernel"] == "dmma_ws_128x64" and d[4]["tiles"] == [500, 1000]
     # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
-    assert d[3]["math"] == "ffma" and d[3]["kernel"] == "ffma_96x128"
+    assert d[3]["math"] == "tf32x3" and d[3]["kernel"] == "tf32_96x128"
+    ffma = _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_FFMA).describe()
+    assert ffma["math"] == "ffma" and ffma["kernel"] == "ffma_96x128"
     assert d[3]["epi_run"] == 24 and d[3]["epi_n_span"] == 576
     assert d[0]["kernel"] == "dmma_64x64_w4"                                    # tiny problem: one CTA per tile
     # operands whose fastest index is contracted are staged contraction-major with 16-byte copies
@@ -93,8 +95,8 @@ def test_extent_override_and_errors(pkg):
         _plan(pkg, CONFIGS[0][0], path=pkg.PATH_FFMA).describe()
     assert e.value.status == 2
     with pytest.raises(pkg.TcError) as e:
-        _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_3XTF32).describe()
-    assert e.value.status == 3
+        _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_DMMA).describe()
+    assert e.value.status == 2
 
 
 def test_strided_views(pkg):
