@@ -89,9 +89,12 @@ struct WsCfg {
   // Epilogue staging for the bulk reduce: per consumer warp 8 rows of WM outputs, pitch WM+2
   // (16-byte aligned rows, conflict-free 16-byte writes).
   static constexpr int CPITCH = WM + 2;
-  static constexpr int CSTAGE_ELEMS = 8 * CPITCH;
-  static constexpr int SMEM_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8 +
-                                    GROUPS * 4 * CSTAGE_ELEMS * 8;
+  static constexpr int CBATCH_ELEMS = 8 * CPITCH;
+  static constexpr int BASE_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8;
+  // two staging batches per warp (the copies of one batch drain while the next is written) where they fit
+  static constexpr int CBUF = BASE_BYTES + GROUPS * 4 * 2 * CBATCH_ELEMS * 8 <= 232448 - 1024 ? 2 : 1;
+  static constexpr int CSTAGE_ELEMS = CBUF * CBATCH_ELEMS;
+  static constexpr int SMEM_BYTES = BASE_BYTES + GROUPS * 4 * CSTAGE_ELEMS * 8;
   static constexpr int PRODUCER_REGS = 56, CONSUMER_REGS = 224;
 };
 
@@ -392,12 +395,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       const int64_t c_lo = offc_m[wm0];
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
-        // the previous batch must have been read out of the staging rows
-        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        // the batch that last used this staging buffer must have been read out of it
+        asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
         __syncwarp();
+        double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;
 #pragma unroll
         for (int i = 0; i < MB2; ++i) {
-          double2* dst = reinterpret_cast<double2*>(cst + g * CF::CPITCH + 16 * i + 4 * t);
+          double2* dst = reinterpret_cast<double2*>(cbuf + g * CF::CPITCH + 16 * i + 4 * t);
           dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
           dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
         }
@@ -406,7 +410,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         if (lane < 8) {
           const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * lane + (nb & 1)];
           if (cn >= 0) {
-            const uint32_t src = smem_u32(cst + lane * CF::CPITCH);
+            const uint32_t src = smem_u32(cbuf + lane * CF::CPITCH);
             double* dstg = C + cn + c_lo;
             if (accumulate)
               asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f64 [%0], [%1], %2;\n" ::"l"(dstg),
