@@ -284,8 +284,8 @@ def run_ours(args):
                    "plan": {k: desc[k] for k in ("kernel", "math", "tile", "tiles", "ksplit", "vec_c")}},
         "roofline": roof,
         "e2e": {"value": e2e_value, "unit": "GFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": slab_bytes,
-                "steps": e2e_steps, "call": "tc_execute_host (allocate, H2D of C, A, B from pinned host memory, "
-                                            "kernel, D2H of C, free)"},
+                "steps": e2e_steps, "call": "tc_execute_host on pinned host buffers (H2D of C, A, B, kernels, D2H of C; "
+                                            "slabs of the slowest output index pipelined over two streams)"},
         "gpu_launches": sh.plan.launches * args.steps,
         "clocks": clocks,
     }

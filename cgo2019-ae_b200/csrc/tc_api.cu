@@ -251,11 +251,15 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   return TC_OK;
 }
 
+struct TcHostPipe;
+static void host_pipe_destroy(TcHostPipe* h);
+
 extern "C" void tc_plan_destroy(tc_plan* p) {
   if (!p) return;
   if (p->d_koff) cudaFree(p->d_koff);
   if (p->d_ws) cudaFree(p->d_ws);
   if (p->d_status) cudaFree(p->d_status);
+  host_pipe_destroy(p->host);
   delete p;
 }
 
@@ -384,43 +388,162 @@ extern "C" int tc_execute_noalloc(tc_plan* p, void* C, const void* A, const void
   return execute_impl(p, C, A, B, ws, (size_t)TC_NOALLOC_MAX_WORKSPACE_BYTES, stream);
 }
 
+// Host-pointer path.  The reference's wrapper copies everything in, runs, copies the output back
+// (cogent/src/codes/others/tc_pre_CUDA_Malloc.py:6-47, tc_interface.py:1368-1388).  Here the output's
+// slowest index is cut into slabs and the slabs are pipelined over two streams: while slab i computes, slab
+// i+1 is on its way in and slab i-1 on its way out, so a pass costs about max(bytes in, bytes out) over
+// PCIe instead of their sum.  Inputs that carry the cut index as THEIR slowest index travel slab by slab
+// too; the others go first, whole.  Device buffers, streams and the slab plans are created on the first
+// call and kept with the plan.
+struct TcHostPipe {
+  void *dC = nullptr, *dA = nullptr, *dB = nullptr;
+  cudaStream_t stream[2] = {nullptr, nullptr};
+  cudaEvent_t inputs_ready = nullptr;
+  int cut = -1;                 // position of the cut index in idx_names (-1: no slabs)
+  int64_t extent = 1, slab = 1; // extent of the cut index, values per slab
+  int64_t step[3] = {0, 0, 0};  // elements per value of the cut index where the tensor travels slab by slab (0: whole, first)
+  int64_t view[3] = {0, 0, 0};  // element stride of the cut index in C, A, B (0: the tensor does not carry it)
+  tc_plan* plan_slab = nullptr; // slab-sized sub-plan (strides of the full tensors)
+  tc_plan* plan_tail = nullptr; // last, shorter slab
+};
+
+static void host_pipe_destroy(TcHostPipe* h) {
+  if (!h) return;
+  if (h->dC) cudaFree(h->dC);
+  if (h->dA) cudaFree(h->dA);
+  if (h->dB) cudaFree(h->dB);
+  for (cudaStream_t s : h->stream)
+    if (s) cudaStreamDestroy(s);
+  if (h->inputs_ready) cudaEventDestroy(h->inputs_ready);
+  if (h->plan_slab) tc_plan_destroy(h->plan_slab);
+  if (h->plan_tail) tc_plan_destroy(h->plan_tail);
+  delete h;
+}
+
+static int make_slab_plan(const tc_plan* p, int cut, int64_t count, tc_plan** out) {
+  tc_plan* q = new (std::nothrow) tc_plan();
+  if (!q) return TC_ERR_INVALID_ARG;
+  q->expr = p->expr;
+  q->dtype = p->dtype;
+  q->opt = p->opt;
+  q->idx_names = p->idx_names;
+  q->idx_extent = p->idx_extent;
+  q->idx_extent[cut] = count;
+  // views into the full (compact) device tensors
+  const std::vector<std::string>* tidx[3] = {&p->expr.out_idx, &p->expr.left_idx, &p->expr.right_idx};
+  for (int t = 0; t < 3; ++t) {
+    int64_t acc = 1;
+    for (const std::string& n : *tidx[t]) {
+      q->strides[t].push_back(acc);
+      for (size_t j = 0; j < p->idx_names.size(); ++j)
+        if (p->idx_names[j] == n) acc *= p->idx_extent[j];
+    }
+    q->custom_strides[t] = true;
+  }
+  const int st = tc_plan_commit(q);
+  if (st != TC_OK) { tc_plan_destroy(q); return st; }
+  *out = q;
+  return TC_OK;
+}
+
+static int host_pipe_create(tc_plan* p) {
+  TcHostPipe* h = new (std::nothrow) TcHostPipe();
+  if (!h) return TC_ERR_INVALID_ARG;
+  p->host = h;
+  const size_t es = p->dtype == TC_F64 ? 8 : 4;
+  TC_CUDA_OK(cudaMalloc(&h->dC, p->size_c * es));
+  TC_CUDA_OK(cudaMalloc(&h->dA, p->size_a * es));
+  TC_CUDA_OK(cudaMalloc(&h->dB, p->size_b * es));
+  for (cudaStream_t& s : h->stream) TC_CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  TC_CUDA_OK(cudaEventCreateWithFlags(&h->inputs_ready, cudaEventDisableTiming));
+  // Slabs only for compact tensors, outputs worth pipelining (>= 32 MB) and plans that do not slice K.
+  const bool compact = !p->custom_strides[0] && !p->custom_strides[1] && !p->custom_strides[2];
+  const TcExpr& e = p->expr;
+  if (!compact || e.out_idx.empty() || p->count_c * (int64_t)es < (32 << 20) || p->args.ksplit > 1) return TC_OK;
+  const std::string& name = e.out_idx.back();
+  int cut = -1;
+  for (size_t j = 0; j < p->idx_names.size(); ++j)
+    if (p->idx_names[j] == name) cut = (int)j;
+  const int64_t extent = p->idx_extent[cut];
+  if (extent < 4) return TC_OK;
+  const int64_t nslabs = std::min<int64_t>(extent, 12);
+  h->slab = (extent + nslabs - 1) / nslabs;
+  h->extent = extent;
+  h->step[0] = h->view[0] = p->count_c / extent;
+  if (!e.left_idx.empty() && e.left_idx.back() == name) h->step[1] = p->count_a / extent;
+  if (!e.right_idx.empty() && e.right_idx.back() == name) h->step[2] = p->count_b / extent;
+  const std::vector<std::string>* in_idx[2] = {&e.left_idx, &e.right_idx};
+  for (int t = 0; t < 2; ++t) {
+    int64_t acc = 1;
+    for (const std::string& n : *in_idx[t]) {
+      if (n == name) h->view[t + 1] = acc;
+      for (size_t j = 0; j < p->idx_names.size(); ++j)
+        if (p->idx_names[j] == n) acc *= p->idx_extent[j];
+    }
+  }
+  int st = make_slab_plan(p, cut, h->slab, &h->plan_slab);
+  if (st != TC_OK) return st;
+  if (extent % h->slab) {
+    st = make_slab_plan(p, cut, extent % h->slab, &h->plan_tail);
+    if (st != TC_OK) return st;
+  }
+  if (h->plan_slab->args.ksplit > 1 || (h->plan_tail && h->plan_tail->args.ksplit > 1)) return TC_OK;  // keep one stream
+  h->cut = cut;
+  return TC_OK;
+}
+
 extern "C" int tc_execute_host(tc_plan* p, void* C, const void* A, const void* B) {
   if (!p || !C || !A || !B) return TC_ERR_INVALID_ARG;
   if (!p->committed) {
     const int st = tc_plan_commit(p);
     if (st != TC_OK) return st;
   }
+  int dev = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev != p->device) return TC_ERR_STATE;
+  if (!p->host) {
+    const int st = host_pipe_create(p);
+    if (st != TC_OK) { host_pipe_destroy(p->host); p->host = nullptr; return st; }
+  }
+  TcHostPipe* h = p->host;
   const size_t es = p->dtype == TC_F64 ? 8 : 4;
-  void *dC = nullptr, *dA = nullptr, *dB = nullptr;
-  int st = TC_OK;
-  auto cleanup = [&]() {
-    if (dC) cudaFree(dC);
-    if (dA) cudaFree(dA);
-    if (dB) cudaFree(dB);
-  };
-#define TC_HOST_OK(call)                                   \
-  do {                                                     \
-    cudaError_t e_ = (call);                               \
-    if (e_ != cudaSuccess) {                               \
-      tc_note_cuda_error((int)e_, #call);                  \
-      cleanup();                                           \
-      return TC_ERR_CUDA;                                  \
-    }                                                      \
-  } while (0)
-  TC_HOST_OK(cudaMalloc(&dC, p->size_c * es));
-  TC_HOST_OK(cudaMalloc(&dA, p->size_a * es));
-  TC_HOST_OK(cudaMalloc(&dB, p->size_b * es));
-  cudaStream_t s = nullptr;
-  TC_HOST_OK(cudaMemcpyAsync(dA, A, p->size_a * es, cudaMemcpyHostToDevice, s));
-  TC_HOST_OK(cudaMemcpyAsync(dB, B, p->size_b * es, cudaMemcpyHostToDevice, s));
-  if (p->args.beta || p->size_c != p->count_c)
-    TC_HOST_OK(cudaMemcpyAsync(dC, C, p->size_c * es, cudaMemcpyHostToDevice, s));
-  st = execute_impl(p, dC, dA, dB, p->d_ws, p->ws_bytes, s);
-  if (st != TC_OK) { cleanup(); return st; }
-  TC_HOST_OK(cudaMemcpyAsync(C, dC, p->size_c * es, cudaMemcpyDeviceToHost, s));
-  TC_HOST_OK(cudaStreamSynchronize(s));
-#undef TC_HOST_OK
-  cleanup();
+  char* hC = static_cast<char*>(C);
+  const char* hA = static_cast<const char*>(A);
+  const char* hB = static_cast<const char*>(B);
+  char *dC = static_cast<char*>(h->dC), *dA = static_cast<char*>(h->dA), *dB = static_cast<char*>(h->dB);
+  const bool read_c = p->args.beta || p->size_c != p->count_c;
+  cudaStream_t s0 = h->stream[0];
+  if (h->cut < 0) {  // one piece
+    TC_CUDA_OK(cudaMemcpyAsync(dA, hA, p->size_a * es, cudaMemcpyHostToDevice, s0));
+    TC_CUDA_OK(cudaMemcpyAsync(dB, hB, p->size_b * es, cudaMemcpyHostToDevice, s0));
+    if (read_c) TC_CUDA_OK(cudaMemcpyAsync(dC, hC, p->size_c * es, cudaMemcpyHostToDevice, s0));
+    const int st = execute_impl(p, dC, dA, dB, p->d_ws, p->ws_bytes, s0);
+    if (st != TC_OK) return st;
+    TC_CUDA_OK(cudaMemcpyAsync(hC, dC, p->size_c * es, cudaMemcpyDeviceToHost, s0));
+    TC_CUDA_OK(cudaStreamSynchronize(s0));
+    return TC_OK;
+  }
+  // inputs that are not sliced go first, whole
+  if (!h->step[1]) TC_CUDA_OK(cudaMemcpyAsync(dA, hA, p->size_a * es, cudaMemcpyHostToDevice, s0));
+  if (!h->step[2]) TC_CUDA_OK(cudaMemcpyAsync(dB, hB, p->size_b * es, cudaMemcpyHostToDevice, s0));
+  TC_CUDA_OK(cudaEventRecord(h->inputs_ready, s0));
+  int i = 0;
+  for (int64_t v = 0; v < h->extent; v += h->slab, ++i) {
+    const int64_t n = std::min(h->slab, h->extent - v);
+    tc_plan* q = n == h->slab ? h->plan_slab : h->plan_tail;
+    cudaStream_t s = h->stream[i & 1];
+    const size_t oc = (size_t)(v * h->step[0]) * es, oa = (size_t)(v * h->step[1]) * es, ob = (size_t)(v * h->step[2]) * es;
+    if (read_c) TC_CUDA_OK(cudaMemcpyAsync(dC + oc, hC + oc, (size_t)(n * h->step[0]) * es, cudaMemcpyHostToDevice, s));
+    if (h->step[1]) TC_CUDA_OK(cudaMemcpyAsync(dA + oa, hA + oa, (size_t)(n * h->step[1]) * es, cudaMemcpyHostToDevice, s));
+    if (h->step[2]) TC_CUDA_OK(cudaMemcpyAsync(dB + ob, hB + ob, (size_t)(n * h->step[2]) * es, cudaMemcpyHostToDevice, s));
+    if (s != s0) TC_CUDA_OK(cudaStreamWaitEvent(s, h->inputs_ready, 0));
+    const int st = execute_impl(q, dC + oc, dA + (size_t)(v * h->view[1]) * es, dB + (size_t)(v * h->view[2]) * es, q->d_ws,
+                                q->ws_bytes, s);
+    if (st != TC_OK) return st;
+    TC_CUDA_OK(cudaMemcpyAsync(hC + oc, dC + oc, (size_t)(n * h->step[0]) * es, cudaMemcpyDeviceToHost, s));
+  }
+  TC_CUDA_OK(cudaStreamSynchronize(h->stream[0]));
+  TC_CUDA_OK(cudaStreamSynchronize(h->stream[1]));
   return TC_OK;
 }
 

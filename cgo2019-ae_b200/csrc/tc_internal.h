@@ -93,6 +93,8 @@ struct TcKernelChoice {
   bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
 };
 
+struct TcHostPipe;
+
 // Host-side plan.
 struct tc_plan {
   TcExpr expr;
@@ -114,6 +116,7 @@ struct tc_plan {
   void* d_koff = nullptr;      // device copy of both tables
   void* d_ws = nullptr;        // plan-owned K-slice workspace
   int* d_status = nullptr;     // device status word
+  struct TcHostPipe* host = nullptr;  // device buffers, streams and slab plans of the host-pointer path
   size_t ws_bytes = 0;
   int64_t size_c = 0, size_a = 0, size_b = 0;  // elements spanned (max offset + 1)
   int64_t count_c = 0, count_a = 0, count_b = 0;  // logical element counts
