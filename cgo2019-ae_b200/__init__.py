@@ -36,7 +36,7 @@ class TcError(RuntimeError):
 class Options(ctypes.Structure):
     _fields_ = [("path", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("variant", ctypes.c_int), ("l2_prefetch", ctypes.c_int),
-                ("c_path", ctypes.c_int), ("reserved", ctypes.c_int * 1)]
+                ("c_path", ctypes.c_int), ("tma", ctypes.c_int)]
 
 
 _lib = None
@@ -138,7 +138,7 @@ def _ptr(x):
 class Plan:
     """One contraction: expression + dtype (+ extents, strides, options)."""
 
-    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None, variant=0, l2_prefetch=0, c_path=0):
+    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None, variant=0, l2_prefetch=0, c_path=0, tma=0):
         self._h = ctypes.c_void_p()
         opt = Options()
         opt.path = path
@@ -148,6 +148,7 @@ class Plan:
         opt.variant = variant
         opt.l2_prefetch = l2_prefetch
         opt.c_path = c_path
+        opt.tma = tma
         self.expr = expr
         self.dtype = dtype
         _check(lib().tc_plan_create(expr.encode(), dtype, ctypes.byref(opt), ctypes.byref(self._h)), "tc_plan_create")

@@ -1,5 +1,6 @@
 // C ABI: plan / execute / free, the seeded input generator and small utilities.
 // Declarations and the reference interfaces they replace are in include/tc_b200.h.
+#include <cuda.h>  // types of the tensor-map encoder only; the entry point is looked up at run time
 #include <cuda_runtime.h>
 
 #include <algorithm>
@@ -101,6 +102,33 @@ static tc_inst_fn pick_inst(const TcKernelChoice& c) {
 
 static int mode_of(bool ext_vec, bool k_vec) { return ext_vec ? 1 : k_vec ? 2 : 0; }
 
+// Tiled TMA descriptor of an operand seen as a 2-D fp64 matrix: dimension 0 = contraction index (stride 1),
+// dimension 1 = flattened external index at `pitch` elements; box = 16 x rows, 128-byte swizzle, zero fill
+// outside the tensor.  cuTensorMapEncodeTiled is resolved through the runtime (no link against libcuda).
+static bool encode_operand_map(TcTensorMap* out, const void* base, uint64_t k_extent, uint64_t ext_extent,
+                               uint64_t pitch, uint32_t rows) {
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<encode_fn>(f);
+  }();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 8) % 16 != 0 || rows > 256) return false;
+  const cuuint64_t dims[2] = {k_extent, ext_extent};
+  const cuuint64_t strides[1] = {pitch * 8};
+  const cuuint32_t box[2] = {16, rows};
+  const cuuint32_t estr[2] = {1, 1};
+  static_assert(sizeof(CUtensorMap) == sizeof(TcTensorMap), "tensor map storage");
+  return fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 2, const_cast<void*>(base), dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk) {
   if (bk) *bk = TC_BK;
   tc_inst_fn fn = pick_inst(c);
@@ -114,8 +142,10 @@ int tc_kernels_prepare(const TcKernelChoice& c) {
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
   const int mx = mode_of(c.vec_x, c.kvec_x), my = mode_of(c.vec_y, c.kvec_y);
-  for (int vx = 0; vx <= mx; vx += (mx ? mx : 1))
-    for (int vy = 0; vy <= my; vy += (my ? my : 1)) {
+  const bool ws = tc_kernel_is_persistent(c);
+  const int xs[3] = {0, mx, (ws && c.tma_x) ? 3 : 0}, ys[3] = {0, my, (ws && c.tma_y) ? 3 : 0};
+  for (int vx : xs)
+    for (int vy : ys) {
       const int st = fn(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
       if (st != TC_OK) return st;
     }
@@ -139,7 +169,12 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   const bool x16 = (reinterpret_cast<uintptr_t>(X) & 15) == 0, y16 = (reinterpret_cast<uintptr_t>(Y) & 15) == 0;
   const uintptr_t cu = reinterpret_cast<uintptr_t>(C);
   if ((cu & 15) != 0) a.vec_c = 1;
-  const int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
+  int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
+  // Persistent kernels fetch operands that are plain 2-D matrices with one tiled TMA copy per stage.
+  if (tc_kernel_is_persistent(c) && p.opt.tma != 1) {
+    if (c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
+    if (c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
+  }
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
   int st = fn(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);

@@ -10,7 +10,7 @@
 enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3 };
 
 // mode_x / mode_y: 0 element loads, 1 16-byte loads along the external index, 2 16-byte loads along the
-// contraction index (kernels without a contraction-major image treat 2 as 0).
+// contraction index, 3 one tiled TMA copy per stage (kernels without these images treat 2 and 3 as 0).
 typedef int (*tc_inst_fn)(int mode_x, int mode_y, const TcKernelArgs* args, void* C, const void* X, const void* Y,
                           cudaStream_t stream, int mode, int* threads, int* smem_bytes);
 
@@ -85,9 +85,10 @@ int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
 #define TC_DEFINE_WS_INST(NAME, BM, BN, STAGES)                                                              \
   extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,         \
                       cudaStream_t s, int mode, int* threads, int* smem) {                                  \
-    TC_WS_CASE(0, 0, BM, BN, STAGES) TC_WS_CASE(0, 1, BM, BN, STAGES) TC_WS_CASE(0, 2, BM, BN, STAGES)      \
-    TC_WS_CASE(1, 0, BM, BN, STAGES) TC_WS_CASE(1, 1, BM, BN, STAGES) TC_WS_CASE(1, 2, BM, BN, STAGES)      \
-    TC_WS_CASE(2, 0, BM, BN, STAGES) TC_WS_CASE(2, 1, BM, BN, STAGES) TC_WS_CASE(2, 2, BM, BN, STAGES)      \
+    TC_WS_CASE(0, 0, BM, BN, STAGES) TC_WS_CASE(0, 1, BM, BN, STAGES) TC_WS_CASE(0, 2, BM, BN, STAGES) TC_WS_CASE(0, 3, BM, BN, STAGES) \
+    TC_WS_CASE(1, 0, BM, BN, STAGES) TC_WS_CASE(1, 1, BM, BN, STAGES) TC_WS_CASE(1, 2, BM, BN, STAGES) TC_WS_CASE(1, 3, BM, BN, STAGES) \
+    TC_WS_CASE(2, 0, BM, BN, STAGES) TC_WS_CASE(2, 1, BM, BN, STAGES) TC_WS_CASE(2, 2, BM, BN, STAGES) TC_WS_CASE(2, 3, BM, BN, STAGES) \
+    TC_WS_CASE(3, 0, BM, BN, STAGES) TC_WS_CASE(3, 1, BM, BN, STAGES) TC_WS_CASE(3, 2, BM, BN, STAGES) TC_WS_CASE(3, 3, BM, BN, STAGES) \
     return TC_ERR_INVALID_ARG;                                                                              \
   }
 

@@ -55,6 +55,9 @@ struct TcDims {
   int64_t s_out[TC_MAX_DIMS];  // element stride in the output
 };
 
+// Opaque storage of a CUtensorMap (128 bytes, 64-byte aligned), so host-only sources need no CUDA headers.
+struct alignas(64) TcTensorMap { uint64_t opaque[16]; };
+
 // Everything a kernel launch needs besides the three tensor pointers.
 // "M" is the external class of operand X (the one holding the output's fastest
 // index after the planner's optional operand swap), "N" the class of operand Y.
@@ -79,6 +82,7 @@ struct TcKernelArgs {
   void* ws;          // K-slice partials: [ksplit][tiles][BN][BM]
   int32_t epi_run;       // staged bulk epilogue: run length E0 in elements (0 = not available)
   int32_t epi_n_span;    // ... F0 > 0: consecutive n are adjacent in the output within blocks of F0 (0: never)
+  TcTensorMap tmap_x, tmap_y;  // tiled TMA descriptors of X / Y as 2-D (k, flattened external) tensors, when used
   int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
@@ -91,6 +95,7 @@ struct TcKernelChoice {
   int variant;    // warp layout of the tile (0-based)
   bool vec_x, vec_y;    // 16-byte loads along the external index of X / Y are legal
   bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
+  bool tma_x, tma_y;    // X / Y is a plain 2-D (k fastest, flattened external) matrix: tiles are TMA boxes
 };
 
 struct TcHostPipe;

@@ -36,7 +36,6 @@
 #define TC_WS_KERNEL_LIST(X) \
   X(dmma_ws_128x64, 128, 64, 3, 2)     \
   X(dmma_ws_64x96, 64, 96, 3, 2)       \
-  X(dmma_ws_128x96, 128, 96, 2, 2)     \
   X(dmma_ws_64x64, 64, 64, 4, 2)
 
 #endif  // TC_KERNEL_LIST_H_

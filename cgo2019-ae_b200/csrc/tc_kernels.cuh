@@ -532,6 +532,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
     const int g = lane >> 2, t = lane & 3;
     const int wm0 = (warp % CF::WARPS_M) * WM, wn0 = (warp / CF::WARPS_M) * WN;
     const float alpha = (float)p.alpha;
+    const bool rmw = accumulate;  // this path has no "accumulators start from C" mode: c_mode 1 means 0 here
     float acc[NB][2 * MB2][4];
 #pragma unroll
     for (int j = 0; j < NB; ++j)

@@ -223,6 +223,17 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   };
   loader(a.M, true, &c.vec_x, &c.kvec_x, &a.lanes_k_x);
   loader(a.N, false, &c.vec_y, &c.kvec_y, &a.lanes_k_y);
+  // An operand is a plain 2-D matrix (k fastest, then the flattened external index at a constant pitch)
+  // when it has one fused contraction dimension of stride 1 and its external dimensions are contiguous
+  // among themselves: then a tile of the flattened class is a box, which TMA can fetch.  fp64 only.
+  auto affine = [&](const TcDims& ext, bool k_is_in) {
+    if (es != 8 || kd.n != 1 || (k_is_in ? kd.s_in[0] : kd.s_out[0]) != 1 || ext.n < 1) return false;
+    for (int d = 1; d < ext.n; ++d)
+      if (ext.s_in[d] != ext.s_in[d - 1] * (int64_t)ext.extent[d - 1]) return false;
+    return ext.s_in[0] % 2 == 0 && ext.s_in[0] >= (int64_t)kd.extent[0];
+  };
+  c.tma_x = affine(a.M, true);
+  c.tma_y = affine(a.N, false);
 
   // Contiguous output elements per thread access.
   a.vec_c = 1;
@@ -341,7 +352,8 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
-      << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
+      << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
+      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"epi_run\":" << a.epi_run << ",\"epi_n_span\":" << a.epi_n_span << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches
       << ",\"flops\":" << p.flops << ",\"bytes\":" << p.bytes;

@@ -39,6 +39,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival that also announces `bytes` of asynchronous (TMA) traffic for the current phase.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Tiled TMA load of one 2-D box (no multicast): box corner (c0 = innermost coordinate, c1) of the tensor
+// described by `tmap` into shared memory at `dst`; completion is signalled on `bar` as transferred bytes.
+// c0 times the element size must be a multiple of 16 bytes; `dst` must be 1024-byte aligned for the
+// 128-byte swizzle the descriptor asks for.
+__device__ __forceinline__ void tma_load_2d(void* dst, const TcTensorMap* tmap, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -65,7 +78,10 @@ template <int R> __device__ __forceinline__ void reg_inc() { asm volatile("setma
 //   LM_ELEM     element copies, external-major image  [k][ext], pitch ROWS+4
 //   LM_EXT_VEC  16-byte copies along the external index, same image
 //   LM_K_VEC    16-byte copies along the contraction index, contraction-major image [ext][k], pitch 18
-enum { LM_ELEM = 0, LM_EXT_VEC = 1, LM_K_VEC = 2 };
+//   LM_TMA_K    one tiled TMA copy (cp.async.bulk.tensor.2d) per stage for operands that are plain 2-D
+//               matrices: dense contraction-major image [ext][16] with the 128-byte swizzle, i.e. the
+//               16-byte chunk c of row e sits at chunk position c ^ (e & 7)
+enum { LM_ELEM = 0, LM_EXT_VEC = 1, LM_K_VEC = 2, LM_TMA_K = 3 };
 
 template <int BM_, int BN_, int STAGES_, int MODEX_, int MODEY_>
 struct WsCfg {
@@ -79,11 +95,17 @@ struct WsCfg {
   static constexpr int CTA_THREADS = GROUPS * (CONSUMER_THREADS + THREADS);
   static constexpr int WM = BM / 2, WN = BN / 2;
   static constexpr int LDK = BK + 2;            // pitch of a contraction-major image (18 = 2 mod 16: conflict-free)
-  static constexpr int LDX = MODEX == LM_K_VEC ? LDK : BM + 4;
-  static constexpr int LDY = MODEY == LM_K_VEC ? LDK : BN + 4;
-  static constexpr int XIMG = MODEX == LM_K_VEC ? BM * LDK : BK * (BM + 4);
-  static constexpr int YIMG = MODEY == LM_K_VEC ? BN * LDK : BK * (BN + 4);
+  static constexpr int LDX = MODEX == LM_K_VEC ? LDK : MODEX == LM_TMA_K ? BK : BM + 4;
+  static constexpr int LDY = MODEY == LM_K_VEC ? LDK : MODEY == LM_TMA_K ? BK : BN + 4;
+  static constexpr bool ANY_TMA = MODEX == LM_TMA_K || MODEY == LM_TMA_K;
+  static constexpr int round128(int x) { return (x + 127) / 128 * 128; }  // TMA images start on 1024 bytes
+  static constexpr int XIMG_RAW = MODEX == LM_K_VEC ? BM * LDK : MODEX == LM_TMA_K ? BM * BK : BK * (BM + 4);
+  static constexpr int YIMG_RAW = MODEY == LM_K_VEC ? BN * LDK : MODEY == LM_TMA_K ? BN * BK : BK * (BN + 4);
+  static constexpr int XIMG = ANY_TMA ? round128(XIMG_RAW) : XIMG_RAW;
+  static constexpr int YIMG = ANY_TMA ? round128(YIMG_RAW) : YIMG_RAW;
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
+  static constexpr uint32_t TMA_BYTES = (MODEX == LM_TMA_K ? BM * BK * 8 : 0) + (MODEY == LM_TMA_K ? BN * BK * 8 : 0);
+  static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);
   static constexpr int TABLE_ELEMS = 2 * BM + 2 * BN;            // offx_m, offc_m, offy_n, offc_n
   static constexpr int NBARS = GROUPS * (2 * STAGES + 4);
   // Epilogue staging for the bulk reduce: per consumer warp 8 rows of WM outputs, pitch WM+2
@@ -213,6 +235,7 @@ __device__ __forceinline__ void ws_load(double* img, const double* __restrict__ 
                                         const int64_t* __restrict__ koff, uint32_t k0, uint32_t kend, int ptid, int lg) {
   if constexpr (MODE == LM_EXT_VEC) ws_load_ext_vec<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid);
   else if constexpr (MODE == LM_K_VEC) ws_load_k_vec<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid);
+  else if constexpr (MODE == LM_TMA_K) return;  // fetched by the producer's TMA copy
   else ws_load_elem<CF, ROWS>(img, g, s_off, koff, k0, kend, ptid, lg);
 }
 
@@ -220,7 +243,11 @@ __device__ __forceinline__ void ws_load(double* img, const double* __restrict__ 
 template <int MODE, int LD>
 __device__ __forceinline__ double2 ws_frag(const double* img, int e, int k) {
   if constexpr (MODE == LM_K_VEC) return make_double2(img[e * LD + k], img[(e + 1) * LD + k]);
-  else return *reinterpret_cast<const double2*>(img + k * LD + e);
+  else if constexpr (MODE == LM_TMA_K) {
+    // rows e and e+1 (e even): swizzled chunk position of k differs by the row's low bits
+    const int c = k >> 1, w = k & 1;
+    return make_double2(img[e * 16 + (((c ^ (e & 7)) << 1) | w)], img[(e + 1) * 16 + (((c ^ ((e + 1) & 7)) << 1) | w)]);
+  } else return *reinterpret_cast<const double2*>(img + k * LD + e);
 }
 
 template <class CF>
@@ -229,11 +256,11 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
                                                                          const double* __restrict__ X,
                                                                          const double* __restrict__ Y) {
   constexpr int BM = CF::BM, BN = CF::BN, BK = CF::BK, LDX = CF::LDX, LDY = CF::LDY, STAGES = CF::STAGES;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
-  int64_t* tables = reinterpret_cast<int64_t*>(bars + CF::NBARS);
-  double* stages = reinterpret_cast<double*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  double* stages = reinterpret_cast<double*>(smem_raw);  // first: TMA images need 1024-byte alignment
   double* cstages = stages + CF::GROUPS * CF::STAGES * CF::STAGE_ELEMS;
+  int64_t* tables = reinterpret_cast<int64_t*>(cstages + CF::GROUPS * 4 * CF::CSTAGE_ELEMS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -249,7 +276,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   if (tid == 0) {
     for (int q = 0; q < CF::GROUPS; ++q) {
       uint64_t* b = bars + q * (2 * STAGES + 4);
-      for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::THREADS); mbar_init(b + STAGES + s, 4); }
+      for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::FULL_ARRIVALS); mbar_init(b + STAGES + s, 4); }
       for (int s = 0; s < 2; ++s) { mbar_init(b + 2 * STAGES + s, CF::THREADS); mbar_init(b + 2 * STAGES + 2 + s, 4); }
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -298,6 +325,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         double* xs = gstage + s * CF::STAGE_ELEMS;
         double* ys = xs + CF::XIMG;
         const uint32_t k0 = (uint32_t)ks * BK;
+        if constexpr (CF::ANY_TMA) {
+          if (ptid == 0) {
+            mbar_arrive_expect_tx(&full[s], CF::TMA_BYTES);
+            if constexpr (CF::MODEX == LM_TMA_K) tma_load_2d(xs, &p.tmap_x, (int)k0, (int)m0, &full[s]);
+            if constexpr (CF::MODEY == LM_TMA_K) tma_load_2d(ys, &p.tmap_y, (int)k0, (int)n0, &full[s]);
+          }
+        }
         ws_load<CF, BM, CF::MODEX>(xs, X, offx_m, p.koff_x, k0, kend, ptid, lgx);
         ws_load<CF, BN, CF::MODEY>(ys, Y, offy_n, p.koff_y, k0, kend, ptid, lgy);
         mbar_arrive_on_copies(&full[s]);

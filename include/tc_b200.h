@@ -59,7 +59,7 @@ typedef struct tc_options {
                    /*   write in the epilogue, 2 = accumulators start from the output,       */
                    /*   3 = bulk asynchronous reduce-add from shared memory (persistent      */
                    /*   kernels, rows contiguous in the output; falls back to 1 elsewhere)   */
-  int reserved[1];
+  int tma;         /* tiled TMA loads of operands that are plain 2-D matrices: 0 = on, 1 = off */
 } tc_options;
 
 typedef struct tc_plan tc_plan;

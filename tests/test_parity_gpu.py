@@ -81,7 +81,8 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
         assert err <= TOL[dt], (expr, tile, err)
     if dt == "float32":  # both fp32 arithmetic paths, both ways of reaching the output
         for path in (pkg.PATH_FFMA, pkg.PATH_3XTF32):
-            for kw in ({}, {"tile": (96, 128), "c_path": 1}, {"tile": (128, 128), "c_path": 3}, {"tile": (64, 64), "split_k": 2}):
+            for kw in ({}, {"tile": (96, 128), "c_path": 1}, {"tile": (128, 128), "c_path": 3}, {"tile": (64, 64), "split_k": 2},
+                       {"tile": (64, 64), "c_path": 2}):
                 err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, path=path, **kw)
                 assert err <= TOL[dt], (expr, path, kw, err)
         err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, path=pkg.PATH_FFMA, tile=(128, 64))
@@ -91,7 +92,7 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
                    {"tile": (64, 64), "l2_prefetch": 1}, {"tile": (64, 64), "c_path": 2},
                    {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3},
                    {"tile": (64, 64), "variant": 3, "c_path": 2}, {"tile": (128, 64), "variant": 3, "c_path": 1},
-                   {"tile": (64, 96), "variant": 3, "c_path": 1, "l2_prefetch": 2}):
+                   {"tile": (64, 96), "variant": 3, "c_path": 1, "l2_prefetch": 2}, {"tile": (128, 64), "variant": 3, "tma": 1}):
             err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
             assert err <= TOL[dt], (expr, kw, err)
 
@@ -217,6 +218,8 @@ EDGE = [
     "C [a,31,b,37] = sum(c,4099) * A [c,a] * B [b,c];",                     # long prime contraction, overwrite
     "C [a,64,b,64] -= sum(c,64) * A [a,c] * B [b,c];",                      # both operands external-contiguous
     "C [a,64,b,64] += sum(c,64) * A [c,a] * B [c,b];",                      # both operands contraction-contiguous
+    "C [a,150,b,70] -= sum(d,37) * A [d,a] * B [d,b];",                     # 2-D operands (TMA boxes), ragged everywhere
+    "C [a,24,b,8,c,70] = sum(d,50) * A [d,a,b] * B [d,c];",                 # fused externals behind one TMA map
 ]
 
 
