@@ -142,7 +142,7 @@ int tc_kernels_prepare(const TcKernelChoice& c) {
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
   const int mx = mode_of(c.vec_x, c.kvec_x), my = mode_of(c.vec_y, c.kvec_y);
-  const bool ws = tc_kernel_is_persistent(c);
+  const bool ws = tc_kernel_is_persistent(c) && c.math == TC_MATH_DMMA;
   const int xs[3] = {0, mx, (ws && c.tma_x) ? 3 : 0}, ys[3] = {0, my, (ws && c.tma_y) ? 3 : 0};
   for (int vx : xs)
     for (int vy : ys) {
@@ -171,7 +171,7 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   if ((cu & 15) != 0) a.vec_c = 1;
   int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
   // Persistent kernels fetch operands that are plain 2-D matrices with one tiled TMA copy per stage.
-  if (tc_kernel_is_persistent(c) && p.opt.tma != 1) {
+  if (tc_kernel_is_persistent(c) && c.math == TC_MATH_DMMA && p.opt.tma != 1) {
     if (c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
     if (c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
   }
