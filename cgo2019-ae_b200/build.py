@@ -17,6 +17,7 @@ LIB = os.path.join(HERE, "libtc_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
+COMMON += os.environ.get("TC_NVCC_FLAGS", "").split()  # e.g. -DTC_WS_TIMING for the cycle counters of the persistent kernel
 
 
 def _newer(target, deps):

@@ -2,6 +2,7 @@
 // Declarations and the reference interfaces they replace are in include/tc_b200.h.
 #include <cuda.h>  // types of the tensor-map encoder only; the entry point is looked up at run time
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <cstdio>
@@ -129,6 +130,37 @@ static bool encode_operand_map(TcTensorMap* out, const void* base, uint64_t k_ex
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Rank-5 tiled TMA descriptor of the fp64 output for the persistent kernel's epilogue.  Dimensions, fastest
+// first: the contiguous run of the fastest M dimensions; the parity of n; n / 2 inside N's fastest dimensions;
+// then the remaining N and M dimensions (at most two together, padded with extent 1).
+// Box = (wm, 1, 8, 1, 1): the 8 rows one consumer warp stages at a time.  No swizzle, no fill.
+static bool encode_output_map(TcTensorMap* out, const void* base, const TcOutMap& o, uint32_t wm) {
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<encode_fn>(f);
+  }();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || wm > 256 || o.e0 == 0 || o.f0 < 2 || o.ne + o.me > 2) return false;
+  cuuint64_t dims[5] = {o.e0, 2, o.f0 / 2, 1, 1};
+  cuuint64_t strides[4] = {(cuuint64_t)o.stride_n * 8, (cuuint64_t)o.stride_n * 16, 0, 0};
+  int r = 3;
+  for (int d = 0; d < o.ne + o.me; ++d, ++r) { dims[r] = o.ext[d]; strides[r - 1] = (cuuint64_t)o.stride[d] * 8; }
+  for (; r < 5; ++r) strides[r - 1] = strides[r - 2] * dims[r - 1];  // extent-1 padding: any aligned stride
+  for (int i = 0; i < 4; ++i)
+    if (strides[i] % 16 != 0 || strides[i] >= (cuuint64_t(1) << 40)) return false;
+  const cuuint32_t box[5] = {wm, 1, 8, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  return fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 5, const_cast<void*>(base), dims,
+            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int* bk) {
   if (bk) *bk = TC_BK;
   tc_inst_fn fn = pick_inst(c);
@@ -172,8 +204,10 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
   // Persistent kernels fetch operands that are plain 2-D matrices with one tiled TMA copy per stage.
   if (tc_kernel_is_persistent(c) && c.math == TC_MATH_DMMA && p.opt.tma != 1) {
-    if (c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
-    if (c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
+    const bool operands = p.opt.tma == 0 || p.opt.tma == 2, output = p.opt.tma == 0 || p.opt.tma == 3;
+    if (operands && c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
+    if (operands && c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
+    a.c_tensor = (output && c.tma_c && a.c_mode == 2 && encode_output_map(&a.tmap_c, C, a.cmap, (uint32_t)a.bm / 2)) ? 1 : 0;
   }
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
@@ -360,6 +394,9 @@ static int execute_impl(tc_plan* p, void* C, const void* A, const void* B, void*
     if (!ws || ws_bytes < p->ws_bytes || (reinterpret_cast<uintptr_t>(ws) & 15)) return TC_ERR_WORKSPACE;
     a.ws = ws;
   }
+#ifdef TC_WS_TIMING
+  a.ws = ws;
+#endif
   const void* X = p->swapped ? B : A;
   const void* Y = p->swapped ? A : B;
   return tc_launch_contraction(*p, a, C, X, Y, static_cast<cudaStream_t>(stream));

@@ -58,6 +58,18 @@ struct TcDims {
 // Opaque storage of a CUtensorMap (128 bytes, 64-byte aligned), so host-only sources need no CUDA headers.
 struct alignas(64) TcTensorMap { uint64_t opaque[16]; };
 
+// The output seen as a tensor of rank <= 5 for tiled TMA copies: dimension 0 is the contiguous run of the
+// fastest M dimensions (fused as far as they are contiguous in C), dimensions 1 and 2 the parity of n and
+// n / 2 inside N's fastest dimensions (fused likewise), then `ne` further N dimensions and `me` further M
+// dimensions (ne + me <= 2).
+struct TcOutMap {
+  uint32_t e0, f0;     // extents of the fused fastest M / N dimensions
+  int32_t ne, me;      // slower dimensions of N / M that follow
+  uint32_t ext[2];     // their extents, N's first
+  int64_t stride_n;    // element stride of n inside f0
+  int64_t stride[2];   // element strides of ext[]
+};
+
 // Everything a kernel launch needs besides the three tensor pointers.
 // "M" is the external class of operand X (the one holding the output's fastest
 // index after the planner's optional operand swap), "N" the class of operand Y.
@@ -83,6 +95,9 @@ struct TcKernelArgs {
   int32_t epi_run;       // staged bulk epilogue: run length E0 in elements (0 = not available)
   int32_t epi_n_span;    // ... F0 > 0: consecutive n are adjacent in the output within blocks of F0 (0: never)
   TcTensorMap tmap_x, tmap_y;  // tiled TMA descriptors of X / Y as 2-D (k, flattened external) tensors, when used
+  int32_t c_tensor;      // persistent kernels: 1 = output batches leave as tiled TMA reduce/store boxes of tmap_c
+  TcOutMap cmap;         // ... the view of C they are boxes of
+  TcTensorMap tmap_c;    // its rank-5 descriptor
   int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
@@ -96,6 +111,7 @@ struct TcKernelChoice {
   bool vec_x, vec_y;    // 16-byte loads along the external index of X / Y are legal
   bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
   bool tma_x, tma_y;    // X / Y is a plain 2-D (k fastest, flattened external) matrix: tiles are TMA boxes
+  bool tma_c;           // a warp's 8-row output batch is a box of a rank-5 tensor over C
 };
 
 struct TcHostPipe;

@@ -322,6 +322,47 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     }
   }
 
+  // Persistent fp64 kernel: a consumer warp's batch of 8 output rows (n = base + 2g + parity, WM consecutive
+  // m) is one box of a rank-5 view of C when, with each class's dimensions fused as far as they are
+  // contiguous IN C (the flattened index does not change by that),
+  //   * the warp's WM outputs of a row sit inside one contiguous run: the fastest fused M dimension has
+  //     stride 1 and is the only one, or a multiple of the tile,
+  //   * the 16 rows of two batches stay inside N's fastest fused dimension (the only one, or a multiple of
+  //     16), which must be even so that n splits into (parity, n / 2),
+  //   * what is left of both classes fits the two remaining tensor dimensions, and every stride keeps
+  //     16-byte alignment.
+  // Then one tiled TMA reduce-add (or store) replaces eight per-row bulk copies.
+  c.tma_c = false;
+  a.cmap = TcOutMap{};
+  if (persistent && es == 8 && a.vec_c == 4 && a.M.n >= 1 && a.N.n >= 1 && a.M.s_out[0] == 1) {
+    auto fuse_out = [](const TcDims& cls, std::vector<int64_t>* ext, std::vector<int64_t>* str) {
+      for (int d = 0; d < cls.n; ++d) {
+        if (!ext->empty() && cls.s_out[d] == str->back() * ext->back()) ext->back() *= cls.extent[d];
+        else { ext->push_back(cls.extent[d]); str->push_back(cls.s_out[d]); }
+      }
+    };
+    std::vector<int64_t> me, ms, ne, ns;
+    fuse_out(a.M, &me, &ms);
+    fuse_out(a.N, &ne, &ns);
+    bool ok = (me.size() == 1 || me[0] % bm == 0) && ne[0] % 2 == 0 && (ne.size() == 1 || ne[0] % 16 == 0) &&
+              (me.size() - 1) + (ne.size() - 1) <= 2;
+    for (size_t d = 0; d < ne.size(); ++d) ok = ok && ns[d] % 2 == 0 && ns[d] > 0 && ns[d] < (int64_t(1) << 36) && ne[d] < (int64_t(1) << 31);
+    for (size_t d = 1; d < me.size(); ++d) ok = ok && ms[d] % 2 == 0 && ms[d] > 0 && ms[d] < (int64_t(1) << 36) && me[d] < (int64_t(1) << 31);
+    ok = ok && me[0] < (int64_t(1) << 31);
+    if (ok) {
+      TcOutMap& o = a.cmap;
+      o.e0 = (uint32_t)me[0];
+      o.f0 = (uint32_t)ne[0];
+      o.stride_n = ns[0];
+      o.ne = (int32_t)ne.size() - 1;
+      o.me = (int32_t)me.size() - 1;
+      int r = 0;
+      for (size_t d = 1; d < ne.size(); ++d, ++r) { o.ext[r] = (uint32_t)ne[d]; o.stride[r] = ns[d]; }
+      for (size_t d = 1; d < me.size(); ++d, ++r) { o.ext[r] = (uint32_t)me[d]; o.stride[r] = ms[d]; }
+      c.tma_c = true;
+    }
+  }
+
   double prod = 1.0;
   for (int64_t x : p->idx_extent) prod *= (double)x;
   p->flops = 2.0 * prod;
@@ -353,7 +394,8 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
-      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"lanes_k_x\":" << a.lanes_k_x
+      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false")
+      << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"epi_run\":" << a.epi_run << ",\"epi_n_span\":" << a.epi_n_span << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches
       << ",\"flops\":" << p.flops << ",\"bytes\":" << p.bytes;

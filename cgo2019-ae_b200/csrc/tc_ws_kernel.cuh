@@ -350,6 +350,11 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const int wm0 = (cw & 1) * WM, wn0 = (cw >> 1) * WN;
   const double alpha = p.alpha;
   uint32_t it = 0, titer = 0;
+#ifdef TC_WS_TIMING
+  long long tm_wait = 0, tm_mma = 0, tm_epi = 0, tm_rd = 0, tm_tab = 0, tm_tiles = 0;
+  const long long tm_begin = clock64();
+#define TM_NOW() clock64()
+#endif
   for (uint32_t tile = first; tile < total; tile += step, ++titer) {
     const uint32_t par = titer & 1;
     const int64_t* offc_m = gtab + par * CF::TABLE_ELEMS + BM;
@@ -384,7 +389,16 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 
     for (int ks = 0; ks < nk; ++ks, ++it) {
       const uint32_t s = it % STAGES;
+#ifdef TC_WS_TIMING
+      const long long tm0 = TM_NOW();
+      if (ks == 0 && p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
+        reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 0] = tm0;
+#endif
       if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, 3)) return;
+#ifdef TC_WS_TIMING
+      const long long tm1 = TM_NOW();
+      tm_wait += tm1 - tm0;
+#endif
       const double* xs = gstage + s * CF::STAGE_ELEMS;
       const double* ys = xs + CF::XIMG;
       const int kleft = (int)kend - ks * BK;
@@ -411,10 +425,22 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);  // this warp no longer reads the stage
+#ifdef TC_WS_TIMING
+      tm_mma += TM_NOW() - tm1;
+#endif
     }
+#ifdef TC_WS_TIMING
+    const long long tm2 = TM_NOW();
+    if (p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
+      reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 1] = tm2;
+#endif
 
     // ---- epilogue: read-modify-write of C (the tile was prefetched into L2 by the producers) ----
     if (!from_c && !mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4)) return;
+#ifdef TC_WS_TIMING
+    const long long tm3 = TM_NOW();
+    tm_tab += tm3 - tm2;
+#endif
     const bool rmw = accumulate && !from_c;
     // c_mode 2: the warp's tile leaves through shared memory as bulk asynchronous copies, one per output
     // row (WM contiguous elements): `+=`/`-=` become reduce-adds performed by the memory system, so the SM
@@ -424,14 +450,79 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       const int64_t c_lo = offc_m[wm0], c_hi = offc_m[wm0 + WM - 1];
       bulk = c_lo >= 0 && c_hi == c_lo + WM - 1;  // uniform across the warp
     }
-    if (bulk) {
+    // Tensor form of the same idea: a batch of 8 rows is one box of the rank-5 descriptor of C, so one tiled
+    // TMA reduce-add (or store) per batch replaces eight per-row copies.  Rows and columns beyond the tensor are
+    // clipped by the copy engine; boxes that lie outside altogether are not issued.
+    const uint32_t m_idx = (tile % p.tiles_m) * BM + wm0, n_base = (tile / p.tiles_m) * BN + wn0;
+    if (p.c_tensor && p.c_mode == 2 && !from_c) {
+      if (m_idx < p.Mflat) {
+        double* cst = cstages + (gi * 4 + cw) * CF::CSTAGE_ELEMS;
+        const uint64_t tmap = reinterpret_cast<uint64_t>(&p.tmap_c);
+        const uint32_t e0 = p.cmap.e0, f0 = p.cmap.f0;
+        const int ne = p.cmap.ne, me = p.cmap.me;
+        int xm[2] = {0, 0};  // coordinates 3 and 4: slower N dimensions first, then slower M dimensions
+        {
+          const uint32_t r = m_idx / e0;
+          if (me == 2) { xm[0] = (int)(r % p.cmap.ext[0]); xm[1] = (int)(r / p.cmap.ext[0]); }
+          else if (me == 1) { if (ne == 0) xm[0] = (int)r; else xm[1] = (int)r; }
+        }
+        const int c0 = (int)(m_idx % e0);
+#pragma unroll
+        for (int j = 0; j < NB2; ++j) {
+          const uint32_t n_idx = n_base + 16 * j;
+          if (n_idx >= p.Nflat) break;  // uniform across the warp
+          int x3 = xm[0], x4 = xm[1];
+          {
+            const uint32_t r = n_idx / f0;
+            if (ne == 2) { x3 = (int)(r % p.cmap.ext[0]); x4 = (int)(r / p.cmap.ext[0]); }
+            else if (ne == 1) x3 = (int)r;
+          }
+          const int q = (int)((n_idx % f0) >> 1);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int nb = 2 * j + h;
+            asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
+            __syncwarp();
+            double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;  // dense rows of WM: the box image
+#pragma unroll
+            for (int i = 0; i < MB2; ++i) {
+              double2* dst = reinterpret_cast<double2*>(cbuf + g * WM + 16 * i + 4 * t);
+              dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
+              dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t src = smem_u32(cbuf);
+              if (accumulate)
+                asm volatile(
+                    "cp.reduce.async.bulk.tensor.5d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];\n" ::"l"(tmap),
+                    "r"(c0), "r"(h), "r"(q), "r"(x3), "r"(x4), "r"(src)
+                    : "memory");
+              else
+                asm volatile(
+                    "cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];\n" ::"l"(tmap),
+                    "r"(c0), "r"(h), "r"(q), "r"(x3), "r"(x4), "r"(src)
+                    : "memory");
+              asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+            }
+          }
+        }
+      }
+    } else if (bulk) {
       double* cst = cstages + (gi * 4 + cw) * CF::CSTAGE_ELEMS;
       const int64_t c_lo = offc_m[wm0];
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
         // the batch that last used this staging buffer must have been read out of it
+#ifdef TC_WS_TIMING
+        const long long tm4 = TM_NOW();
+#endif
         asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
         __syncwarp();
+#ifdef TC_WS_TIMING
+        tm_rd += TM_NOW() - tm4;
+#endif
         double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;
 #pragma unroll
         for (int i = 0; i < MB2; ++i) {
@@ -524,7 +615,19 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&tab_empty[par]);  // the producers may overwrite this table set
+#ifdef TC_WS_TIMING
+    tm_epi += TM_NOW() - tm3;
+    if (p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
+      reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 2] = TM_NOW();
+    ++tm_tiles;
+#endif
   }
+#ifdef TC_WS_TIMING
+  if (p.ws && lane == 0) {
+    long long* o = reinterpret_cast<long long*>(p.ws) + ((blockIdx.x * 2 + gi) * 4 + cw) * 8;
+    o[0] = TM_NOW() - tm_begin; o[1] = tm_wait; o[2] = tm_mma; o[3] = tm_epi; o[4] = tm_rd; o[5] = tm_tab; o[6] = tm_tiles;
+  }
+#endif
   asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // outstanding bulk copies of this thread
 }
 

@@ -59,7 +59,9 @@ typedef struct tc_options {
                    /*   write in the epilogue, 2 = accumulators start from the output,       */
                    /*   3 = bulk asynchronous reduce-add from shared memory (persistent      */
                    /*   kernels, rows contiguous in the output; falls back to 1 elsewhere)   */
-  int tma;         /* tiled TMA loads of operands that are plain 2-D matrices: 0 = on, 1 = off */
+  int tma;         /* tiled TMA copies in the persistent fp64 kernel (operand tiles that are plain 2-D boxes;
+                      output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
+                      2 = operands only, 3 = output only */
 } tc_options;
 
 typedef struct tc_plan tc_plan;

@@ -235,6 +235,43 @@ def test_edge_shapes(pkg, orc, torch_cuda, expr):
         assert err <= TOL["float64"], (expr, kw, err)
 
 
+TENSOR_OUT = [
+    # one M run and one N dimension: tails of both are clipped by the copy engine
+    "C [a,200,b,70] += sum(c,40) * A [c,a] * B [c,b];",
+    "C [a,136,b,50] -= sum(c,24) * A [a,c] * B [b,c];",
+    "C [a,132,b,34] = sum(c,19) * A [c,a] * B [b,c];",
+    # the fastest M dimension is a multiple of both tiles; slower M and N dimensions become tensor dimensions
+    "C [a,128,b,32,c,3,d,2] += sum(e,24) * A [e,a,c] * B [b,d,e];",
+    "C [a,128,b,3,c,16,d,5] -= sum(e,33) * A [a,e,b] * B [e,c,d];",
+    "C [a,64,b,2,c,96] += sum(e,32) * A [a,e,b] * B [e,c];",
+    # N's fastest dimension is not a multiple of 16 while N has two dimensions: must fall back
+    "C [a,128,b,24,c,4] += sum(e,16) * A [e,a] * B [b,e,c];",
+]
+
+
+@pytest.mark.parametrize("expr", TENSOR_OUT)
+def test_persistent_tensor_box_epilogue(pkg, orc, torch_cuda, expr):
+    """Output batches as tiled TMA reduce/store boxes agree with the checker and, bit for bit, with the per-row
+    bulk copies they replace (both add the same products to the same words)."""
+    torch = torch_cuda
+    for tile in ((128, 64), (64, 96), (64, 64)):
+        outs = []
+        for tma in (0, 2):
+            c0, a, b = orc.make_inputs(expr, 77, "float64")
+            ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+            plan = pkg.Plan(expr, pkg.F64, tile=tile, variant=3, c_path=3, tma=tma)
+            dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+            plan.execute(dc, da, db)
+            torch.cuda.synchronize()
+            assert plan.status() == 0
+            d = plan.describe()
+            plan.close()
+            got = dc.cpu().numpy()
+            assert orc.rel_error(got, ref) <= TOL["float64"], (expr, tile, tma, d)
+            outs.append(got)
+        assert np.array_equal(outs[0], outs[1]), (expr, tile)
+
+
 def test_overwrite_ignores_initial_output_even_nan(pkg, orc, torch_cuda):
     torch = torch_cuda
     expr = "C [a,40,b,24] = sum(c,33) * A [c,a] * B [b,c];"
