@@ -207,7 +207,7 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
     const bool operands = p.opt.tma == 0 || p.opt.tma == 2, output = p.opt.tma == 0 || p.opt.tma == 3;
     if (operands && c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
     if (operands && c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
-    a.c_tensor = (output && c.tma_c && a.c_mode == 2 && encode_output_map(&a.tmap_c, C, a.cmap, (uint32_t)a.bm / 2)) ? 1 : 0;
+    a.c_tensor = (output && c.tma_c && a.c_mode == 2 && encode_output_map(&a.tmap_c, C, a.cmap, (uint32_t)a.bm / 2 /* rows of a consumer warp's block */)) ? 1 : 0;
   }
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;

@@ -5,18 +5,21 @@
 //
 //   * one CTA per SM lives for the whole contraction and walks a strided list of
 //     output tiles;
-//   * warps 0-3 and 4-7 are two CONSUMER groups, each owning its own tile
-//     (BM x BN, 2 x 2 warps) and its own stage ring: shared loads, DMMA and the
-//     read-modify-write of C, nothing else;
-//   * warps 8-9 / 10-11 are the PRODUCERS of group 0 / 1: they decode the tile's
-//     offset tables, prefetch its C tile into L2 and issue every cp.async of its
-//     stages, running ahead of the consumers by the depth of the ring -- across
-//     tile boundaries, so the set-up and load latency of tile i+1 and the DRAM
-//     fetch of its C hide behind the products of tile i, and one group's
-//     epilogue overlaps the other group's products;
+//   * the first 2*CW warps are two CONSUMER groups (CW = 4, 6 or 8 warps, one per
+//     32 x 32 block of the group's BM x BN tile), each group owning its own tile
+//     and its own stage ring: shared loads, DMMA and the output of C, nothing
+//     else;
+//   * the last four warps are the PRODUCERS, two per group: they decode the tile's
+//     offset tables, optionally prefetch its C tile into L2 and issue every copy of
+//     its stages (cp.async, or one tiled TMA box per operand), running ahead of
+//     the consumers by the depth of the ring -- across tile boundaries, so the
+//     set-up and load latency of tile i+1 hide behind the products of tile i, and
+//     one group's epilogue overlaps the other group's products;
 //   * stages and tables are handed over through mbarriers in shared memory
 //     (cp.async.mbarrier.arrive makes a stage "full" when its copies land);
-//   * registers follow the roles (setmaxnreg): producers shrink, consumers grow.
+//   * registers follow the roles (setmaxnreg): producers shrink, consumers grow;
+//     every warp executes its setmaxnreg (all four warps of a warpgroup must, or
+//     the instruction never completes).
 //
 // Every mbarrier wait is bounded: a wait that does not complete within
 // kSpinLimit polls records an error code in *args.status and the thread leaves
@@ -90,10 +93,13 @@ struct WsCfg {
   static constexpr int MODEX = MODEX_, MODEY = MODEY_;
   static constexpr int ES = 8, VW = 2;
   static constexpr int GROUPS = 2;
-  static constexpr int CONSUMER_THREADS = 128;  // per group: 2 x 2 warps
+  // Consumer warps of a group: 2 x 2 blocks of 64 x 32 outputs on a 128 x 64 tile, 2 x 3 blocks of 32 x 32
+  // on 64 x 96 (six warps: measured faster there than four warps of 32 x 48), 2 x 2 of 32 x 32 on 64 x 64.
+  static constexpr int WGM = 2, WGN = BN == 96 ? 3 : 2, CW = WGM * WGN;  // consumer warps per group
+  static constexpr int WM = BM / WGM, WN = BN / WGN;
+  static constexpr int CONSUMER_THREADS = CW * 32;
   static constexpr int THREADS = 64;            // producer threads per group
   static constexpr int CTA_THREADS = GROUPS * (CONSUMER_THREADS + THREADS);
-  static constexpr int WM = BM / 2, WN = BN / 2;
   static constexpr int LDK = BK + 2;            // pitch of a contraction-major image (18 = 2 mod 16: conflict-free)
   static constexpr int LDX = MODEX == LM_K_VEC ? LDK : MODEX == LM_TMA_K ? BK : BM + 4;
   static constexpr int LDY = MODEY == LM_K_VEC ? LDK : MODEY == LM_TMA_K ? BK : BN + 4;
@@ -114,10 +120,16 @@ struct WsCfg {
   static constexpr int CBATCH_ELEMS = 8 * CPITCH;
   static constexpr int BASE_BYTES = NBARS * 8 + GROUPS * 2 * TABLE_ELEMS * 8 + GROUPS * STAGES * STAGE_ELEMS * 8;
   // two staging batches per warp (the copies of one batch drain while the next is written) where they fit
-  static constexpr int CBUF = BASE_BYTES + GROUPS * 4 * 2 * CBATCH_ELEMS * 8 <= 232448 - 1024 ? 2 : 1;
+  static constexpr int CBUF = BASE_BYTES + GROUPS * CW * 2 * CBATCH_ELEMS * 8 <= 232448 - 1024 ? 2 : 1;
   static constexpr int CSTAGE_ELEMS = CBUF * CBATCH_ELEMS;
-  static constexpr int SMEM_BYTES = BASE_BYTES + GROUPS * 4 * CSTAGE_ELEMS * 8;
-  static constexpr int PRODUCER_REGS = 56, CONSUMER_REGS = 224;
+  static constexpr int SMEM_BYTES = BASE_BYTES + GROUPS * CW * CSTAGE_ELEMS * 8;
+  // Registers follow the roles.  The CTA starts with LAUNCH_REGS per thread (what fits 64 K registers, in
+  // units of 8); producers shrink to PRODUCER_REGS and the consumers share what that frees.
+  static constexpr int LAUNCH_REGS = (65536 / CTA_THREADS) / 8 * 8 > 255 ? 248 : (65536 / CTA_THREADS) / 8 * 8;
+  static constexpr int PRODUCER_REGS = 56;
+  static constexpr int CONSUMER_REGS_RAW =
+      (LAUNCH_REGS + (LAUNCH_REGS - PRODUCER_REGS) * GROUPS * THREADS / (GROUPS * CONSUMER_THREADS)) / 8 * 8;
+  static constexpr int CONSUMER_REGS = CONSUMER_REGS_RAW > 224 ? 224 : CONSUMER_REGS_RAW;
 };
 
 // Producer loaders.  A producer thread keeps what does not change inside a stage in
@@ -259,13 +271,14 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   double* stages = reinterpret_cast<double*>(smem_raw);  // first: TMA images need 1024-byte alignment
   double* cstages = stages + CF::GROUPS * CF::STAGES * CF::STAGE_ELEMS;
-  int64_t* tables = reinterpret_cast<int64_t*>(cstages + CF::GROUPS * 4 * CF::CSTAGE_ELEMS);
+  int64_t* tables = reinterpret_cast<int64_t*>(cstages + CF::GROUPS * CF::CW * CF::CSTAGE_ELEMS);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const bool is_producer = warp >= 8;
-  const int gi = is_producer ? (warp - 8) >> 1 : warp >> 2;  // group served
+  constexpr int CW = CF::CW;
+  const bool is_producer = warp >= 2 * CW;
+  const int gi = is_producer ? (warp - 2 * CW) >> 1 : warp / CW;  // group served
   uint64_t* full = bars + gi * (2 * STAGES + 4);             // [STAGES]
   uint64_t* empty = full + STAGES;                           // [STAGES]
   uint64_t* tab_full = empty + STAGES;                       // [2]
@@ -276,8 +289,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   if (tid == 0) {
     for (int q = 0; q < CF::GROUPS; ++q) {
       uint64_t* b = bars + q * (2 * STAGES + 4);
-      for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::FULL_ARRIVALS); mbar_init(b + STAGES + s, 4); }
-      for (int s = 0; s < 2; ++s) { mbar_init(b + 2 * STAGES + s, CF::THREADS); mbar_init(b + 2 * STAGES + 2 + s, 4); }
+      for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::FULL_ARRIVALS); mbar_init(b + STAGES + s, CW); }
+      for (int s = 0; s < 2; ++s) { mbar_init(b + 2 * STAGES + s, CF::THREADS); mbar_init(b + 2 * STAGES + 2 + s, CW); }
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -292,7 +305,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   if (is_producer) {
     // ------------------------------------------------------------ producer ----
     reg_dec<CF::PRODUCER_REGS>();
-    const int ptid = tid - 256 - gi * CF::THREADS;
+    const int ptid = tid - 2 * CF::CONSUMER_THREADS - gi * CF::THREADS;
     const int lgx = p.lanes_k_x == 1 ? 0 : 2, lgy = p.lanes_k_y == 1 ? 0 : 2;
     uint32_t it = 0, titer = 0;
     for (uint32_t tile = first; tile < total; tile += step, ++titer) {
@@ -345,9 +358,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   reg_inc<CF::CONSUMER_REGS>();
   constexpr int WM = CF::WM, WN = CF::WN;
   constexpr int MB2 = WM / 16, NB2 = WN / 16;
-  const int lane = tid & 31, cw = warp & 3;
+  const int lane = tid & 31, cw = warp % CW;
   const int g = lane >> 2, t = lane & 3;
-  const int wm0 = (cw & 1) * WM, wn0 = (cw >> 1) * WN;
+  const int wm0 = (cw % CF::WGM) * WM, wn0 = (cw / CF::WGM) * WN;
   const double alpha = p.alpha;
   uint32_t it = 0, titer = 0;
 #ifdef TC_WS_TIMING
@@ -456,7 +469,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     const uint32_t m_idx = (tile % p.tiles_m) * BM + wm0, n_base = (tile / p.tiles_m) * BN + wn0;
     if (p.c_tensor && p.c_mode == 2 && !from_c) {
       if (m_idx < p.Mflat) {
-        double* cst = cstages + (gi * 4 + cw) * CF::CSTAGE_ELEMS;
+        double* cst = cstages + (gi * CW + cw) * CF::CSTAGE_ELEMS;
         const uint64_t tmap = reinterpret_cast<uint64_t>(&p.tmap_c);
         const uint32_t e0 = p.cmap.e0, f0 = p.cmap.f0;
         const int ne = p.cmap.ne, me = p.cmap.me;
@@ -510,7 +523,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         }
       }
     } else if (bulk) {
-      double* cst = cstages + (gi * 4 + cw) * CF::CSTAGE_ELEMS;
+      double* cst = cstages + (gi * CW + cw) * CF::CSTAGE_ELEMS;
       const int64_t c_lo = offc_m[wm0];
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
@@ -623,7 +636,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 #endif
   }
 #ifdef TC_WS_TIMING
-  if (p.ws && lane == 0) {
+  if (p.ws && lane == 0 && cw < 4) {
     long long* o = reinterpret_cast<long long*>(p.ws) + ((blockIdx.x * 2 + gi) * 4 + cw) * 8;
     o[0] = TM_NOW() - tm_begin; o[1] = tm_wait; o[2] = tm_mma; o[3] = tm_epi; o[4] = tm_rd; o[5] = tm_tab; o[6] = tm_tiles;
   }
