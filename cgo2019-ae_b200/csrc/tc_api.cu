@@ -133,8 +133,10 @@ static bool encode_operand_map(TcTensorMap* out, const void* base, uint64_t k_ex
 // Rank-5 tiled TMA descriptor of the fp64 output for the persistent kernel's epilogue.  Dimensions, fastest
 // first: the contiguous run of the fastest M dimensions; the parity of n; n / 2 inside N's fastest dimensions;
 // then the remaining N and M dimensions (at most two together, padded with extent 1).
-// Box = (wm, 1, 8, 1, 1): the 8 rows one consumer warp stages at a time.  No swizzle, no fill.
-static bool encode_output_map(TcTensorMap* out, const void* base, const TcOutMap& o, uint32_t wm) {
+// Box = (bw, bh, bq, 1, 1): (warp rows, 1, 8) for the 8 rows one consumer warp stages at a time, or
+// (bm, 2, bn / 2) for a whole tile.  No swizzle, no fill.
+static bool encode_output_map(TcTensorMap* out, const void* base, const TcOutMap& o, uint32_t bw, uint32_t bh,
+                              uint32_t bq) {
   typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -146,7 +148,7 @@ static bool encode_output_map(TcTensorMap* out, const void* base, const TcOutMap
       f = nullptr;
     return reinterpret_cast<encode_fn>(f);
   }();
-  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || wm > 256 || o.e0 == 0 || o.f0 < 2 || o.ne + o.me > 2) return false;
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || bw > 256 || bq > 256 || o.e0 == 0 || o.f0 < 2 || o.ne + o.me > 2) return false;
   cuuint64_t dims[5] = {o.e0, 2, o.f0 / 2, 1, 1};
   cuuint64_t strides[4] = {(cuuint64_t)o.stride_n * 8, (cuuint64_t)o.stride_n * 16, 0, 0};
   int r = 3;
@@ -154,7 +156,7 @@ static bool encode_output_map(TcTensorMap* out, const void* base, const TcOutMap
   for (; r < 5; ++r) strides[r - 1] = strides[r - 2] * dims[r - 1];  // extent-1 padding: any aligned stride
   for (int i = 0; i < 4; ++i)
     if (strides[i] % 16 != 0 || strides[i] >= (cuuint64_t(1) << 40)) return false;
-  const cuuint32_t box[5] = {wm, 1, 8, 1, 1};
+  const cuuint32_t box[5] = {bw, bh, bq, 1, 1};
   const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   return fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT64, 5, const_cast<void*>(base), dims,
             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -204,10 +206,14 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   int vx = x16 ? mode_of(c.vec_x, c.kvec_x) : 0, vy = y16 ? mode_of(c.vec_y, c.kvec_y) : 0;
   // Persistent kernels fetch operands that are plain 2-D matrices with one tiled TMA copy per stage.
   if (tc_kernel_is_persistent(c) && c.math == TC_MATH_DMMA && p.opt.tma != 1) {
-    const bool operands = p.opt.tma == 0 || p.opt.tma == 2, output = p.opt.tma == 0 || p.opt.tma == 3;
+    const bool operands = p.opt.tma == 0 || p.opt.tma == 2 || p.opt.tma == 4, output = p.opt.tma == 0 || p.opt.tma == 3 || p.opt.tma == 4;
     if (operands && c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm)) vx = 3;
     if (operands && c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn)) vy = 3;
-    a.c_tensor = (output && c.tma_c && a.c_mode == 2 && encode_output_map(&a.tmap_c, C, a.cmap, (uint32_t)a.bm / 2 /* rows of a consumer warp's block */)) ? 1 : 0;
+    a.c_tensor = (output && c.tma_c && a.c_mode == 2 &&
+                  encode_output_map(&a.tmap_c, C, a.cmap, (uint32_t)a.bm / 2 /* rows of a consumer warp's block */, 1, 8)) ? 1 : 0;
+    if (a.c_tensor == 1 && c.tma_ct && p.opt.tma != 4 &&
+        encode_output_map(&a.tmap_ct, C, a.cmap, (uint32_t)a.bm, 2, (uint32_t)a.bn / 2))
+      a.c_tensor = 2;
   }
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;

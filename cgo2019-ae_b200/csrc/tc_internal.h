@@ -95,9 +95,12 @@ struct TcKernelArgs {
   int32_t epi_run;       // staged bulk epilogue: run length E0 in elements (0 = not available)
   int32_t epi_n_span;    // ... F0 > 0: consecutive n are adjacent in the output within blocks of F0 (0: never)
   TcTensorMap tmap_x, tmap_y;  // tiled TMA descriptors of X / Y as 2-D (k, flattened external) tensors, when used
-  int32_t c_tensor;      // persistent kernels: 1 = output batches leave as tiled TMA reduce/store boxes of tmap_c
+  int32_t c_tensor;      // persistent kernels: output leaves as tiled TMA reduce/store boxes: 1 = one box per
+                         // consumer warp and batch of 8 rows (tmap_c), 2 = one box per tile (tmap_ct) where the
+                         // kernel has room to stage a whole tile, else as 1
   TcOutMap cmap;         // ... the view of C they are boxes of
-  TcTensorMap tmap_c;    // its rank-5 descriptor
+  TcTensorMap tmap_c;    // its rank-5 descriptor with box (warp rows, 1, 8, 1, 1)
+  TcTensorMap tmap_ct;   // the same tensor with box (bm, 2, bn / 2, 1, 1)
   int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
@@ -112,6 +115,7 @@ struct TcKernelChoice {
   bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
   bool tma_x, tma_y;    // X / Y is a plain 2-D (k fastest, flattened external) matrix: tiles are TMA boxes
   bool tma_c;           // a warp's 8-row output batch is a box of a rank-5 tensor over C
+  bool tma_ct;          // ... and so is a whole bm x bn tile
 };
 
 struct TcHostPipe;

@@ -333,6 +333,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   //     16-byte alignment.
   // Then one tiled TMA reduce-add (or store) replaces eight per-row bulk copies.
   c.tma_c = false;
+  c.tma_ct = false;
   a.cmap = TcOutMap{};
   if (persistent && es == 8 && a.vec_c == 4 && a.M.n >= 1 && a.N.n >= 1 && a.M.s_out[0] == 1) {
     auto fuse_out = [](const TcDims& cls, std::vector<int64_t>* ext, std::vector<int64_t>* str) {
@@ -360,6 +361,8 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       for (size_t d = 1; d < ne.size(); ++d, ++r) { o.ext[r] = (uint32_t)ne[d]; o.stride[r] = ns[d]; }
       for (size_t d = 1; d < me.size(); ++d, ++r) { o.ext[r] = (uint32_t)me[d]; o.stride[r] = ms[d]; }
       c.tma_c = true;
+      // a whole tile is a box too when its bn rows stay inside N's fastest fused dimension
+      c.tma_ct = ne.size() == 1 || ne[0] % bn == 0;
     }
   }
 
@@ -394,7 +397,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
-      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false")
+      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false") << ",\"tma_ct\":" << (p.choice.tma_ct ? "true" : "false")
       << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"epi_run\":" << a.epi_run << ",\"epi_n_span\":" << a.epi_n_span << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches

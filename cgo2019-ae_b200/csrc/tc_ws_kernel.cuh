@@ -99,7 +99,11 @@ struct WsCfg {
   static constexpr int WM = BM / WGM, WN = BN / WGN;
   static constexpr int CONSUMER_THREADS = CW * 32;
   static constexpr int THREADS = 64;            // producer threads per group
-  static constexpr int CTA_THREADS = GROUPS * (CONSUMER_THREADS + THREADS);
+  // Whole-tile output (below) pays on the 64 x 96 tile, whose six consumer warps otherwise queue 24 small
+  // copies per tile; on 128 x 64 the extra warpgroup costs the consumers registers and measured slower.
+  static constexpr bool TILE_OUT = BN == 96;
+  static constexpr int STORE_THREADS = TILE_OUT ? 128 : 0;  // one more warpgroup: its first lane issues those copies
+  static constexpr int CTA_THREADS = GROUPS * (CONSUMER_THREADS + THREADS) + STORE_THREADS;
   static constexpr int LDK = BK + 2;            // pitch of a contraction-major image (18 = 2 mod 16: conflict-free)
   static constexpr int LDX = MODEX == LM_K_VEC ? LDK : MODEX == LM_TMA_K ? BK : BM + 4;
   static constexpr int LDY = MODEY == LM_K_VEC ? LDK : MODEY == LM_TMA_K ? BK : BN + 4;
@@ -113,7 +117,9 @@ struct WsCfg {
   static constexpr uint32_t TMA_BYTES = (MODEX == LM_TMA_K ? BM * BK * 8 : 0) + (MODEY == LM_TMA_K ? BN * BK * 8 : 0);
   static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);
   static constexpr int TABLE_ELEMS = 2 * BM + 2 * BN;            // offx_m, offc_m, offy_n, offc_n
-  static constexpr int NBARS = GROUPS * (2 * STAGES + 4);
+  // per group: full[STAGES], empty[STAGES], tab_full[2], tab_empty[2]; then staged[2], cfree, and eight
+  // words used as the mailbox of tile coordinates (two groups x eight ints)
+  static constexpr int NBARS = GROUPS * (2 * STAGES + 4) + 3 + 8;
   // Epilogue staging for the bulk reduce: per consumer warp 8 rows of WM outputs, pitch WM+2
   // (16-byte aligned rows, conflict-free 16-byte writes).
   static constexpr int CPITCH = WM + 2;
@@ -122,13 +128,20 @@ struct WsCfg {
   // two staging batches per warp (the copies of one batch drain while the next is written) where they fit
   static constexpr int CBUF = BASE_BYTES + GROUPS * CW * 2 * CBATCH_ELEMS * 8 <= 232448 - 1024 ? 2 : 1;
   static constexpr int CSTAGE_ELEMS = CBUF * CBATCH_ELEMS;
-  static constexpr int SMEM_BYTES = BASE_BYTES + GROUPS * CW * CSTAGE_ELEMS * 8;
+  // Where a whole BM x BN tile fits beside the stages, ONE staging area shared by both groups takes a tile at
+  // a time ([n][m], dense): the consumers only write it, a separate thread issues the single tiled TMA copy
+  // and waits for it to be read, so no consumer waits for the copy engine.
+  static constexpr bool TILE_OK = TILE_OUT && BASE_BYTES + BM * BN * 8 <= 232448 - 1024;
+  static constexpr int CREGION_ELEMS =
+      (TILE_OK && BM * BN > GROUPS * CW * CSTAGE_ELEMS) ? BM * BN : GROUPS * CW * CSTAGE_ELEMS;
+  static constexpr int SMEM_BYTES = BASE_BYTES + CREGION_ELEMS * 8;
   // Registers follow the roles.  The CTA starts with LAUNCH_REGS per thread (what fits 64 K registers, in
   // units of 8); producers shrink to PRODUCER_REGS and the consumers share what that frees.
   static constexpr int LAUNCH_REGS = (65536 / CTA_THREADS) / 8 * 8 > 255 ? 248 : (65536 / CTA_THREADS) / 8 * 8;
-  static constexpr int PRODUCER_REGS = 56;
+  static constexpr int PRODUCER_REGS = 56, STORE_REGS = 40;
   static constexpr int CONSUMER_REGS_RAW =
-      (LAUNCH_REGS + (LAUNCH_REGS - PRODUCER_REGS) * GROUPS * THREADS / (GROUPS * CONSUMER_THREADS)) / 8 * 8;
+      (LAUNCH_REGS * CTA_THREADS - PRODUCER_REGS * GROUPS * THREADS - STORE_REGS * STORE_THREADS) /
+      (GROUPS * CONSUMER_THREADS) / 8 * 8;
   static constexpr int CONSUMER_REGS = CONSUMER_REGS_RAW > 224 ? 224 : CONSUMER_REGS_RAW;
 };
 
@@ -271,14 +284,18 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   double* stages = reinterpret_cast<double*>(smem_raw);  // first: TMA images need 1024-byte alignment
   double* cstages = stages + CF::GROUPS * CF::STAGES * CF::STAGE_ELEMS;
-  int64_t* tables = reinterpret_cast<int64_t*>(cstages + CF::GROUPS * CF::CW * CF::CSTAGE_ELEMS);
+  int64_t* tables = reinterpret_cast<int64_t*>(cstages + CF::CREGION_ELEMS);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tables + CF::GROUPS * 2 * CF::TABLE_ELEMS);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   constexpr int CW = CF::CW;
-  const bool is_producer = warp >= 2 * CW;
-  const int gi = is_producer ? (warp - 2 * CW) >> 1 : warp / CW;  // group served
+  const bool is_store = CF::STORE_THREADS > 0 && warp >= 2 * CW + 4;
+  const bool is_producer = !is_store && warp >= 2 * CW;
+  const int gi = is_producer ? (warp - 2 * CW) >> 1 : is_store ? 0 : warp / CW;  // group served
+  uint64_t* staged = bars + CF::GROUPS * (2 * STAGES + 4);  // [2] a group's tile is in the shared staging area
+  uint64_t* cfree = staged + 2;                             // the staging area has been read out once more
+  int* mailbox = reinterpret_cast<int*>(cfree + 1);         // [2][8] tensor coordinates of the staged tile
   uint64_t* full = bars + gi * (2 * STAGES + 4);             // [STAGES]
   uint64_t* empty = full + STAGES;                           // [STAGES]
   uint64_t* tab_full = empty + STAGES;                       // [2]
@@ -292,6 +309,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       for (int s = 0; s < STAGES; ++s) { mbar_init(b + s, CF::FULL_ARRIVALS); mbar_init(b + STAGES + s, CW); }
       for (int s = 0; s < 2; ++s) { mbar_init(b + 2 * STAGES + s, CF::THREADS); mbar_init(b + 2 * STAGES + 2 + s, CW); }
     }
+    mbar_init(staged, CW);
+    mbar_init(staged + 1, CW);
+    mbar_init(cfree, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -301,6 +321,45 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const int nk = (int)((p.Kflat + BK - 1) / BK);
   const uint32_t kend = p.Kflat;
   const bool accumulate = p.beta != 0;
+
+  // Whole-tile output: the geometry allows it, the kernel has the room, and the epilogue is the bulk one.
+  const bool tile_out = CF::TILE_OK && p.c_tensor == 2 && p.c_mode == 2;
+
+  if (is_store) {
+    // --------------------------------------------------------------- store ----
+    // One thread takes the staged tiles in the fixed order group 0, group 1, group 0, ... (the order in which
+    // the consumers are allowed to fill the area), issues one tiled TMA reduce-add / store per tile and
+    // releases the area once the copy engine has read it.
+    reg_dec<CF::STORE_REGS>();
+    if (!tile_out || warp != 2 * CW + 4 || (tid & 31) != 0) return;
+    const uint64_t tmap = reinterpret_cast<uint64_t>(&p.tmap_ct);
+    const uint32_t src = smem_u32(cstages);
+    for (uint32_t t = 0;; ++t) {
+      bool any = false;
+      for (int g = 0; g < 2; ++g) {
+        if (2u * blockIdx.x + g + t * step >= total) continue;
+        any = true;
+        if (!mbar_wait(&staged[g], t & 1, p.status, 6)) return;
+        const int* mb = mailbox + g * 8;
+        if (accumulate)
+          asm volatile(
+              "cp.reduce.async.bulk.tensor.5d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];\n" ::"l"(tmap),
+              "r"(mb[0]), "r"(0), "r"(mb[2]), "r"(mb[3]), "r"(mb[4]), "r"(src)
+              : "memory");
+        else
+          asm volatile(
+              "cp.async.bulk.tensor.5d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];\n" ::"l"(tmap),
+              "r"(mb[0]), "r"(0), "r"(mb[2]), "r"(mb[3]), "r"(mb[4]), "r"(src)
+              : "memory");
+        asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        mbar_arrive(cfree);
+      }
+      if (!any) break;
+    }
+    asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
+    return;
+  }
 
   if (is_producer) {
     // ------------------------------------------------------------ producer ----
@@ -364,6 +423,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const double alpha = p.alpha;
   uint32_t it = 0, titer = 0;
 #ifdef TC_WS_TIMING
+  long long tm_wait_ks[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tm_fence = 0;
   long long tm_wait = 0, tm_mma = 0, tm_epi = 0, tm_rd = 0, tm_tab = 0, tm_tiles = 0;
   const long long tm_begin = clock64();
 #define TM_NOW() clock64()
@@ -411,6 +471,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 #ifdef TC_WS_TIMING
       const long long tm1 = TM_NOW();
       tm_wait += tm1 - tm0;
+      if (ks < 8) tm_wait_ks[ks] += tm1 - tm0;
 #endif
       const double* xs = gstage + s * CF::STAGE_ELEMS;
       const double* ys = xs + CF::XIMG;
@@ -467,7 +528,44 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // TMA reduce-add (or store) per batch replaces eight per-row copies.  Rows and columns beyond the tensor are
     // clipped by the copy engine; boxes that lie outside altogether are not issued.
     const uint32_t m_idx = (tile % p.tiles_m) * BM + wm0, n_base = (tile / p.tiles_m) * BN + wn0;
-    if (p.c_tensor && p.c_mode == 2 && !from_c) {
+    if (tile_out) {
+      // Whole tile through the shared staging area, filled in the order g0, g1, g0, ...: use number u may start
+      // once use u - 1 has been read out.  After the first wait the two groups stay out of phase.
+      const uint32_t u = 2u * titer + gi;
+      if (u > 0 && !mbar_wait(cfree, (u - 1) & 1, p.status, 7)) return;
+      double* tb = cstages;
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        double* row = tb + (wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)) * BM + wm0 + 4 * t;
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          double2* dst = reinterpret_cast<double2*>(row + 16 * i);
+          dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
+          dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        if (cw == 0) {
+          const uint32_t m0t = m_idx - wm0, n0t = n_base - wn0;
+          const uint32_t e0 = p.cmap.e0, f0 = p.cmap.f0;
+          const int ne = p.cmap.ne, me = p.cmap.me;
+          int x3 = 0, x4 = 0;
+          const uint32_t rm = m0t / e0, rn = n0t / f0;
+          if (me == 2) { x3 = (int)(rm % p.cmap.ext[0]); x4 = (int)(rm / p.cmap.ext[0]); }
+          else if (me == 1) { if (ne == 0) x3 = (int)rm; else x4 = (int)rm; }
+          if (ne == 2) { x3 = (int)(rn % p.cmap.ext[0]); x4 = (int)(rn / p.cmap.ext[0]); }
+          else if (ne == 1) x3 = (int)rn;
+          int* mb = mailbox + gi * 8;
+          mb[0] = (int)(m0t % e0);
+          mb[2] = (int)((n0t % f0) >> 1);
+          mb[3] = x3;
+          mb[4] = x4;
+        }
+        mbar_arrive(&staged[gi]);  // release: the mailbox and this warp's part of the tile are visible
+      }
+    } else if (p.c_tensor && p.c_mode == 2 && !from_c) {
       if (m_idx < p.Mflat) {
         double* cst = cstages + (gi * CW + cw) * CF::CSTAGE_ELEMS;
         const uint64_t tmap = reinterpret_cast<uint64_t>(&p.tmap_c);
@@ -494,8 +592,14 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int nb = 2 * j + h;
+#ifdef TC_WS_TIMING
+            const long long tm4 = TM_NOW();
+#endif
             asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
             __syncwarp();
+#ifdef TC_WS_TIMING
+            tm_rd += TM_NOW() - tm4;
+#endif
             double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;  // dense rows of WM: the box image
 #pragma unroll
             for (int i = 0; i < MB2; ++i) {
@@ -503,8 +607,14 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
               dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
               dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
             }
+#ifdef TC_WS_TIMING
+            const long long tm5 = TM_NOW();
+#endif
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
+#ifdef TC_WS_TIMING
+            tm_fence += TM_NOW() - tm5;
+#endif
             if (lane == 0) {
               const uint32_t src = smem_u32(cbuf);
               if (accumulate)
@@ -639,6 +749,11 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   if (p.ws && lane == 0 && cw < 4) {
     long long* o = reinterpret_cast<long long*>(p.ws) + ((blockIdx.x * 2 + gi) * 4 + cw) * 8;
     o[0] = TM_NOW() - tm_begin; o[1] = tm_wait; o[2] = tm_mma; o[3] = tm_epi; o[4] = tm_rd; o[5] = tm_tab; o[6] = tm_tiles;
+    o[7] = tm_fence;
+    if (blockIdx.x == 0 && cw == 0) {
+      long long* w = reinterpret_cast<long long*>(p.ws) + 148 * 64 + 240 + gi * 8;
+      for (int i = 0; i < 8; ++i) w[i] = tm_wait_ks[i];
+    }
   }
 #endif
   asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // outstanding bulk copies of this thread

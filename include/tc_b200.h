@@ -61,7 +61,7 @@ typedef struct tc_options {
                    /*   kernels, rows contiguous in the output; falls back to 1 elsewhere)   */
   int tma;         /* tiled TMA copies in the persistent fp64 kernel (operand tiles that are plain 2-D boxes;
                       output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
-                      2 = operands only, 3 = output only */
+                      2 = operands only, 3 = output only, 4 = both but the output per warp, never per tile */
 } tc_options;
 
 typedef struct tc_plan tc_plan;
