@@ -47,8 +47,8 @@ WORKLOADS = {
 METRIC = "GFLOP/s per contraction"
 # DRAM bytes one launch of the workload's kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture, summarised under profiles/); cfg5 is 8 x the captured one-eighth slab.
-NCU_TRAFFIC_BYTES = {"cfg2": 1983567872, "cfg3": 1341919744, "cfg4": 1472908800,
-                     "cfg5_shard8": 8384225280, "cfg5": 8 * 8384225280}
+NCU_TRAFFIC_BYTES = {"cfg2": 1984793088, "cfg3": 1341919744, "cfg4": 1472908800,
+                     "cfg5_shard8": 8369612032, "cfg5": 8 * 8369612032}
 
 
 def measured_peaks():

@@ -103,6 +103,8 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       tstr[t] = p->strides[t];
       for (int64_t s : tstr[t])
         if (s <= 0) { *why = "strides must be positive"; return TC_ERR_EXTENT; }
+      // strides that merely restate the compact layout keep the plan eligible for everything compact plans get
+      if (tstr[t] == compact_strides(*tidx[t], *p)) p->custom_strides[t] = false;
     } else {
       tstr[t] = compact_strides(*tidx[t], *p);
     }
