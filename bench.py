@@ -9,9 +9,12 @@ flops per pass), whole job.
 
   N = 1   workload "cfg2" (fp64, C[a,b,c,d] += sum(e) A[a,e,b,d] B[e,c], extents 96).
           The other configurations are measured briefly and listed under "configs".
-  N > 1   workload "cfg5" (fp64 6-D, extents 40, 32.8 GB of output) cut along its
-          slowest output index f, one contiguous slab of C per rank, no communication;
-          total work is fixed, so "scaling" is "strong".
+  N > 1   the same "cfg2" with its slowest output index d extended to 96 N and cut into
+          N contiguous slabs, one cfg2-sized slab of C per rank, no communication: per-GPU
+          work is fixed, so "scaling" is "weak" and the N = 1 line is its first point.
+          The partitioned configuration "cfg5" (fp64 6-D, extents 40, 32.8 GB of output,
+          cut along f; total work fixed) is timed in the same run on N GPUs and on rank 0
+          alone, and listed under "configs" with its parallel efficiency.
 
 The timed region holds exactly K passes on device-resident tensors (larger than
 L2), between barrier + synchronize pairs, timed with CUDA events on the stream
@@ -154,6 +157,62 @@ def quick_config(pkg, orc, torch, name, steps=5):
             "algorithmic_gbs": nbytes * steps / sec * 1e-9, "kernel": d["kernel"]}
 
 
+def host_threads(orc):
+    """Host cores this process may use.  torchrun exports OMP_NUM_THREADS=1 to its ranks, which would make
+    OpenMP report one thread; the CPU arm uses the cores the process is allowed on instead."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return max(n, orc.max_threads())
+
+
+def weak_cfg2(world):
+    """cfg2 with its slowest output index extended so that every rank owns a cfg2-sized slab."""
+    return WORKLOADS["cfg2"][0].replace("d,96", "d,%d" % (96 * world))
+
+
+def workload_label(name, world):
+    return name if world == 1 or name != "cfg2" else "cfg2 x %d (d = 96 x %d, one cfg2-sized slab per GPU)" % (world, world)
+
+
+def strong_scaling_cfg5(pkg, shard, torch, dist, rank, world, stream, steps=5):
+    """cfg5 cut along its slowest output index over all ranks (max over ranks), then whole on rank 0 alone."""
+    expr, dtype, seed = WORKLOADS["cfg5"]
+
+    def timed(r, w, barrier):
+        sh = shard.ExternalShard(expr, pkg.F64, r, w)
+        g = sh.geom
+        nc, na, nb = g.full_sizes
+        dc = torch.empty(g.c_slab_elems, dtype=torch.float64, device="cuda")
+        da = torch.empty(na, dtype=torch.float64, device="cuda")
+        db = torch.empty(nb, dtype=torch.float64, device="cuda")
+        pkg.fill_uniform(dc, seed, 0, first_index=g.offsets[0])
+        pkg.fill_uniform(da, seed, 1)
+        pkg.fill_uniform(db, seed, 2)
+        sh.plan.commit()
+        sec = time_passes(torch, lambda: sh.execute(dc, da, db, stream=stream, c_is_slab=True), steps, 3,
+                          dist.barrier if barrier else None)
+        sh.plan.close()
+        del dc, da, db
+        torch.cuda.empty_cache()
+        return sec / steps
+
+    flops = 2.0 * 40.0 ** 7
+    sec_n = timed(rank, world, True)
+    t = torch.tensor([sec_n], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec_n = float(t.item())
+    sec_1 = timed(0, 1, False) if rank == 0 else 0.0
+    dist.barrier()
+    if rank != 0:
+        return None
+    return {"workload": "cfg5", "dtype": "f64", "scaling": "strong", "n_gpus": world,
+            "sharding": "output index f cut into %d contiguous slabs, no communication" % world,
+            "gflops": flops / sec_n * 1e-9, "ms": sec_n * 1e3, "ms_one_gpu": sec_1 * 1e3,
+            "gflops_one_gpu": flops / sec_1 * 1e-9, "parallel_efficiency": sec_1 / (world * sec_n)}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -169,8 +228,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    name = args.workload or ("cfg2" if world == 1 else "cfg5")
+    name = args.workload or "cfg2"
     expr, dtype, seed = WORKLOADS[name]
+    if world > 1 and name == "cfg2":
+        expr = weak_cfg2(world)  # one cfg2-sized slab per rank
     tdt = torch.float64 if dtype == "f64" else torch.float32
     es = 8 if dtype == "f64" else 4
     stream = torch.cuda.current_stream().cuda_stream
@@ -246,6 +307,12 @@ def run_ours(args):
     hplan.close()
     del hc, ha, hb
 
+    strong = None
+    if world > 1 and not args.workload:
+        del dc, da, db
+        torch.cuda.empty_cache()
+        strong = strong_scaling_cfg5(pkg, shard, torch, dist, rank, world, stream)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -267,7 +334,7 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": shard_bytes / launch_s * 1e-9, "peak": hbm_peak, "unit": "GB/s",
                 "peak_source": "MEASURED_PEAKS.json hbm_gbs (of %s)" % hbm_src}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name) if world == 1 else None
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name) if world == 1 or name == "cfg2" else None  # per launch: every rank runs a cfg2-sized slab
     roof["kernel"] = desc["kernel"]
     roof["algorithmic_bytes_per_launch"] = shard_bytes
     roof["algorithmic_flops_per_launch"] = shard_flops
@@ -277,8 +344,8 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": name, "expression": expr, "seed": seed,
+        "scaling": "weak" if name == "cfg2" or world == 1 else "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": workload_label(name, world), "expression": expr, "seed": seed,
                    "sharding": "output index %s cut into %d contiguous slabs, no communication" % (g.index, world)
                    if world > 1 else "none",
                    "l2": "inputs larger than L2 (%.0f MB touched per pass per GPU)" % (shard_bytes / 2 ** 20),
@@ -298,6 +365,8 @@ def run_ours(args):
             del dc, da, db
             torch.cuda.empty_cache()
             line["configs"] = [quick_config(pkg, orc, torch, n) for n in ("cfg1", "cfg3", "cfg4", "cfg5")]
+    if strong:
+        line["configs"] = [strong]
     print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -350,7 +419,7 @@ def _time_sample(orc, name, count, threads):
 
 def cpu_baseline(orc, name, budget_s):
     """GFLOP/s of the loop nest on all host threads over a sample sized for about budget_s seconds."""
-    threads = orc.max_threads()
+    threads = host_threads(orc)
     sec, flops, what, full = _time_sample(orc, name, 1, threads)
     count = int(max(1, min(full, budget_s / max(sec, 1e-4))))
     if count > 1:
@@ -369,9 +438,9 @@ def run_reference(args):
         orc.lib()
     except ImportError:
         entry._load_script(os.path.join(ROOT, "oracle", "build_oracle.py"), "tc_oracle_build").build_all()
-    name = args.workload or ("cfg2" if world == 1 else "cfg5")
+    name = args.workload or "cfg2"
     expr, dtype, seed = WORKLOADS[name]
-    threads = orc.max_threads()
+    threads = host_threads(orc)
     # size one step so that warm-up + steps stay near two minutes
     per_step = max(0.05, 110.0 / (args.steps + args.warmup))
     t1, _, _, full = _time_sample(orc, name, 1, threads)
@@ -387,8 +456,9 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": name, "expression": expr, "seed": seed},
+        "scaling": "weak" if name == "cfg2" or world == 1 else "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": workload_label(name, world),
+                   "expression": weak_cfg2(world) if world > 1 and name == "cfg2" else expr, "seed": seed},
         "cpu_baseline": {"value": value, "unit": "GFLOP/s", "cores": threads, "kind": "port",
                          "sample": what + "; the reference's CPU loop nest (restated in C, bit-identical to its "
                                           "compiled drivers), OpenMP over the outermost output loop"},

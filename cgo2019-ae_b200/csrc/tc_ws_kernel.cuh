@@ -46,7 +46,7 @@ __device__ __forceinline__ void mbar_arrive_on_copies(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n}\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Tiled TMA load of one 2-D box (no multicast): box corner (c0 = innermost coordinate, c1) of the tensor
+// Tiled TMA load of one 2-D box into this CTA only: box corner (c0 = innermost coordinate, c1) of the tensor
 // described by `tmap` into shared memory at `dst`; completion is signalled on `bar` as transferred bytes.
 // c0 times the element size must be a multiple of 16 bytes; `dst` must be 1024-byte aligned for the
 // 128-byte swizzle the descriptor asks for.
