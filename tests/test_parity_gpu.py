@@ -244,8 +244,10 @@ TENSOR_OUT = [
     "C [a,128,b,32,c,3,d,2] += sum(e,24) * A [e,a,c] * B [b,d,e];",
     "C [a,128,b,3,c,16,d,5] -= sum(e,33) * A [a,e,b] * B [e,c,d];",
     "C [a,64,b,2,c,96] += sum(e,32) * A [a,e,b] * B [e,c];",
-    # N's fastest dimension is not a multiple of 16 while N has two dimensions: must fall back
+    # (b, c) are contiguous in C, not in B: one N dimension of 96 for the output view
     "C [a,128,b,24,c,4] += sum(e,16) * A [e,a] * B [b,e,c];",
+    # N's fastest dimension is not a multiple of 16 while N has two dimensions: must fall back
+    "C [a,128,b,24,c,3,d,4] += sum(e,16) * A [e,a,c] * B [b,d,e];",
 ]
 
 

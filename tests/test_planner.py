@@ -69,6 +69,32 @@ def test_tile_choices(pkg):
     assert forced["ksplit"] == 1 and forced["kernel"] == "dmma_ws_128x64"
 
 
+def test_output_tensor_boxes(pkg):
+    """Which outputs the persistent fp64 kernel may write as tiled TMA boxes (per warp batch / per tile)."""
+    d = [_plan(pkg, e, dt).describe() for e, dt, _ in CONFIGS]
+    # cfg2: (a, b) are contiguous in C although not in A: runs of 9216 hold the 64-row tiles; N = c alone
+    assert d[1]["tma_c"] and d[1]["tma_ct"]
+    # cfg5: M and N both fuse into one dimension
+    assert d[4]["tma_c"] and d[4]["tma_ct"]
+    # cfg3: the fastest M dimension (64) is shorter than the 128-row tile
+    assert not d[2]["tma_c"] and not d[2]["tma_ct"]
+    kw = dict(tile=(64, 96), variant=3)
+    # N = (b: 32, d: 2): a batch of 16 rows stays inside b, a 96-row tile does not
+    e = _plan(pkg, "C [a,128,b,32,c,3,d,2] += sum(e,24) * A [e,a,c] * B [b,d,e];", **kw).describe()
+    assert e["tma_c"] and not e["tma_ct"]
+    # N's fastest dimension 24 is not a multiple of 16 and N has a second dimension
+    e = _plan(pkg, "C [a,128,b,24,c,3,d,4] += sum(e,16) * A [e,a,c] * B [b,d,e];", **kw).describe()
+    assert not e["tma_c"]
+    # ... but (b, c) contiguous in C count as one dimension of 96 whatever their order in B
+    e = _plan(pkg, "C [a,128,b,24,c,4] += sum(e,16) * A [e,a] * B [b,e,c];", **kw).describe()
+    assert e["tma_c"] and e["tma_ct"]
+    # odd extent of the only N dimension: n cannot split into (parity, n / 2)
+    e = _plan(pkg, "C [a,128,b,33] += sum(e,16) * A [e,a] * B [e,b];", **kw).describe()
+    assert not e["tma_c"]
+    # fp32 and the one-CTA-per-tile kernels never use them
+    assert not d[3]["tma_c"] and not d[0]["tma_c"]
+
+
 def test_k_split_plans(pkg):
     p = _plan(pkg, "C [a,33,b,17] += sum(c,1000,d,9) * A [a,c,d] * B [d,b,c];")
     d = p.describe()
