@@ -17,7 +17,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtc_b200.so")
 
 F64, F32 = 0, 1
-PATH_AUTO, PATH_DMMA, PATH_DFMA, PATH_FFMA, PATH_3XTF32 = 0, 1, 2, 3, 4
+PATH_AUTO, PATH_DMMA, PATH_DFMA, PATH_FFMA, PATH_3XTF32, PATH_TCGEN05 = 0, 1, 2, 3, 4, 5
 TENSOR_OUT, TENSOR_LEFT, TENSOR_RIGHT = 0, 1, 2
 
 PEAK_NAMES = {0: "dmma_m8n8k4", 1: "dmma_m16n8k4", 2: "dmma_m16n8k8", 3: "dmma_m16n8k16",

@@ -243,7 +243,7 @@ extern "C" int tc_plan_create(const char* expr, int dtype, const tc_options* opt
   p->expr = e;
   p->dtype = dtype;
   if (options) p->opt = *options;
-  if (p->opt.path < TC_PATH_AUTO || p->opt.path > TC_PATH_3XTF32 || p->opt.split_k < 0) {
+  if (p->opt.path < TC_PATH_AUTO || p->opt.path > TC_PATH_TCGEN05 || p->opt.split_k < 0) {
     delete p;
     return TC_ERR_INVALID_ARG;
   }

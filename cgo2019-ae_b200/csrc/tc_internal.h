@@ -104,7 +104,7 @@ struct TcKernelArgs {
   int* status;       // device word: 0, or the code of a wait that ran out of polls (persistent kernels)
 };
 
-enum TcMath { TC_MATH_DMMA = 0, TC_MATH_SIMT = 1, TC_MATH_TF32X3 = 2 };
+enum TcMath { TC_MATH_DMMA = 0, TC_MATH_SIMT = 1, TC_MATH_TF32X3 = 2, TC_MATH_TF32TC = 3 };
 
 struct TcKernelChoice {
   int dtype;      // tc_dtype

@@ -52,6 +52,88 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// ---- mbarriers (shared memory), every wait bounded ----
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and *status = code) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  atomicMax(status, code);
+  return false;
+}
+
+// ---- tcgen05: tensor memory and the 5th-generation MMA (inline PTX, one CTA per MMA) ----
+// Tensor-memory address: lane in bits [31:16], column in bits [15:0]; a column holds one 32-bit value per lane.
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {  // one whole warp; cols a power of two >= 32
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {  // the warp that allocated
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// One arrival on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void tc05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A * B^T, A and B in shared memory behind matrix descriptors, TF32 inputs, fp32 accumulate.
+__device__ __forceinline__ void tc05_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+// 16 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane id) into registers.  The load is
+// asynchronous: nothing may touch the destination registers (not even a move) before tc05_wait_ld(), so the
+// values land directly in the caller's floats.
+__device__ __forceinline__ void tc05_ld16(uint32_t taddr, float* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+      : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]), "=f"(v[8]),
+        "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+// Shared-memory matrix descriptor, no swizzle, K-major: 16 bytes hold 4 consecutive k of one row (external), 8
+// rows are contiguous (a 128-byte core matrix); `lbo` bytes lead to the next 4 k, `sbo` bytes to the next 8 rows.
+// (The MN-major form without swizzle returned zeros for TF32 on B200; this form is exact.)
+__device__ __forceinline__ uint64_t umma_desc_k(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+         (1ull << 46);
+}
+// Instruction descriptor of kind::tf32: fp32 accumulate, TF32 inputs, both operands K-major, D is m x n.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// v = hi + lo with hi, lo representable in TF32 (round to nearest on the 13 dropped bits, as cvt.rna.tf32 does).
+__device__ __forceinline__ void split_tf32_bits(float v, float& hi, float& lo) {
+  hi = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xFFFFE000u);
+  const float r = v - hi;
+  lo = __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
+}
+
+
 // D(16x8) += A(16x8) * B(8x8), TF32 inputs, fp32 accumulate.
 __device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -96,13 +178,20 @@ struct Cfg {
   // row pitch: +4 words keeps the fp64 / vector-pipe reads conflict-free, the TF32 fragment reads want +8
   static constexpr int PAD = MATH == TC_MATH_TF32X3 ? 8 : 4;
   static constexpr int LDX = BM + PAD, LDY = BN + PAD;
+  // tcgen05 path: hi and lo TF32 images of both operands for one K step, in the layout the MMA's matrix
+  // descriptors expect; one mbarrier and the tensor-memory address follow them.
+  static constexpr bool TCGEN = MATH == TC_MATH_TF32TC;
+  static constexpr int UMMA_ELEMS = TCGEN ? 2 * BK * (BM + BN) : 0;
+  static constexpr int TMEM_COLS = BM <= 32 ? 32 : BM <= 64 ? 64 : BM <= 128 ? 128 : 256;
   // Contraction offsets of the stages in flight live in a shared ring (filled by
   // cp.async one pipeline depth ahead), so the loaders never wait on global memory.
   static constexpr int KRING = 2 * STAGES - 2;
   // + output offsets of the tile whose C is prefetched into L2 (BM + BN entries)
   static constexpr int TABLE_BYTES = (3 * BM + 3 * BN + KRING * 2 * BK) * 8;
   static constexpr int STAGE_ELEMS = BK * (LDX + LDY);
-  static constexpr int SMEM_BYTES = TABLE_BYTES + STAGES * STAGE_ELEMS * ES;
+  static constexpr int SMEM_BYTES = TABLE_BYTES + (STAGES * STAGE_ELEMS + UMMA_ELEMS) * ES + (TCGEN ? 16 : 0);
+  static_assert(!TCGEN || (BN == 128 && BM % 16 == 0 && BM <= 256 && sizeof(T) == 4 && WARPS_M_ * WARPS_N_ == 8),
+                "tcgen05 path: D is BN (=128 lanes) x BM columns, eight warps");
 };
 
 // ------------------------------------------------------- offset tables ----
@@ -660,6 +749,157 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
           }
         }
       }
+  } else if constexpr (CF::MATH == TC_MATH_TF32TC) {
+    // ---------------- fp32 as three TF32 products on tcgen05, accumulators in tensor memory ----------------
+    // D (tensor memory) has one lane per n (BN = 128) and one column per m (BM): D += Y * X^T.  Each K step the
+    // gathered fp32 images are split once per element into hi and lo TF32 images laid out as 128-byte core
+    // matrices (8 externals x 4 k), one elected thread issues lo*hi, hi*lo and hi*hi for each group of 8 k, and a
+    // commit on an mbarrier tells when the images may be overwritten.  The epilogue reads each lane's BM values
+    // with tcgen05.ld and leaves through the same staged bulk reduce as the other fp32 kernels.
+    constexpr int TCOLS = CF::TMEM_COLS;
+    const int warp = tid >> 5, lane = tid & 31;
+    float* ua_hi = Ys + STAGES * BK * LDY;   // Y: BN rows
+    float* ua_lo = ua_hi + BK * BN;
+    float* ub_hi = ua_lo + BK * BN;          // X: BM rows
+    float* ub_lo = ub_hi + BK * BM;
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(ub_lo + BK * BM);
+    uint32_t* slot = reinterpret_cast<uint32_t*>(mbar + 1);
+    volatile uint32_t* flag = slot + 1;      // 0, or 1 after a wait that ran out of polls
+    const float alpha = (float)p.alpha;
+    if (warp == 0) {
+      tmem_alloc(slot, TCOLS);
+      tmem_relinquish();
+    }
+    if (tid == 0) {
+      mbar_init(mbar, 1);
+      *flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    tc05_fence_before();
+    __syncthreads();
+    tc05_fence_after();
+    const uint32_t tmem = *slot;
+    constexpr uint32_t IDESC = umma_idesc_tf32(BN, BM);
+
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) issue(s);
+    prefetch_next();
+
+    bool gave_up = false;
+    for (int it = 0; it < nk; ++it) {
+      cp_async_wait<STAGES - 2>();
+      // the MMAs of the previous step must have read the images before they are rewritten
+      if (tid == 0 && it > 0 && !mbar_wait(mbar, (uint32_t)(it - 1) & 1u, p.status, 8)) *flag = 1;
+      __syncthreads();
+      if (*flag) { gave_up = true; break; }  // uniform
+      issue_koff(it);
+      issue(it + STAGES - 1);
+      const int st = it % STAGES;
+      const float* xs = Xs + st * BK * LDX;
+      const float* ys = Ys + st * BK * LDY;
+      // Chunk f of an operand with R rows: row r = f % R, the four k = 4 * (f / R) .. + 3; its 16 bytes go to
+      // core matrix (r / 8, f / R), row r % 8.  Lanes walk r: conflict-free reads and writes.
+      for (int f = tid; f < BN * (BK / 4); f += CF::THREADS) {
+        const int r = f % BN, kc = f / BN;
+        const float* src = ys + (4 * kc) * LDY + r;
+        float4 h, l;
+        split_tf32_bits(src[0], h.x, l.x); split_tf32_bits(src[LDY], h.y, l.y);
+        split_tf32_bits(src[2 * LDY], h.z, l.z); split_tf32_bits(src[3 * LDY], h.w, l.w);
+        const int d = ((r >> 3) * (BK / 4) + kc) * 8 + (r & 7);
+        reinterpret_cast<float4*>(ua_hi)[d] = h;
+        reinterpret_cast<float4*>(ua_lo)[d] = l;
+      }
+      for (int f = tid; f < BM * (BK / 4); f += CF::THREADS) {
+        const int r = f % BM, kc = f / BM;
+        const float* src = xs + (4 * kc) * LDX + r;
+        float4 h, l;
+        split_tf32_bits(src[0], h.x, l.x); split_tf32_bits(src[LDX], h.y, l.y);
+        split_tf32_bits(src[2 * LDX], h.z, l.z); split_tf32_bits(src[3 * LDX], h.w, l.w);
+        const int d = ((r >> 3) * (BK / 4) + kc) * 8 + (r & 7);
+        reinterpret_cast<float4*>(ub_hi)[d] = h;
+        reinterpret_cast<float4*>(ub_lo)[d] = l;
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
+      tc05_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc05_fence_after();
+        const int kleft = (int)(kend - (kbeg + it * BK));
+        const int nk8 = kleft >= BK ? BK / 8 : (kleft + 7) / 8;
+        for (int kg = 0; kg < nk8; ++kg) {
+          // two 4-k chunks per MMA: 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
+          const uint64_t ah = umma_desc_k(smem_u32(ua_hi) + kg * 256, 128, (BK / 4) * 128);
+          const uint64_t al = umma_desc_k(smem_u32(ua_lo) + kg * 256, 128, (BK / 4) * 128);
+          const uint64_t bh = umma_desc_k(smem_u32(ub_hi) + kg * 256, 128, (BK / 4) * 128);
+          const uint64_t bl = umma_desc_k(smem_u32(ub_lo) + kg * 256, 128, (BK / 4) * 128);
+          tc05_mma_tf32(tmem, al, bh, IDESC, (it > 0 || kg > 0) ? 1u : 0u);
+          tc05_mma_tf32(tmem, ah, bl, IDESC, 1u);
+          tc05_mma_tf32(tmem, ah, bh, IDESC, 1u);
+        }
+        tc05_commit(mbar);
+      }
+    }
+    cp_async_wait<0>();
+    if (!gave_up) {
+      if (tid == 0 && nk > 0 && !mbar_wait(mbar, (uint32_t)(nk - 1) & 1u, p.status, 9)) *flag = 1;
+      __syncthreads();
+      gave_up = *flag != 0;
+    }
+    // This thread's lane of D: n = 32 * (warp % 4) + lane; warps 0-3 take the first half of the columns, 4-7 the second.
+    constexpr int CPT = BM / 2;
+    static_assert(CPT % 16 == 0, "columns per thread");
+    float v[CPT];
+    const int nl = 32 * (warp & 3) + lane, mbase = (warp >> 2) * CPT;
+    if (!gave_up && nk > 0) {
+      tc05_fence_after();
+#pragma unroll
+      for (int c = 0; c < CPT / 16; ++c)
+        tc05_ld16(tmem + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)(mbase + 16 * c), v + 16 * c);
+      tc05_wait_ld();
+    } else {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) v[c] = 0.f;
+    }
+    tc05_fence_before();
+    __syncthreads();  // every warp has its values: tensor memory and the operand images are free
+    if (warp == 0) tmem_dealloc(tmem, TCOLS);
+    if (gave_up) return;
+
+    if (p.ksplit > 1) {
+      float* ws = reinterpret_cast<float*>(p.ws) +
+                  ((size_t)slice * p.tiles_m * p.tiles_n + (size_t)tile_n * p.tiles_m + tile_m) * (size_t)(BM * BN);
+#pragma unroll
+      for (int c = 0; c < CPT; c += 4)
+        *reinterpret_cast<float4*>(ws + (size_t)nl * BM + mbase + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+      return;
+    }
+    const int E0 = p.epi_run;
+    if (p.c_mode == 2 && E0 > 0 && p.vec_c >= 4 && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
+      float* ctile = Xs;  // BM * BN floats: fits in the stage images plus the MMA images
+      const int run_elems = E0 * BN;
+#pragma unroll
+      for (int c = 0; c < CPT; c += 4) {
+        const int m = mbase + c;
+        *reinterpret_cast<float4*>(ctile + (m / E0) * run_elems + nl * E0 + (m % E0)) =
+            make_float4(alpha * v[c], alpha * v[c + 1], alpha * v[c + 2], alpha * v[c + 3]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      __syncthreads();
+      bulk_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
+      return;
+    }
+    {
+      const int64_t cn = offc_n[nl];
+      if (cn >= 0) {
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const int64_t co = offc_m[mbase + c];
+          if (co < 0) continue;
+          const float c0 = accumulate ? C[cn + co] : 0.f;
+          C[cn + co] = fmaf(alpha, v[c], c0);
+        }
+      }
+    }
   } else {
     // ---------------- vector pipe (FFMA / DFMA) ----------------
     // (BM/8) x (BN/8) threads, 8 x 8 outputs each, as groups of VW contiguous

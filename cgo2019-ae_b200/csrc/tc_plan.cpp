@@ -194,13 +194,14 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   c.dtype = p->dtype;
   const int path = p->opt.path;
   if (p->dtype == TC_F64) {
-    if (path == TC_PATH_FFMA || path == TC_PATH_3XTF32) { *why = "fp32 path requested for an fp64 plan"; return TC_ERR_INVALID_ARG; }
+    if (path == TC_PATH_FFMA || path == TC_PATH_3XTF32 || path == TC_PATH_TCGEN05) { *why = "fp32 path requested for an fp64 plan"; return TC_ERR_INVALID_ARG; }
     c.math = path == TC_PATH_DFMA ? TC_MATH_SIMT : TC_MATH_DMMA;
   } else {
     if (path == TC_PATH_DMMA || path == TC_PATH_DFMA) { *why = "fp64 path requested for an fp32 plan"; return TC_ERR_INVALID_ARG; }
     // AUTO: three TF32 tensor-core products per fp32 product measured faster than FFMA on B200 (the
     // vector-pipe kernel is issue-bound on short contractions) at the same observed error (~3e-7).
-    c.math = path == TC_PATH_FFMA ? TC_MATH_SIMT : TC_MATH_TF32X3;
+    // The tcgen05 form of the same arithmetic (TMEM accumulators) is opt-in: measured beside the mma.sync one.
+    c.math = path == TC_PATH_FFMA ? TC_MATH_SIMT : path == TC_PATH_TCGEN05 ? TC_MATH_TF32TC : TC_MATH_TF32X3;
   }
 
   // Loader per operand.
@@ -275,8 +276,31 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       const int64_t e0 = (a.M.n > 0 && a.M.s_out[0] == 1) ? a.M.extent[0] : 0;
       if (e0 > 0 && e0 % 128 != 0 && 128 % e0 != 0 && (96 % e0 == 0 || e0 % 96 == 0)) bm = 96;
     }
+    if (c.math == TC_MATH_TF32X3 && path == TC_PATH_AUTO && p->opt.split_k <= 1) {
+      // The same three products as tcgen05.mma with the accumulators in tensor memory measured 10 % (K = 24)
+      // to 80 % (K = 2048) faster than the mma.sync form on B200.  Its tiles are bm x 128; it is chosen when
+      // they fill the GPU, almost all of them are whole (ragged tiles leave element by element) and whole
+      // tiles can leave through the staged bulk epilogue.
+      auto mostly_whole = [](int64_t n, int64_t b) { return n % b == 0 || n >= 16 * b; };
+      bool bulk_ok = false;
+      if (a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= 4) {
+        const int64_t e = a.M.extent[0];
+        const int64_t e0 = e % bm == 0 ? bm : (bm % e == 0 ? e : std::gcd<int64_t>(bm, e));
+        const bool n_adjacent = e0 == e && a.N.n > 0 && a.N.s_out[0] == e && (int64_t)a.N.extent[0] >= 128;
+        bulk_ok = e0 % 4 == 0 && (n_adjacent || e0 * es >= 256);
+      }
+      const int64_t ctas_tc = ((mf + bm - 1) / bm) * ((nf + 127) / 128);
+      if (bulk_ok && ctas_tc >= 2 * 148 && mostly_whole(mf, bm) && mostly_whole(nf, 128) &&
+          tc_kernel_exists(TC_F32, TC_MATH_TF32TC, bm, 128, 0)) {
+        c.math = TC_MATH_TF32TC;
+        bn = 128;
+      }
+    }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
-    if (ctas < 2 * 148) { bm = 64; bn = 64; variant = 0; }
+    if (ctas < 2 * 148) {
+      bm = 64; bn = 64; variant = 0;
+      if (c.math == TC_MATH_TF32TC) c.math = TC_MATH_TF32X3;  // no 64-wide tcgen05 tile: same arithmetic on mma.sync
+    }
     if (p->opt.variant > 0) variant = p->opt.variant - 1;
   }
   c.bm = bm;
@@ -298,6 +322,13 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   else if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
   else if (p->opt.split_k == 0 && tiles * 2 <= 148 && ksteps >= 16)
     ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * 148) / tiles, ksteps / 8));
+  // The tensor cores accumulate fp32 with truncation: measured against exact sums on B200 the relative error of
+  // one accumulation chain grows linearly with its length (2e-6 at K = 256, 7e-6 at 1024, 3e-5 at 4096), for
+  // mma.sync and tcgen05 alike, while FFMA stays at 1e-6.  Chains are therefore cut at 512: longer contractions
+  // are sliced and the slices added by the combine kernel in round-to-nearest fp32 (tc_options.split_k >= 1
+  // overrides this, as does TC_PATH_FFMA).
+  if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0)
+    ksplit = std::max<int64_t>(ksplit, std::min<int64_t>((kf + 511) / 512, ksteps));
   int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
   ksplit = (ksteps + chunk_steps - 1) / chunk_steps;
   a.ksplit = (uint32_t)ksplit;
@@ -393,7 +424,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     o << ",\"N\":";
     dims(a.N);
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
-      << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
+      << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")

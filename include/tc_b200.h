@@ -44,7 +44,9 @@ typedef enum tc_path {
   TC_PATH_DMMA = 1,  /* fp64 on the tensor pipe (mma.sync f64)     */
   TC_PATH_DFMA = 2,  /* fp64 on the vector pipe                    */
   TC_PATH_FFMA = 3,  /* fp32 on the vector pipe                    */
-  TC_PATH_3XTF32 = 4 /* fp32 as three TF32 tensor-core products (mma.sync), fp32 accumulate */
+  TC_PATH_3XTF32 = 4, /* fp32 as three TF32 tensor-core products (mma.sync), fp32 accumulate */
+  TC_PATH_TCGEN05 = 5 /* the same three products issued as tcgen05.mma with the accumulators in tensor memory;
+                         problems too small for its 128-wide tiles run on TC_PATH_3XTF32 */
 } tc_path;
 
 typedef struct tc_options {

@@ -274,6 +274,50 @@ def test_persistent_tensor_box_epilogue(pkg, orc, torch_cuda, expr):
         assert np.array_equal(outs[0], outs[1]), (expr, tile)
 
 
+TCGEN05 = [
+    ("C [a,96,b,128] = sum(c,8) * A [a,c] * B [b,c];", (96, 128)),                 # one tile, one group of 8 k
+    ("C [a,96,b,128] += sum(c,16) * A [a,c] * B [b,c];", (96, 128)),               # one full K step
+    ("C [a,128,b,128] -= sum(c,40) * A [c,a] * B [c,b];", (128, 128)),             # three K steps, the last half full
+    ("C [a,200,b,300] -= sum(c,37) * A [c,a] * B [b,c];", (128, 128)),             # ragged tiles: element-wise output
+    ("C [a,200,b,300] += sum(c,37) * A [c,a] * B [b,c];", (96, 128)),
+    ("C [a,24,b,24,c,24,i,8,j,8,k,8] += sum(l,24) * A [l,a,i,j] * B [b,c,k,l];", None),  # the shape of configuration 4
+    ("C [a,48,b,8,c,16] += sum(d,1000,e,3) * A [a,e,d] * B [d,b,c,e];", (96, 128)),      # long contraction
+]
+
+
+@pytest.mark.parametrize("expr,tile", TCGEN05)
+def test_tcgen05_three_tf32_products(pkg, orc, torch_cuda, expr, tile):
+    """fp32 on tcgen05.mma with tensor-memory accumulators: same arithmetic as the mma.sync path, same tolerance."""
+    kw = {"path": pkg.PATH_TCGEN05}
+    if tile:
+        kw["tile"] = tile
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 21, **kw)
+    assert d["math"] == "tf32x3_tcgen05", d
+    assert err <= TOL["float32"], (expr, err, d)
+    # K slices (partials through the workspace) and the read-modify-write output
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 22, split_k=8, **kw)
+    assert err <= TOL["float32"], (expr, "split_k", err, d)
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 23, c_path=1, **kw)
+    assert err <= TOL["float32"], (expr, "c_path 1", err, d)
+
+
+@pytest.mark.parametrize("path", ["tcgen05", "mma.sync", "auto"])
+def test_fp32_long_contractions_stay_within_tolerance(pkg, orc, torch_cuda, path):
+    """Tensor-core fp32 accumulation truncates, so one chain of 8192 products would be off by 7e-5; the planner
+    slices the contraction into chains of at most 512 and the combine kernel adds them in round-to-nearest."""
+    expr = "C [a,96,b,128] = sum(c,8192) * A [c,a] * B [c,b];"
+    kw = {"tcgen05": {"path": pkg.PATH_TCGEN05, "tile": (96, 128)}, "mma.sync": {"path": pkg.PATH_3XTF32, "tile": (96, 128)},
+          "auto": {}}[path]
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 31, **kw)
+    assert d["ksplit"] >= 16, d
+    assert err <= TOL["float32"], (path, err, d)
+
+
+def test_tcgen05_small_problems_use_the_mma_sync_kernel(pkg):
+    d = pkg.Plan("C [a,40,b,40] += sum(c,40) * A [c,a] * B [c,b];", pkg.F32, path=pkg.PATH_TCGEN05).describe()
+    assert d["math"] == "tf32x3" and d["kernel"] == "tf32_64x64"
+
+
 def test_overwrite_ignores_initial_output_even_nan(pkg, orc, torch_cuda):
     torch = torch_cuda
     expr = "C [a,40,b,24] = sum(c,33) * A [c,a] * B [b,c];"

@@ -56,7 +56,13 @@ def test_tile_choices(pkg):
     assert d[2]["kernel"] == "dmma_ws_128x64" and d[2]["tiles"] == [32, 64]
     assert d[4]["kernel"] == "dmma_ws_128x64" and d[4]["tiles"] == [500, 1000]
     # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
-    assert d[3]["math"] == "tf32x3" and d[3]["kernel"] == "tf32_96x128"
+    # (default: the tcgen05 form of the three-TF32 product; the mma.sync form on request or for small problems)
+    assert d[3]["math"] == "tf32x3_tcgen05" and d[3]["kernel"] == "tf32tc_96x128"
+    sync = _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_3XTF32).describe()
+    assert sync["math"] == "tf32x3" and sync["kernel"] == "tf32_96x128"
+    # a 96-wide N leaves a quarter of a 128-wide tcgen05 tile empty and every tile ragged: mma.sync form
+    n96 = _plan(pkg, CONFIGS[1][0], "float32").describe()
+    assert n96["math"] == "tf32x3" and n96["kernel"] == "tf32_96x128"
     ffma = _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_FFMA).describe()
     assert ffma["math"] == "ffma" and ffma["kernel"] == "ffma_96x128"
     assert d[3]["epi_run"] == 24 and d[3]["epi_n_span"] == 576
