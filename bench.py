@@ -50,7 +50,7 @@ WORKLOADS = {
 METRIC = "GFLOP/s per contraction"
 # DRAM bytes one launch of the workload's kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture, summarised under profiles/); cfg5 is 8 x the captured one-eighth slab.
-NCU_TRAFFIC_BYTES = {"cfg2": 1984793088, "cfg3": 1341919744, "cfg4": 1472908800,
+NCU_TRAFFIC_BYTES = {"cfg2": 1984793088, "cfg3": 1341919744, "cfg4": 1472347904,
                      "cfg5_shard8": 8369612032, "cfg5": 8 * 8369612032}
 
 
@@ -237,7 +237,11 @@ def run_ours(args):
     stream = torch.cuda.current_stream().cuda_stream
 
     # This rank's share: the whole contraction, or the slab of the slowest output index.
-    sh = shard.ExternalShard(expr, pkg.F64 if dtype == "f64" else pkg.F32, rank, world)
+    plan_kw = {}
+    if args.path != "auto":  # pin the arithmetic path (the profiles of non-default kernels are made this way)
+        plan_kw["path"] = {"dmma": pkg.PATH_DMMA, "dfma": pkg.PATH_DFMA, "ffma": pkg.PATH_FFMA, "3xtf32": pkg.PATH_3XTF32,
+                           "tcgen05": pkg.PATH_TCGEN05}[args.path]
+    sh = shard.ExternalShard(expr, pkg.F64 if dtype == "f64" else pkg.F32, rank, world, **plan_kw)
     g = sh.geom
     if world > 1 and not g.c_slab_contiguous:
         raise SystemExit("workload %s cannot be cut into contiguous output slabs" % name)
@@ -290,7 +294,7 @@ def run_ours(args):
     hb.copy_(db)
     torch.cuda.synchronize()
     # the host call sees full input tensors and this rank's C slab: a plan over the slab's own extents
-    hplan = g.make_plan(pkg.F64 if dtype == "f64" else pkg.F32)
+    hplan = g.make_plan(pkg.F64 if dtype == "f64" else pkg.F32, **plan_kw)
     hviews = (hc, ha[g.offsets[1]:], hb[g.offsets[2]:])
     hplan.execute_host(*hviews)  # warm-up (also commits the plan)
     sync_all()
@@ -334,7 +338,7 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": shard_bytes / launch_s * 1e-9, "peak": hbm_peak, "unit": "GB/s",
                 "peak_source": "MEASURED_PEAKS.json hbm_gbs (of %s)" % hbm_src}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name) if world == 1 or name == "cfg2" else None  # per launch: every rank runs a cfg2-sized slab
+    roof["traffic"] = NCU_TRAFFIC_BYTES.get(name) if (world == 1 or name == "cfg2") and args.path == "auto" else None  # per launch: every rank runs a cfg2-sized slab
     roof["kernel"] = desc["kernel"]
     roof["algorithmic_bytes_per_launch"] = shard_bytes
     roof["algorithmic_flops_per_launch"] = shard_flops
@@ -474,6 +478,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--path", default="auto", choices=["auto", "dmma", "dfma", "ffma", "3xtf32", "tcgen05"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
