@@ -683,33 +683,35 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         }
       }
     } else {
+      // Any alignment, any strides: the warp's rows pass through its staging buffer so that the read-modify-write
+      // of a row is done by consecutive lanes on consecutive m -- whole sectors per instruction wherever
+      // consecutive m are contiguous in C, which fragment-order accesses of 8 bytes are not.
+      double* cst = cstages + (gi * CW + cw) * CF::CSTAGE_ELEMS;
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // an earlier tile's copies may still read it
+      __syncwarp();
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
-        const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
-        if (cn < 0) continue;
-        if (p.vec_c == 2) {
 #pragma unroll
-          for (int i = 0; i < MB2; ++i)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + 2 * e];
-              if (co < 0) continue;
-              double2* dst = reinterpret_cast<double2*>(C + cn + co);
-              double2 c = make_double2(0.0, 0.0);
-              if (accumulate) c = *dst;
-              *dst = make_double2(fma(alpha, acc[nb][2 * i][e], c.x), fma(alpha, acc[nb][2 * i + 1][e], c.y));
-            }
-        } else {
-#pragma unroll
-          for (int i = 0; i < MB2; ++i)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int64_t co = offc_m[wm0 + 16 * i + 4 * t + q];
-              if (co < 0) continue;
-              const double c = accumulate ? C[cn + co] : 0.0;
-              C[cn + co] = fma(alpha, acc[nb][2 * i + (q & 1)][q >> 1], c);
-            }
+        for (int i = 0; i < MB2; ++i) {
+          double2* dst = reinterpret_cast<double2*>(cst + g * CF::CPITCH + 16 * i + 4 * t);
+          dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
+          dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
         }
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * r + (nb & 1)];
+          if (cn < 0) continue;  // uniform across the warp
+#pragma unroll
+          for (int m = lane; m < WM; m += 32) {
+            const int64_t co = offc_m[wm0 + m];
+            if (co < 0) continue;
+            double* q = C + cn + co;
+            const double v = cst[r * CF::CPITCH + m];
+            *q = accumulate ? v + *q : v;
+          }
+        }
+        __syncwarp();
       }
     }
     __syncwarp();

@@ -208,6 +208,61 @@ def test_cuda_path_against_every_compiled_reference_nest(pkg, orc, torch_cuda):
         plan.close()
 
 
+@pytest.mark.parametrize("extents", ["ragged", "multiples_of_8"])
+def test_every_reference_class_at_kernel_scale(pkg, orc, torch_cuda, extents):
+    """The same 57 expression classes with extents large enough (4-16 M outputs) that the planner picks the
+    kernels the benchmarks run on -- persistent fp64, tcgen05 fp32, tensor-map copies where the shape allows --
+    checked against the checker's loop nest.  Throughput per class goes to gpurun_out/ when that folder exists."""
+    if not orc.ref_available():
+        pytest.skip("the reference's expression table is not built here (oracle/_ref absent)")
+    import json
+    import os
+    torch = torch_cuda
+    rng = np.random.default_rng(77)
+    rows = []
+    kernels = set()
+    for tag, info in sorted(orc.ref_table().items()):
+        p = orc.parse(info["expr"])
+        rank, nsum = len(p["out_idx"]), len(p["sum_idx"])
+        base = {2: 2600, 3: 190, 4: 52, 5: 23, 6: 14}.get(rank, 10)
+        ext = {n: int(base + rng.integers(-base // 8, base // 8 + 1)) for n in p["out_idx"]}
+        kbase = {1: 40, 2: 7, 3: 4}.get(nsum, 3)
+        ext.update({n: int(kbase + rng.integers(0, kbase // 2 + 1)) for n in p["sum_idx"]})
+        if extents == "multiples_of_8":  # the sizes benchmark suites for this operation typically use
+            ext = {n: max(8, (e + 4) // 8 * 8) for n, e in ext.items()}
+        expr = orc.with_extents(info["expr"], ext)
+        dt = "float64" if info["dtype"] == "f64" else "float32"
+        c0, a, b = orc.make_inputs(expr, 900, dt)
+        ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+        plan = pkg.Plan(expr, _dt(pkg, dt))
+        dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+        plan.execute(dc, da, db)
+        torch.cuda.synchronize()
+        d = plan.describe()
+        assert plan.status() == 0, (tag, expr)
+        err = orc.rel_error(dc.cpu().numpy(), ref)
+        assert err <= TOL[dt], (tag, expr, err, d["kernel"])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            plan.execute(dc, da, db)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 3
+        rows.append({"tag": tag, "dtype": info["dtype"], "expr": expr, "kernel": d["kernel"], "ms": ms,
+                     "gflops": d["flops"] / ms * 1e-6, "gbs": d["bytes"] / ms * 1e-6, "rel_err": err,
+                     "tma": [d.get("tma_x"), d.get("tma_y"), d.get("tma_c"), d.get("tma_ct")]})
+        kernels.add(d["kernel"])
+        plan.close()
+        del dc, da, db
+    assert len(rows) == 57
+    assert any(k.startswith("dmma_ws") for k in kernels), kernels
+    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
+    if os.path.isdir(out):
+        with open(os.path.join(out, "sweep_reference_classes_%s.json" % extents), "w") as f:
+            json.dump(rows, f, indent=1)
+
+
 EDGE = [
     "C [a,1,b,1] += sum(c,1) * A [c,a] * B [b,c];",                         # everything is a scalar
     "C [a,5] += sum(b,7) * A [b,a] * B [b];",                               # right operand has no external index
