@@ -162,6 +162,46 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   dn = fuse(dn);
   dk = fuse(dk);
 
+  // Operand-friendly orders.  By output stride alone, an operand whose own fastest index is an external one that
+  // comes late in the output would be gathered 8 bytes per sector (the reference's mapping search blocks two
+  // indices in that situation, cogent/src/algs/bases/enumeration.py:72-278).  Tiles here are ranges of the
+  // flattened class, so the same effect comes from the ORDER of the class's dimensions:
+  //   * N, fp64 (never holds the output's fastest index): ordered by stride in Y when Y's fastest index is external;
+  //   * M, fp64: the output's fastest index a and X's fastest external index x are both split by 4 and the digits
+  //     ordered (a_lo, x_lo, a_hi, ..., x_hi): a thread still owns 4 consecutive output elements (32 bytes), and
+  //     the 4 lanes that share an a_lo fetch 4 consecutive x, one whole sector of X.  (Putting x_lo first made
+  //     the loads 16-byte vectors but sent the output through the element-wise epilogue: measured slower.)
+  if (p->dtype == TC_F64 && !y_k_unit && dn.size() > 1) {  // (the fp32 epilogues lean on N's order in the output)
+    bool y_ext_unit = false;
+    for (const Dim& d : dn) y_ext_unit = y_ext_unit || (d.extent > 1 && d.s_in == 1);
+    if (y_ext_unit && dn[0].s_in != 1) {
+      std::stable_sort(dn.begin(), dn.end(), [](const Dim& a, const Dim& b) { return a.s_in < b.s_in; });
+      dn = fuse(dn);
+    }
+  }
+  if (p->dtype == TC_F64 && !x_k_unit && dm.size() > 1 && dm[0].s_in != 1 && dm[0].s_out == 1 && dm[0].extent % 4 == 0) {
+    for (size_t j = 1; j < dm.size(); ++j) {
+      if (dm[j].s_in != 1 || dm[j].extent < 4 || dm[j].extent % 4 != 0) continue;
+      if (dm.size() + 2 > (size_t)TC_MAX_DIMS) break;
+      // only when a 128-row tile in output order would hold at most two values of x: with short faster
+      // dimensions the tile reaches x by itself and keeps the cheaper row-wise output
+      int64_t before = 1;
+      for (size_t i = 0; i < j; ++i) before *= dm[i].extent;
+      if (before < 64) break;
+      const Dim o = dm[0], x = dm[j];
+      std::vector<Dim> r;
+      r.push_back({4, o.s_in, o.s_out});            // 4 consecutive output elements: 32 bytes of C per thread
+      r.push_back({4, x.s_in, x.s_out});            // 4 consecutive x: one whole sector of X per 4 lanes
+      if (o.extent / 4 > 1) r.push_back({o.extent / 4, o.s_in * 4, o.s_out * 4});
+      for (size_t i = 1; i < dm.size(); ++i) {
+        if (i != j) r.push_back(dm[i]);
+        else if (x.extent / 4 > 1) r.push_back({x.extent / 4, x.s_in * 4, x.s_out * 4});
+      }
+      dm = r;
+      break;
+    }
+  }
+
   TcKernelArgs& a = p->args;
   std::memset(&a, 0, sizeof(a));
   int64_t mf = 1, nf = 1, kf = 1;
