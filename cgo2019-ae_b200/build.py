@@ -35,7 +35,8 @@ def _generate_kernel_units():
     for m in re.finditer(r"^\s*X\((\w+),\s*(\w+),\s*(\w+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", text, re.M):
         name, t, math, bm, bn, wm, wn, st, minb, _variant = m.groups()
         body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'
-                "TC_DEFINE_INST(tc_inst_%s, %s, %s, %s, %s, %s, %s, %s, %s)\n" % (name, t, math, bm, bn, wm, wn, st, minb))
+                "%s(tc_inst_%s, %s, %s, %s, %s, %s, %s, %s, %s)\n"
+                % ("TC_DEFINE_INST_KV" if math == "TC_MATH_TF32TC" else "TC_DEFINE_INST", name, t, math, bm, bn, wm, wn, st, minb))
         path = os.path.join(OBJ, "gen_%s.cu" % name)
         if not os.path.exists(path) or open(path).read() != body:
             with open(path, "w") as f:

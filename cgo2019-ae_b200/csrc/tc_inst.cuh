@@ -92,6 +92,23 @@ int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
     return TC_ERR_INVALID_ARG;                                                                              \
   }
 
+// Kernels with a third loader per operand (16 bytes along the contraction index): modes 0 element, 1 external
+// vector, 2 contraction vector.
+#define TC_KV_CASE(MX, MY, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                                   \
+  if (vx == MX && vy == MY)                                                                                           \
+    return tck::run_variant<tck::Cfg<T, MATH, BM, BN, WMN, WNN, STAGES, MINB, MX == 1, MY == 1, MX == 2, MY == 2>>(     \
+        a, C, X, Y, s, mode, threads, smem);
+#define TC_DEFINE_INST_KV(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                              \
+  extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,                  \
+                      cudaStream_t s, int mode, int* threads, int* smem) {                                           \
+    TC_KV_CASE(0, 0, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) TC_KV_CASE(0, 1, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) \
+    TC_KV_CASE(0, 2, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) TC_KV_CASE(1, 0, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) \
+    TC_KV_CASE(1, 1, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) TC_KV_CASE(1, 2, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) \
+    TC_KV_CASE(2, 0, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) TC_KV_CASE(2, 1, T, MATH, BM, BN, WMN, WNN, STAGES, MINB) \
+    TC_KV_CASE(2, 2, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                                         \
+    return TC_ERR_INVALID_ARG;                                                                                        \
+  }
+
 #define TC_DEFINE_INST(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB)                                                  \
   extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,              \
                       cudaStream_t s, int mode, int* threads, int* smem) {                                       \

@@ -28,9 +28,6 @@
   X(ffma_64x64, float, TC_MATH_SIMT, 64, 64, 1, 1, 4, 4, 0)               \
   X(tf32_128x128, float, TC_MATH_TF32X3, 128, 128, 2, 4, 4, 2, 0)          \
   X(tf32_96x128, float, TC_MATH_TF32X3, 96, 128, 2, 4, 4, 2, 0)            \
-  X(tf32_96x64, float, TC_MATH_TF32X3, 96, 64, 2, 2, 4, 4, 0)              \
-  X(tf32_96x64s3, float, TC_MATH_TF32X3, 96, 64, 2, 2, 3, 5, 1)            \
-  X(tf32_48x128, float, TC_MATH_TF32X3, 48, 128, 1, 4, 4, 4, 0)            \
   X(tf32tc_96x128, float, TC_MATH_TF32TC, 96, 128, 2, 4, 2, 3, 0)          \
   X(tf32tc_128x128, float, TC_MATH_TF32TC, 128, 128, 2, 4, 2, 3, 0)        \
   X(tf32_64x64, float, TC_MATH_TF32X3, 64, 64, 2, 2, 4, 4, 0)

@@ -126,11 +126,11 @@ __device__ __forceinline__ uint64_t umma_desc_k(uint32_t saddr, uint32_t lbo, ui
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-// v = hi + lo with hi, lo representable in TF32 (round to nearest on the 13 dropped bits, as cvt.rna.tf32 does).
+// v = hi + lo: hi is v rounded to TF32 (nearest, on the 13 dropped bits, as cvt.rna.tf32 does); lo = v - hi is exact
+// in fp32 and is left as it is -- the tensor core reads its upper 19 bits, an error of at most 2^-21 |v|.
 __device__ __forceinline__ void split_tf32_bits(float v, float& hi, float& lo) {
   hi = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xFFFFE000u);
-  const float r = v - hi;
-  lo = __uint_as_float((__float_as_uint(r) + 0x1000u) & 0xFFFFE000u);
+  lo = v - hi;
 }
 
 
@@ -159,7 +159,8 @@ template <> struct Vec16<double> { using type = double2; static constexpr int W 
 template <> struct Vec16<float> { using type = float4; static constexpr int W = 4; };
 
 // ------------------------------------------------------------ configuration ----
-template <typename T_, int MATH_, int BM_, int BN_, int WARPS_M_, int WARPS_N_, int STAGES_, int MINB_, bool VECX_, bool VECY_>
+template <typename T_, int MATH_, int BM_, int BN_, int WARPS_M_, int WARPS_N_, int STAGES_, int MINB_, bool VECX_, bool VECY_,
+          bool KVX_ = false, bool KVY_ = false>
 struct Cfg {
   using T = T_;
   static constexpr int MATH = MATH_;
@@ -167,6 +168,10 @@ struct Cfg {
   static constexpr int STAGES = STAGES_;
   static constexpr int MIN_CTAS = MINB_;
   static constexpr bool VECX = VECX_, VECY = VECY_;
+  // tcgen05 path only: the operand's fastest index is the contracted one and is fetched 16 bytes at a time into a
+  // contraction-major image [external][k], pitch BK + 4 (conflict-free 16-byte reads by consecutive rows)
+  static constexpr bool KVX = KVX_, KVY = KVY_;
+  static constexpr int LDKV = 16 + 4;
   static constexpr int ES = (int)sizeof(T);
   static constexpr int VW = 16 / ES;  // elements per 16 bytes
   // DMMA: WARPS_M x WARPS_N warps, each a (BM/WARPS_M) x (BN/WARPS_N) tile.
@@ -188,7 +193,8 @@ struct Cfg {
   static constexpr int KRING = 2 * STAGES - 2;
   // + output offsets of the tile whose C is prefetched into L2 (BM + BN entries)
   static constexpr int TABLE_BYTES = (3 * BM + 3 * BN + KRING * 2 * BK) * 8;
-  static constexpr int STAGE_ELEMS = BK * (LDX + LDY);
+  static constexpr int XIMG = KVX ? BM * LDKV : BK * LDX, YIMG = KVY ? BN * LDKV : BK * LDY;
+  static constexpr int STAGE_ELEMS = XIMG + YIMG;
   static constexpr int SMEM_BYTES = TABLE_BYTES + (STAGES * STAGE_ELEMS + UMMA_ELEMS) * ES + (TCGEN ? 16 : 0);
   static_assert(!TCGEN || (BN == 128 && BM % 16 == 0 && BM <= 256 && sizeof(T) == 4 && WARPS_M_ * WARPS_N_ == 8),
                 "tcgen05 path: D is BN (=128 lanes) x BM columns, eight warps");
@@ -245,6 +251,24 @@ __device__ __forceinline__ void load_stage_vec(typename CF::T* s_stage, const ty
 // transposing scatter.  The thread -> element map does not change from stage to
 // stage, so it is computed once (elem_slots) and kept packed in registers:
 //   bits 0-15 element offset inside the stage image, 16-23 k, 24-31 external.
+// 16-byte loads along the contraction index into a contraction-major image [row][k] (pitch CF::LDKV): four lanes
+// fetch the 64 bytes one row contributes to a K step.  Needs 4 consecutive flattened k to be contiguous and aligned.
+template <class CF, int ROWS>
+__device__ __forceinline__ void load_stage_kvec(typename CF::T* s_stage, const typename CF::T* __restrict__ g,
+                                                const int64_t* s_off, const int64_t* koff, uint32_t k0, uint32_t kend,
+                                                int tid) {
+  static_assert(CF::ES == 4, "fp32 only");
+  constexpr int CH = CF::BK / 4;  // chunks per row
+  const uint32_t sbase = smem_u32(s_stage);
+  for (int f = tid; f < ROWS * CH; f += CF::THREADS) {
+    const int r = f / CH, kc = f % CH;
+    const int64_t eo = s_off[r];
+    const bool ok = eo >= 0 && k0 + 4 * kc < kend;
+    const typename CF::T* src = ok ? g + eo + koff[4 * kc] : g;
+    cp_async16(sbase + (uint32_t)(r * CF::LDKV + 4 * kc) * 4u, src, ok);
+  }
+}
+
 template <class CF, int ROWS, int LD>
 struct ElemSlots {
   static constexpr int SLABS = ROWS * CF::BK / 32;                      // warp-wide groups of 32 elements
@@ -338,7 +362,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
   int64_t* pf_m = kring + CF::KRING * 2 * BK;
   int64_t* pf_n = pf_m + BM;
   T* Xs = reinterpret_cast<T*>(pf_n + BN);
-  T* Ys = Xs + STAGES * BK * LDX;
+  T* Ys = Xs + STAGES * CF::XIMG;
 
   const int tid = threadIdx.x;
   const uint32_t bid = blockIdx.x;
@@ -365,18 +389,20 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
   const int nk = (int)((kend - kbeg + BK - 1) / BK);
   ElemSlots<CF, BM, LDX> slots_x;
   ElemSlots<CF, BN, LDY> slots_y;
-  if constexpr (!CF::VECX) slots_x.init(tid, p.lanes_k_x == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
-  if constexpr (!CF::VECY) slots_y.init(tid, p.lanes_k_y == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
+  if constexpr (!CF::VECX && !CF::KVX) slots_x.init(tid, p.lanes_k_x == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
+  if constexpr (!CF::VECY && !CF::KVY) slots_y.init(tid, p.lanes_k_y == 1 ? 0 : (CF::ES == 8 ? 2 : 3));
   auto issue = [&](int it) {
     if (it < nk) {
       const int st = it % STAGES;
       const uint32_t k0 = kbeg + it * BK;
-      T* xs = Xs + st * BK * LDX;
-      T* ys = Ys + st * BK * LDY;
+      T* xs = Xs + st * CF::XIMG;
+      T* ys = Ys + st * CF::YIMG;
       const int64_t* kx = kring + (it % CF::KRING) * 2 * BK;
-      if constexpr (CF::VECX) load_stage_vec<CF, BM, LDX>(xs, X, offx_m, kx, k0, kend, tid);
+      if constexpr (CF::KVX) load_stage_kvec<CF, BM>(xs, X, offx_m, kx, k0, kend, tid);
+      else if constexpr (CF::VECX) load_stage_vec<CF, BM, LDX>(xs, X, offx_m, kx, k0, kend, tid);
       else slots_x.load(xs, X, offx_m, kx, k0, kend);
-      if constexpr (CF::VECY) load_stage_vec<CF, BN, LDY>(ys, Y, offy_n, kx + BK, k0, kend, tid);
+      if constexpr (CF::KVY) load_stage_kvec<CF, BN>(ys, Y, offy_n, kx + BK, k0, kend, tid);
+      else if constexpr (CF::VECY) load_stage_vec<CF, BN, LDY>(ys, Y, offy_n, kx + BK, k0, kend, tid);
       else slots_y.load(ys, Y, offy_n, kx + BK, k0, kend);
     }
     cp_async_commit();
@@ -758,7 +784,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
     // with tcgen05.ld and leaves through the same staged bulk reduce as the other fp32 kernels.
     constexpr int TCOLS = CF::TMEM_COLS;
     const int warp = tid >> 5, lane = tid & 31;
-    float* ua_hi = Ys + STAGES * BK * LDY;   // Y: BN rows
+    float* ua_hi = Ys + STAGES * CF::YIMG;   // Y: BN rows
     float* ua_lo = ua_hi + BK * BN;
     float* ub_hi = ua_lo + BK * BN;          // X: BM rows
     float* ub_lo = ub_hi + BK * BM;
@@ -795,26 +821,36 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
       issue_koff(it);
       issue(it + STAGES - 1);
       const int st = it % STAGES;
-      const float* xs = Xs + st * BK * LDX;
-      const float* ys = Ys + st * BK * LDY;
+      const float* xs = Xs + st * CF::XIMG;
+      const float* ys = Ys + st * CF::YIMG;
       // Chunk f of an operand with R rows: row r = f % R, the four k = 4 * (f / R) .. + 3; its 16 bytes go to
       // core matrix (r / 8, f / R), row r % 8.  Lanes walk r: conflict-free reads and writes.
       for (int f = tid; f < BN * (BK / 4); f += CF::THREADS) {
         const int r = f % BN, kc = f / BN;
-        const float* src = ys + (4 * kc) * LDY + r;
+        float4 v4;
+        if constexpr (CF::KVY) v4 = *reinterpret_cast<const float4*>(ys + r * CF::LDKV + 4 * kc);
+        else {
+          const float* src = ys + (4 * kc) * LDY + r;
+          v4 = make_float4(src[0], src[LDY], src[2 * LDY], src[3 * LDY]);
+        }
         float4 h, l;
-        split_tf32_bits(src[0], h.x, l.x); split_tf32_bits(src[LDY], h.y, l.y);
-        split_tf32_bits(src[2 * LDY], h.z, l.z); split_tf32_bits(src[3 * LDY], h.w, l.w);
+        split_tf32_bits(v4.x, h.x, l.x); split_tf32_bits(v4.y, h.y, l.y);
+        split_tf32_bits(v4.z, h.z, l.z); split_tf32_bits(v4.w, h.w, l.w);
         const int d = ((r >> 3) * (BK / 4) + kc) * 8 + (r & 7);
         reinterpret_cast<float4*>(ua_hi)[d] = h;
         reinterpret_cast<float4*>(ua_lo)[d] = l;
       }
       for (int f = tid; f < BM * (BK / 4); f += CF::THREADS) {
         const int r = f % BM, kc = f / BM;
-        const float* src = xs + (4 * kc) * LDX + r;
+        float4 v4;
+        if constexpr (CF::KVX) v4 = *reinterpret_cast<const float4*>(xs + r * CF::LDKV + 4 * kc);
+        else {
+          const float* src = xs + (4 * kc) * LDX + r;
+          v4 = make_float4(src[0], src[LDX], src[2 * LDX], src[3 * LDX]);
+        }
         float4 h, l;
-        split_tf32_bits(src[0], h.x, l.x); split_tf32_bits(src[LDX], h.y, l.y);
-        split_tf32_bits(src[2 * LDX], h.z, l.z); split_tf32_bits(src[3 * LDX], h.w, l.w);
+        split_tf32_bits(v4.x, h.x, l.x); split_tf32_bits(v4.y, h.y, l.y);
+        split_tf32_bits(v4.z, h.z, l.z); split_tf32_bits(v4.w, h.w, l.w);
         const int d = ((r >> 3) * (BK / 4) + kc) * 8 + (r & 7);
         reinterpret_cast<float4*>(ub_hi)[d] = h;
         reinterpret_cast<float4*>(ub_lo)[d] = l;
@@ -877,11 +913,14 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
     if (p.c_mode == 2 && E0 > 0 && p.vec_c >= 4 && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
       float* ctile = Xs;  // BM * BN floats: fits in the stage images plus the MMA images
       const int run_elems = E0 * BN;
+      // m = mbase + c walks the runs of E0 outputs: one division, then steps of 4 (E0 is a multiple of 4)
+      int rem = mbase % E0;
+      float* dst = ctile + (mbase / E0) * run_elems + nl * E0;
 #pragma unroll
       for (int c = 0; c < CPT; c += 4) {
-        const int m = mbase + c;
-        *reinterpret_cast<float4*>(ctile + (m / E0) * run_elems + nl * E0 + (m % E0)) =
-            make_float4(alpha * v[c], alpha * v[c + 1], alpha * v[c + 2], alpha * v[c + 3]);
+        *reinterpret_cast<float4*>(dst + rem) = make_float4(alpha * v[c], alpha * v[c + 1], alpha * v[c + 2], alpha * v[c + 3]);
+        rem += 4;
+        if (rem >= E0) { rem -= E0; dst += run_elems; }
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncthreads();
