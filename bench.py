@@ -50,7 +50,7 @@ WORKLOADS = {
 METRIC = "GFLOP/s per contraction"
 # DRAM bytes one launch of the workload's kernel moves (dram__bytes_read.sum + dram__bytes_write.sum of one
 # ncu capture, summarised under profiles/); cfg5 is 8 x the captured one-eighth slab.
-NCU_TRAFFIC_BYTES = {"cfg2": 1984793088, "cfg3": 1341919744, "cfg4": 1472347904,
+NCU_TRAFFIC_BYTES = {"cfg2": 1984793088, "cfg3": 1341919744, "cfg4": 1472193280,
                      "cfg5_shard8": 8369612032, "cfg5": 8 * 8369612032}
 
 
