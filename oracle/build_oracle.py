@@ -24,7 +24,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DEFAULT = "/root/reference"
+# the reference tree sits beside the repository ("reference" next to the repository's folder) unless TC_REFERENCE_ROOT says otherwise
+REF_DEFAULT = os.environ.get("TC_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 REF_OUT = os.path.join(HERE, "_ref")
 LIB_ORACLE = os.path.join(HERE, "liboracle.so")
 LIB_REF = os.path.join(REF_OUT, "libref_nests.so")

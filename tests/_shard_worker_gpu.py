@@ -1,5 +1,5 @@
 """One rank of the multi-GPU test of the sharded paths: NCCL, one GPU per rank, the CUDA kernels do the work and the
-CPU checker judges the result.  Ranks leave only after a final barrier, with nothing in flight."""
+CPU checker verifies the result.  Ranks leave only after a final barrier, with nothing in flight."""
 import os
 import sys
 

@@ -212,7 +212,8 @@ def test_cuda_path_against_every_compiled_reference_nest(pkg, orc, torch_cuda):
 def test_every_reference_class_at_kernel_scale(pkg, orc, torch_cuda, extents):
     """The same 57 expression classes with extents large enough (4-16 M outputs) that the planner picks the
     kernels the benchmarks run on -- persistent fp64, tcgen05 fp32, tensor-map copies where the shape allows --
-    checked against the checker's loop nest.  Throughput per class goes to gpurun_out/ when that folder exists."""
+    checked against the checker's loop nest.  Throughput per class is written as JSON into the directory named by the
+    environment variable TC_SWEEP_OUT, when it is set."""
     if not orc.ref_available():
         pytest.skip("the reference's expression table is not built here (oracle/_ref absent)")
     import json
@@ -257,8 +258,8 @@ def test_every_reference_class_at_kernel_scale(pkg, orc, torch_cuda, extents):
         del dc, da, db
     assert len(rows) == 57
     assert any(k.startswith("dmma_ws") for k in kernels), kernels
-    out = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "gpurun_out")
-    if os.path.isdir(out):
+    out = os.environ.get("TC_SWEEP_OUT")
+    if out and os.path.isdir(out):
         with open(os.path.join(out, "sweep_reference_classes_%s.json" % extents), "w") as f:
             json.dump(rows, f, indent=1)
 
