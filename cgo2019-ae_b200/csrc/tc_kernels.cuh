@@ -15,6 +15,10 @@
 // cp.async pipeline, fp64 products run on the tensor pipe (DMMA m8n8k4), and the
 // epilogue is a true read-modify-write with up to 32 contiguous bytes per thread.
 //
+// fp32 products run as three TF32 tensor-core products per product: on tcgen05.mma with the accumulators in
+// tensor memory (TC_MATH_TF32TC, one elected thread issues, tcgen05.ld feeds the epilogue) or on mma.sync
+// (TC_MATH_TF32X3); FFMA / DFMA kernels remain for comparison.
+//
 // Shared-memory image of both operands is "external-index major":
 //   Xs[stage][k][m], row pitch BM+4; Ys[stage][k][n], row pitch BN+4.
 // The pitch makes the 16-byte DMMA fragment reads, the 16-byte SIMT reads and

@@ -15,6 +15,9 @@
 //     the consumers by the depth of the ring -- across tile boundaries, so the
 //     set-up and load latency of tile i+1 hide behind the products of tile i, and
 //     one group's epilogue overlaps the other group's products;
+//   * on the 64 x 96 tile one more warpgroup exists; its first lane is the STORE thread: the consumers write
+//     whole output tiles into one staging area shared by both groups, the store thread issues one tiled TMA
+//     reduce-add / store per tile and frees the area when the copy engine has read it;
 //   * stages and tables are handed over through mbarriers in shared memory
 //     (cp.async.mbarrier.arrive makes a stage "full" when its copies land);
 //   * registers follow the roles (setmaxnreg): producers shrink, consumers grow;
