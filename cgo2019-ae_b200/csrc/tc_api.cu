@@ -309,7 +309,10 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   p->args.c_mode = c_path > 0 ? c_path - 1 : ((persistent || p->choice.math != TC_MATH_DMMA) ? 2 : 0);
   p->args.c_stream = 0;
   const bool bulk_out = p->args.c_mode == 2 && (persistent || p->args.epi_run > 0);
-  const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !bulk_out);
+  // ... unless the whole problem is a fraction of one wave: then the tile is in flight anyway and the prefetch
+  // only lengthens a latency-bound kernel (measured on the 64 x 48 x 32 configuration: 10.7 -> 9.4 us).
+  const bool tiny = (int64_t)p->args.tiles_m * p->args.tiles_n * p->args.ksplit < 148;
+  const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !bulk_out && !tiny);
   p->args.prefetch_dist = prefetch ? (uint32_t)resident_ctas(p->choice) : 0u;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));

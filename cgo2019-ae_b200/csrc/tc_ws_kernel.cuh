@@ -282,6 +282,12 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   int64_t* gtab = tables + gi * 2 * CF::TABLE_ELEMS;         // two table sets, alternating per tile
   double* gstage = stages + gi * STAGES * CF::STAGE_ELEMS;
 
+  if (tid == 32) {  // descriptors into the copy engine's cache before the first copy needs them
+    if constexpr (CF::MODEX == LM_TMA_K) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_x)) : "memory");
+    if constexpr (CF::MODEY == LM_TMA_K) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_y)) : "memory");
+    if (p.c_tensor >= 1) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_c)) : "memory");
+    if (p.c_tensor == 2) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_ct)) : "memory");
+  }
   if (tid == 0) {
     for (int q = 0; q < CF::GROUPS; ++q) {
       uint64_t* b = bars + q * (2 * STAGES + 4);
