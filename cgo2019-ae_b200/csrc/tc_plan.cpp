@@ -367,8 +367,14 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // mma.sync and tcgen05 alike, while FFMA stays at 1e-6.  Chains are therefore cut at 512: longer contractions
   // are sliced and the slices added by the combine kernel in round-to-nearest fp32 (tc_options.split_k >= 1
   // overrides this, as does TC_PATH_FFMA).
-  if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0)
-    ksplit = std::max<int64_t>(ksplit, std::min<int64_t>((kf + 511) / 512, ksteps));
+  // The slices' partial tiles live in plan-owned scratch; it is kept under 1 GiB, so very large outputs with very
+  // long contractions get longer chains (use TC_PATH_FFMA where that matters).
+  if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0) {
+    const int64_t per_slice = tiles * bm * bn * (int64_t)es;
+    const int64_t cap = std::max<int64_t>(1, (int64_t(1) << 30) / std::max<int64_t>(per_slice, 1));
+    const int64_t want = std::min<int64_t>(std::min<int64_t>((kf + 511) / 512, ksteps), cap);
+    ksplit = std::max<int64_t>(ksplit, want);
+  }
   int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
   ksplit = (ksteps + chunk_steps - 1) / chunk_steps;
   a.ksplit = (uint32_t)ksplit;
