@@ -136,6 +136,7 @@ struct tc_plan {
   int device = -1;
   bool swapped = false;  // X = right input, Y = left input
   TcKernelArgs args{};
+  TcDims kdims{};  // the contraction class (s_in: stride in X, s_out: stride in Y); the kernels see it as offset tables
   TcKernelChoice choice{};
   std::vector<int64_t> h_koff_x, h_koff_y;
   void* d_koff = nullptr;      // device copy of both tables

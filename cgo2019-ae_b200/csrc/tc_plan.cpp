@@ -213,6 +213,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   a.Mflat = (uint32_t)mf;
   a.Nflat = (uint32_t)nf;
   a.Kflat = (uint32_t)kf;
+  p->kdims = kd;
 
   // Contraction offset tables (one entry per flattened k).
   p->h_koff_x.assign(kf, 0);
@@ -469,6 +470,8 @@ std::string tc_plan_to_json(const tc_plan& p) {
     dims(a.M);
     o << ",\"N\":";
     dims(a.N);
+    o << ",\"K\":";
+    dims(p.kdims);
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK

@@ -149,3 +149,49 @@ def test_sizes_beyond_32_bit(pkg):
     d = _plan(pkg, CONFIGS[4][0]).describe()
     assert d["tiles"][0] * d["tiles"][1] == 500 * 1000
     assert d["N"][0]["s_out"] == 64000
+
+
+def test_index_classes_reproduce_the_contraction(pkg, orc):
+    """What the kernels are told -- the digits of M, N and K with their strides, the operand swap -- evaluated in numpy
+    gives the checker's result for random expressions: the classes cover every element once, fusion, splitting and
+    re-ordering of digits included."""
+    import random
+
+    import numpy as np
+
+    from test_parser import _random_expr
+
+    def flat(dims, key):
+        # flattened index f = sum digit_i * prod(extent_j, j < i)  ->  offset
+        off = np.zeros(1, dtype=np.int64)
+        for d in dims:
+            off = (np.arange(d["extent"], dtype=np.int64)[:, None] * d[key] + off[None, :]).reshape(-1)
+        return off
+
+    rng = random.Random(99)
+    seen_split = 0
+    for n in range(250):
+        expr = _random_expr(rng, max_out=6, max_sum=3)
+        p = orc.parse(expr)
+        # extents from a set that triggers vector, fusion and digit-splitting rules
+        ext = {i: rng.choice([1, 2, 3, 4, 4, 5, 8, 8, 12, 16]) for i in p["out_idx"] + p["sum_idx"]}
+        expr = orc.with_extents(expr, ext)
+        if np.prod([float(v) for v in ext.values()]) > 3e6:
+            continue
+        c0, a, b = orc.make_inputs(expr, n, "float64")
+        want = orc.contract(expr, c0.copy(), a, b)
+        d = _plan(pkg, expr).describe()
+        x, y = (b, a) if d["swapped"] else (a, b)
+        om_x, om_c = flat(d["M"], "s_in"), flat(d["M"], "s_out")
+        on_y, on_c = flat(d["N"], "s_in"), flat(d["N"], "s_out")
+        ok_x, ok_y = flat(d["K"], "s_in"), flat(d["K"], "s_out")
+        assert len(om_x) == d["Mflat"] and len(on_y) == d["Nflat"] and len(ok_x) == d["Kflat"]
+        prod = x[om_x[:, None] + ok_x[None, :]] @ y[on_y[:, None] + ok_y[None, :]].T
+        where = (om_c[:, None] + on_c[None, :]).reshape(-1)
+        assert len(np.unique(where)) == c0.size == where.size, expr      # every output element exactly once
+        got = c0.copy()
+        op = p["op"]
+        got[where] = prod.reshape(-1) if op == "=" else got[where] + (prod.reshape(-1) if op == "+=" else -prod.reshape(-1))
+        assert orc.rel_error(got, want) <= 1e-12, (expr, d["M"], d["N"], d["K"])
+        seen_split += any(dd["extent"] == 4 and dd["s_out"] != 1 for dd in d["M"][1:2])
+    assert seen_split > 0  # the digit re-ordering was exercised
