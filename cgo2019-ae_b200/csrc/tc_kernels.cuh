@@ -932,14 +932,24 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
       return;
     }
     {
-      const int64_t cn = offc_n[nl];
-      if (cn >= 0) {
+      // Ragged tiles, unaligned or non-contiguous outputs: the tile goes through shared memory ([n][m], odd pitch)
+      // so that a row of C is read and written by consecutive lanes on consecutive m.
+      static_assert(STAGES * CF::STAGE_ELEMS + CF::UMMA_ELEMS >= BN * (BM + 1), "staging room");
+      float* ctile = Xs;
+      constexpr int CP = BM + 1;
 #pragma unroll
-        for (int c = 0; c < CPT; ++c) {
-          const int64_t co = offc_m[mbase + c];
+      for (int c = 0; c < CPT; ++c) ctile[nl * CP + mbase + c] = alpha * v[c];
+      __syncthreads();
+      for (int row = warp; row < BN; row += CF::WARPS) {
+        const int64_t cn = offc_n[row];
+        if (cn < 0) continue;  // uniform across the warp
+#pragma unroll
+        for (int m = lane; m < BM; m += 32) {
+          const int64_t co = offc_m[m];
           if (co < 0) continue;
-          const float c0 = accumulate ? C[cn + co] : 0.f;
-          C[cn + co] = fmaf(alpha, v[c], c0);
+          float* q = C + cn + co;
+          const float r = ctile[row * CP + m];
+          *q = accumulate ? r + *q : r;
         }
       }
     }

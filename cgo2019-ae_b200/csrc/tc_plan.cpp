@@ -320,7 +320,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     if (c.math == TC_MATH_TF32X3 && path == TC_PATH_AUTO && p->opt.split_k <= 1) {
       // The same three products as tcgen05.mma with the accumulators in tensor memory measured 10 % (K = 24)
       // to 80 % (K = 2048) faster than the mma.sync form on B200.  Its tiles are bm x 128; it is chosen when
-      // they fill the GPU, almost all of them are whole (ragged tiles leave element by element) and whole
+      // they fill the GPU, almost all of them are whole (ragged tiles leave row by row through shared memory) and whole
       // tiles can leave through the staged bulk epilogue.
       auto mostly_whole = [](int64_t n, int64_t b) { return n % b == 0 || n >= 16 * b; };
       bool bulk_ok = false;
