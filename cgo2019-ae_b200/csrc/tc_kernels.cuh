@@ -349,6 +349,43 @@ __device__ __forceinline__ void bulk_out_tile(const TcKernelArgs& p, typename CF
   asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // shared memory is released at exit
 }
 
+// The same staged tile, applied with plain 16-byte loads and stores: every chunk (a run of E0 outputs times the
+// adjacent n) is contiguous in C, so the whole CTA walks it with one float4 / double2 per thread and step.
+template <class CF>
+__device__ __forceinline__ void rmw_out_tile(const TcKernelArgs& p, typename CF::T* __restrict__ C,
+                                             const typename CF::T* ctile, const int64_t* offc_m,
+                                             const int64_t* offc_n, uint32_t n0, int tid) {
+  using T = typename CF::T;
+  using V = typename Vec16<T>::type;
+  constexpr int BM = CF::BM, BN = CF::BN, VW = CF::VW;
+  const int E0 = p.epi_run, run_elems = E0 * BN, runs = BM / E0;
+  const int F0 = p.epi_n_span;
+  int nb = BN, nseg = BN;
+  if (F0 > 0) {
+    const int left = F0 - (int)(n0 % (uint32_t)F0);
+    nb = left < BN ? left : BN;
+    nseg = nb < BN ? 2 : 1;
+  }
+  const bool acc = p.beta != 0;
+  for (int c = 0; c < runs * nseg; ++c) {
+    const int r = c / nseg, sgi = c % nseg;
+    const int n = F0 > 0 ? (sgi == 0 ? 0 : nb) : sgi;
+    const int len = F0 > 0 ? (sgi == 0 ? nb : BN - nb) : 1;
+    V* dst = reinterpret_cast<V*>(C + offc_m[r * E0] + offc_n[n]);
+    const V* src = reinterpret_cast<const V*>(ctile + r * run_elems + n * E0);
+    const int nv = E0 * len / VW;
+    for (int i = tid; i < nv; i += CF::THREADS) {
+      V v = src[i];
+      if (acc) {
+        const V o = dst[i];
+        if constexpr (CF::ES == 4) { v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        else { v.x += o.x; v.y += o.y; }
+      }
+      dst[i] = v;
+    }
+  }
+}
+
 // --------------------------------------------------------------- kernel ----
 template <class CF>
 __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(const __grid_constant__ TcKernelArgs p,
@@ -914,7 +951,8 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
       return;
     }
     const int E0 = p.epi_run;
-    if (p.c_mode == 2 && E0 > 0 && p.vec_c >= 4 && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
+    const bool staged_rmw = p.c_mode == 0 && p.epi_n_span > 0;  // read-modify-write of long contiguous chunks
+    if ((p.c_mode == 2 || staged_rmw) && E0 > 0 && p.vec_c >= 4 && m0 + BM <= p.Mflat && n0 + BN <= p.Nflat) {
       float* ctile = Xs;  // BM * BN floats: fits in the stage images plus the MMA images
       const int run_elems = E0 * BN;
       // m = mbase + c walks the runs of E0 outputs: one division, then steps of 4 (E0 is a multiple of 4)
@@ -928,7 +966,8 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
       }
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
       __syncthreads();
-      bulk_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
+      if (staged_rmw) rmw_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
+      else bulk_out_tile<CF>(p, C, ctile, offc_m, offc_n, n0, tid);
       return;
     }
     {
