@@ -78,7 +78,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kSpinLimit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  atomicMax(status, code);
+  atomicCAS(status, 0, code);  // the first wait that gives up names the cause; the others follow from it
   return false;
 }
 

@@ -96,9 +96,9 @@ struct WsCfg {
   static constexpr uint32_t TMA_BYTES = (MODEX == LM_TMA_K ? BM * BK * 8 : 0) + (MODEY == LM_TMA_K ? BN * BK * 8 : 0);
   static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);
   static constexpr int TABLE_ELEMS = 2 * BM + 2 * BN;            // offx_m, offc_m, offy_n, offc_n
-  // per group: full[STAGES], empty[STAGES], tab_full[2], tab_empty[2]; then staged[2], cfree, and eight
+  // per group: full[STAGES], empty[STAGES], tab_full[2], tab_empty[2]; then staged[2], cfree[2], and eight
   // words used as the mailbox of tile coordinates (two groups x eight ints)
-  static constexpr int NBARS = GROUPS * (2 * STAGES + 4) + 3 + 8;
+  static constexpr int NBARS = GROUPS * (2 * STAGES + 4) + 4 + 8;
   // Epilogue staging for the bulk reduce: per consumer warp 8 rows of WM outputs, pitch WM+2
   // (16-byte aligned rows, conflict-free 16-byte writes).
   static constexpr int CPITCH = WM + 2;
@@ -273,8 +273,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const bool is_producer = !is_store && warp >= 2 * CW;
   const int gi = is_producer ? (warp - 2 * CW) >> 1 : is_store ? 0 : warp / CW;  // group served
   uint64_t* staged = bars + CF::GROUPS * (2 * STAGES + 4);  // [2] a group's tile is in the shared staging area
-  uint64_t* cfree = staged + 2;                             // the staging area has been read out once more
-  int* mailbox = reinterpret_cast<int*>(cfree + 1);         // [2][8] tensor coordinates of the staged tile
+  uint64_t* cfree = staged + 2;                             // [2] group g's staged tile has been read out
+  int* mailbox = reinterpret_cast<int*>(cfree + 2);         // [2][8] tensor coordinates of the staged tile
   uint64_t* full = bars + gi * (2 * STAGES + 4);             // [STAGES]
   uint64_t* empty = full + STAGES;                           // [STAGES]
   uint64_t* tab_full = empty + STAGES;                       // [2]
@@ -297,6 +297,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     mbar_init(staged, CW);
     mbar_init(staged + 1, CW);
     mbar_init(cfree, 1);
+    mbar_init(cfree + 1, 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
@@ -338,7 +339,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
               : "memory");
         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-        mbar_arrive(cfree);
+        mbar_arrive(&cfree[g]);
       }
       if (!any) break;
     }
@@ -516,8 +517,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     if (tile_out) {
       // Whole tile through the shared staging area, filled in the order g0, g1, g0, ...: use number u may start
       // once use u - 1 has been read out.  After the first wait the two groups stay out of phase.
-      const uint32_t u = 2u * titer + gi;
-      if (u > 0 && !mbar_wait(cfree, (u - 1) & 1, p.status, 7)) return;
+      // The area is used in the order (0,g0) (0,g1) (1,g0) (1,g1) ...: group 1 may write tile t once group 0's tile
+      // t has been read out, group 0 may write tile t once group 1's tile t - 1 has (which implies everything
+      // before it).  One barrier per group keeps every waiter within one phase of what it waits for -- with a
+      // single barrier a group that returns quickly (short contractions) could be two phases off, which a parity
+      // wait cannot tell apart.
+      if (gi == 1) { if (!mbar_wait(&cfree[0], titer & 1, p.status, 7)) return; }
+      else if (titer > 0) { if (!mbar_wait(&cfree[1], (titer - 1) & 1, p.status, 7)) return; }
       double* tb = cstages;
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {

@@ -300,6 +300,10 @@ TENSOR_OUT = [
     "C [a,128,b,32,c,3,d,2] += sum(e,24) * A [e,a,c] * B [b,d,e];",
     "C [a,128,b,3,c,16,d,5] -= sum(e,33) * A [a,e,b] * B [e,c,d];",
     "C [a,64,b,2,c,96] += sum(e,32) * A [a,e,b] * B [e,c];",
+    # one K step per tile: a consumer group is back at the shared staging area before its previous tile has been
+    # read out (the staging hand-over must not confuse that phase with the one it waits for)
+    "t2 [c,20,e,40,h,20,q,40,w,20] += sum(z,16) * C [c,e,z,h] * B [z,w,q];",
+    "C [a,256,b,64,c,96] -= sum(e,8) * A [e,a,b] * B [e,c];",
     # (b, c) are contiguous in C, not in B: one N dimension of 96 for the output view
     "C [a,128,b,24,c,4] += sum(e,16) * A [e,a] * B [b,e,c];",
     # N's fastest dimension is not a multiple of 16 while N has two dimensions: must fall back
