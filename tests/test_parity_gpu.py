@@ -186,6 +186,35 @@ def test_random_contractions(pkg, orc, torch_cuda, path):
         assert err <= TOL[dt], (expr, err, d)
 
 
+def test_random_midsize_contractions_with_forced_kernels_and_options(pkg, orc, torch_cuda):
+    """Random expressions with 0.3-3 M outputs, ragged and aligned extents, contractions of 1 to 64, pushed through
+    the persistent fp64 tiles and the tcgen05 / mma.sync / FFMA fp32 kernels with random epilogue, tensor-map and
+    K-slice options: many tiles per CTA, one K step per tile, clipped boxes -- the mix that exposes hand-over bugs."""
+    rng = random.Random(4242)
+    done = 0
+    while done < 36:
+        expr = _random_expr(rng, max_out=6, max_sum=2)
+        p = orc.parse(expr)
+        base = max(2, int(round(rng.choice([3e5, 1e6, 3e6]) ** (1.0 / len(p["out_idx"])))))
+        pick = lambda b: max(1, rng.choice([b, b + 1, b - 1, (b + 3) // 4 * 4, (b + 7) // 8 * 8, 2 * b, max(1, b // 2)]))
+        ext = {i: pick(base) for i in p["out_idx"]}
+        ext.update({i: rng.choice([1, 3, 8, 16, 24, 40, 64]) for i in p["sum_idx"]})
+        if np.prod([float(v) for v in ext.values()]) > 1.5e8:
+            continue
+        expr = orc.with_extents(expr, ext)
+        kw64 = {"tile": rng.choice([(64, 96), (128, 64), (64, 64)]), "variant": 3, "c_path": rng.choice([0, 1, 2, 3]),
+                "tma": rng.choice([0, 1, 2, 3, 4]), "l2_prefetch": rng.choice([0, 1, 2])}
+        kw32 = rng.choice([
+            {"path": pkg.PATH_TCGEN05, "tile": rng.choice([(96, 128), (128, 128)]), "c_path": rng.choice([0, 1, 3]),
+             "split_k": rng.choice([0, 1, 3])},
+            {"path": pkg.PATH_3XTF32, "c_path": rng.choice([0, 1, 3]), "split_k": rng.choice([0, 1, 2])},
+            {"path": pkg.PATH_FFMA, "c_path": rng.choice([0, 1, 2, 3])}])
+        for dt, kw in (("float64", kw64), ("float32", kw32)):
+            err, d = _run(pkg, orc, torch_cuda, expr, dt, 700 + done, **kw)
+            assert err <= TOL[dt], (expr, dt, kw, err, d["kernel"])
+        done += 1
+
+
 def test_cuda_path_against_every_compiled_reference_nest(pkg, orc, torch_cuda):
     """All 57 loop nests the reference ships (48 fp64 + 9 fp32 drivers), compiled from its own sources:
     the CUDA path is compared with THEIR output, not with the restatement."""
