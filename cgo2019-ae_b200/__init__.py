@@ -20,8 +20,9 @@ F64, F32 = 0, 1
 PATH_AUTO, PATH_DMMA, PATH_DFMA, PATH_FFMA, PATH_3XTF32, PATH_TCGEN05 = 0, 1, 2, 3, 4, 5
 TENSOR_OUT, TENSOR_LEFT, TENSOR_RIGHT = 0, 1, 2
 
+PROBES_PATH = os.path.join(_HERE, "probes", "libtc_probes.so")
 PEAK_NAMES = {0: "dmma_m8n8k4", 1: "dmma_m16n8k4", 2: "dmma_m16n8k8", 3: "dmma_m16n8k16",
-              4: "dfma", 5: "ffma", 6: "tf32_mma_sync"}
+              4: "dfma", 5: "ffma", 6: "tf32_mma_sync", 7: "tf32_tcgen05"}
 
 
 class TcError(RuntimeError):
@@ -36,7 +37,7 @@ class TcError(RuntimeError):
 class Options(ctypes.Structure):
     _fields_ = [("path", ctypes.c_int), ("tile_m", ctypes.c_int), ("tile_n", ctypes.c_int),
                 ("split_k", ctypes.c_int), ("variant", ctypes.c_int), ("l2_prefetch", ctypes.c_int),
-                ("c_path", ctypes.c_int), ("tma", ctypes.c_int)]
+                ("c_path", ctypes.c_int), ("tma", ctypes.c_int), ("test_fault", ctypes.c_int)]
 
 
 _lib = None
@@ -60,6 +61,7 @@ _SIGNATURES = {
                                     ctypes.POINTER(ctypes.c_double)]),
     "tc_plan_launches": (ctypes.c_int, [ctypes.c_void_p]),
     "tc_plan_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]),
+    "tc_plan_status_reset": (ctypes.c_int, [ctypes.c_void_p]),
     "tc_plan_workspace_bytes": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_size_t)]),
     "tc_execute": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                   ctypes.c_void_p]),
@@ -75,8 +77,6 @@ _SIGNATURES = {
                                        ctypes.c_int, ctypes.c_int64, ctypes.c_void_p]),
     "tc_axpy": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
                                ctypes.c_double, ctypes.c_void_p]),
-    "tc_peak_measure": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]),
-    "tc_peak_measure_rmw": (ctypes.c_int, [ctypes.c_int64, ctypes.POINTER(ctypes.c_double)]),
 }
 
 
@@ -122,6 +122,19 @@ def parse(expr):
     return json.loads(buf.value.decode())
 
 
+def _stream(stream, *tensors):
+    """cudaStream_t for a call: the caller's, else torch's current stream when the arguments are torch CUDA tensors
+    (so that the launch is ordered with the surrounding torch work), else the legacy default stream."""
+    if stream:
+        return ctypes.c_void_p(stream)
+    for t in tensors:
+        if hasattr(t, "is_cuda") and t.is_cuda:
+            import torch
+            s = torch.cuda.current_stream(t.device).cuda_stream
+            return ctypes.c_void_p(s) if s else None
+    return None
+
+
 def _ptr(x):
     """Device/host address of a torch tensor, numpy array or raw int."""
     if x is None:
@@ -138,7 +151,8 @@ def _ptr(x):
 class Plan:
     """One contraction: expression + dtype (+ extents, strides, options)."""
 
-    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None, variant=0, l2_prefetch=0, c_path=0, tma=0):
+    def __init__(self, expr, dtype=F64, path=PATH_AUTO, tile=None, split_k=0, extents=None, variant=0, l2_prefetch=0, c_path=0, tma=0,
+                 test_fault=0):
         self._h = ctypes.c_void_p()
         opt = Options()
         opt.path = path
@@ -149,6 +163,7 @@ class Plan:
         opt.l2_prefetch = l2_prefetch
         opt.c_path = c_path
         opt.tma = tma
+        opt.test_fault = test_fault
         self.expr = expr
         self.dtype = dtype
         _check(lib().tc_plan_create(expr.encode(), dtype, ctypes.byref(opt), ctypes.byref(self._h)), "tc_plan_create")
@@ -193,6 +208,9 @@ class Plan:
         _check(lib().tc_plan_status(self._h, ctypes.byref(v)), "tc_plan_status")
         return v.value
 
+    def status_reset(self):
+        _check(lib().tc_plan_status_reset(self._h), "tc_plan_status_reset")
+
     def workspace_bytes(self):
         n = ctypes.c_size_t()
         _check(lib().tc_plan_workspace_bytes(self._h, ctypes.byref(n)), "tc_plan_workspace_bytes")
@@ -200,7 +218,7 @@ class Plan:
 
     def execute(self, C, A, B, stream=None, workspace=None):
         """Enqueue C (op)= sum A*B on device tensors (torch CUDA tensors or raw device addresses)."""
-        s = ctypes.c_void_p(stream) if stream else None
+        s = _stream(stream, C)
         if workspace is None:
             _check(lib().tc_execute(self._h, _ptr(C), _ptr(A), _ptr(B), s), "tc_execute")
         else:
@@ -210,7 +228,7 @@ class Plan:
     def execute_noalloc(self, C, A, B, stream=None):
         """tc_execute that takes K-slice scratch from the library's fixed array instead of allocated memory
         (for callers that cannot allocate); the plan must be committed and the scratch need must fit."""
-        s = ctypes.c_void_p(stream) if stream else None
+        s = _stream(stream, C)
         _check(lib().tc_execute_noalloc(self._h, _ptr(C), _ptr(A), _ptr(B), s), "tc_execute_noalloc")
 
     def execute_host(self, C, A, B):
@@ -239,7 +257,7 @@ def fill_uniform(t, seed, tensor_id, first_index=0, stream=None):
     """Fills a CUDA tensor with the seeded uniform[-1,1) stream for (seed, tensor_id)."""
     import torch
     dt = F64 if t.dtype == torch.float64 else F32
-    s = ctypes.c_void_p(stream) if stream else None
+    s = _stream(stream, t)
     _check(lib().tc_fill_uniform(_ptr(t), t.numel(), dt, seed, tensor_id, first_index, s), "tc_fill_uniform")
     return t
 
@@ -247,22 +265,40 @@ def fill_uniform(t, seed, tensor_id, first_index=0, stream=None):
 def axpy(y, x, alpha=1.0, stream=None):
     import torch
     dt = F64 if y.dtype == torch.float64 else F32
-    s = ctypes.c_void_p(stream) if stream else None
+    s = _stream(stream, y)
     _check(lib().tc_axpy(_ptr(y), _ptr(x), y.numel(), dt, alpha, s), "tc_axpy")
     return y
 
 
+_probes = None
+
+
+def probes():
+    """The bench-only probe library (pipe peaks, streaming read-modify-write); not part of the product ABI."""
+    global _probes
+    if _probes is None:
+        if not os.path.exists(PROBES_PATH):
+            raise ImportError("%s is missing: run build.py" % PROBES_PATH)
+        h = ctypes.CDLL(PROBES_PATH)
+        h.tc_peak_measure.restype = ctypes.c_int
+        h.tc_peak_measure.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        h.tc_peak_measure_rmw.restype = ctypes.c_int
+        h.tc_peak_measure_rmw.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_double)]
+        _probes = h
+    return _probes
+
+
 def measure_peaks(which=(0, 4, 5), iters=4096, ctas_per_sm=2):
-    """TFLOP/s of the arithmetic pipes (register-only loops) on the current device."""
+    """TFLOP/s of the arithmetic pipes (register-only loops; 7 = TF32 on tcgen05 from shared memory) on the current device."""
     out = {}
     for w in which:
         v = ctypes.c_double()
-        _check(lib().tc_peak_measure(w, iters, ctas_per_sm, ctypes.byref(v)), "tc_peak_measure")
+        _check(probes().tc_peak_measure(w, iters, ctas_per_sm, ctypes.byref(v)), "tc_peak_measure")
         out[PEAK_NAMES[w]] = v.value
     return out
 
 
 def measure_rmw(nbytes=4 << 30):
     v = ctypes.c_double()
-    _check(lib().tc_peak_measure_rmw(nbytes, ctypes.byref(v)), "tc_peak_measure_rmw")
+    _check(probes().tc_peak_measure_rmw(nbytes, ctypes.byref(v)), "tc_peak_measure_rmw")
     return v.value

@@ -1,4 +1,6 @@
-"""Builds libtc_b200.so (the C-ABI library with every sm_100a kernel) in-tree.
+"""Builds libtc_b200.so (the C-ABI library with every sm_100a kernel) in-tree, and beside it
+probes/libtc_probes.so (pipe-peak microbenchmarks the bench uses for roofline denominators; not part
+of the product library).
 
 Usage:  python build.py [--force] [--verbose]
 Each .cu/.cpp under csrc/ is compiled to an object in csrc/_obj/ (in parallel,
@@ -17,7 +19,9 @@ LIB = os.path.join(HERE, "libtc_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
-COMMON += os.environ.get("TC_NVCC_FLAGS", "").split()  # e.g. -DTC_WS_TIMING for the cycle counters of the persistent kernel
+COMMON += os.environ.get("TC_NVCC_FLAGS", "").split()
+PROBES_SRC = os.path.join(HERE, "probes", "tc_probes.cu")
+PROBES_LIB = os.path.join(HERE, "probes", "libtc_probes.so")
 
 
 def _newer(target, deps):
@@ -91,6 +95,12 @@ def build(force=False, verbose=False):
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
+    if force or not _newer(PROBES_LIB, [PROBES_SRC]):
+        cmd = [NVCC] + ARCH + COMMON + ["-shared", "-o", PROBES_LIB, PROBES_SRC, "-lcudart_static", "-lpthread", "-ldl", "-lrt"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("probe library failed to build")
     return LIB
 
 

@@ -33,11 +33,12 @@ extern "C" const char* tc_status_string(int s) {
     case TC_ERR_ALIGNMENT: return "misaligned tensor pointer";
     case TC_ERR_STATE: return "call order violated";
     case TC_ERR_WORKSPACE: return "workspace missing or too small";
+    case TC_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel gave up";
     default: return "unknown status";
   }
 }
 
-extern "C" const char* tc_version(void) { return "tc_b200 0.1 (sm_100a)"; }
+extern "C" const char* tc_version(void) { return "tc_b200 0.2 (sm_100a)"; }
 
 static void copy_out(const std::string& s, char* buf, size_t cap) {
   if (!buf || cap == 0) return;
@@ -217,8 +218,18 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
   }
   tc_inst_fn fn = pick_inst(c);
   if (!fn) return TC_ERR_UNSUPPORTED;
-  int st = fn(vx, vy, &a, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
-  if (st != TC_OK) return st;
+  // Plans whose contraction runs as sequential passes (fp32 tensor-core chains kept short on outputs too large
+  // for slice scratch): one launch per range of k, the first with the expression's operator, the rest adding.
+  for (int pass = 0; pass < p.passes; ++pass) {
+    TcKernelArgs b = a;
+    if (p.passes > 1) {
+      b.k_first = (uint32_t)pass * a.k_chunk;
+      b.Kflat = std::min<uint32_t>(a.Kflat, b.k_first + a.k_chunk);
+      if (pass > 0) b.beta = 1;
+    }
+    const int st = fn(vx, vy, &b, C, X, Y, stream, TC_INST_LAUNCH, nullptr, nullptr);
+    if (st != TC_OK) return st;
+  }
   if (a.ksplit > 1) {
     const unsigned grid = a.tiles_m * a.tiles_n;
     const size_t smem = (size_t)(a.bm + a.bn) * sizeof(int64_t);
@@ -243,10 +254,13 @@ extern "C" int tc_plan_create(const char* expr, int dtype, const tc_options* opt
   p->expr = e;
   p->dtype = dtype;
   if (options) p->opt = *options;
-  if (p->opt.path < TC_PATH_AUTO || p->opt.path > TC_PATH_TCGEN05 || p->opt.split_k < 0) {
+  if (p->opt.path < TC_PATH_AUTO || p->opt.path > TC_PATH_TCGEN05 || p->opt.split_k < 0 || p->opt.test_fault < 0 ||
+      p->opt.test_fault > 1) {
     delete p;
     return TC_ERR_INVALID_ARG;
   }
+  p->host_mu = new (std::nothrow) std::mutex();
+  if (!p->host_mu) { delete p; return TC_ERR_INVALID_ARG; }
   for (size_t i = 0; i < e.out_idx.size(); ++i) { p->idx_names.push_back(e.out_idx[i]); p->idx_extent.push_back(e.out_ext[i]); }
   for (size_t i = 0; i < e.sum_idx.size(); ++i) { p->idx_names.push_back(e.sum_idx[i]); p->idx_extent.push_back(e.sum_ext[i]); }
   *out = p;
@@ -292,13 +306,52 @@ extern "C" int tc_plan_set_strides(tc_plan* p, int tensor, int n, const int64_t*
   return TC_OK;
 }
 
+// K-slice scratch that lives in the library image instead of in allocated memory (tc_execute_noalloc).
+// Every GPU that loads the library carries these 8 MiB until the process exits.
+static __device__ __align__(256) unsigned char g_tc_static_ws[TC_NOALLOC_MAX_WORKSPACE_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+// Device address of g_tc_static_ws per device.  In host code the array's name is only a handle for
+// the runtime, not an address a kernel can use; the real address comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+void* g_static_ws_addr[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
+
+// Resolves the static scratch array on the current device (once) and makes sure the combine kernels'
+// module is resident, so that an allocation-free execute later neither looks anything up nor triggers
+// the lazy load of that module (which allocates device memory).
+int prepare_static_scratch(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) return TC_ERR_STATE;
+  if (__atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE)) return TC_OK;
+  void* addr = nullptr;
+  TC_CUDA_OK(cudaGetSymbolAddress(&addr, g_tc_static_ws));
+  if (!addr) return TC_ERR_CUDA;
+  cudaFuncAttributes fa;
+  TC_CUDA_OK(cudaFuncGetAttributes(&fa, tck::tc_combine_kernel<double>));
+  TC_CUDA_OK(cudaFuncGetAttributes(&fa, tck::tc_combine_kernel<float>));
+  __atomic_store_n(&g_static_ws_addr[dev], addr, __ATOMIC_RELEASE);  // same value from every thread
+  return TC_OK;
+}
+
+int device_sm_count(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) return TC_DEFAULT_SMS;
+  int n = __atomic_load_n(&g_sm_count[dev], __ATOMIC_RELAXED);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return TC_DEFAULT_SMS;
+  __atomic_store_n(&g_sm_count[dev], n, __ATOMIC_RELAXED);
+  return n;
+}
+}  // namespace
+
 extern "C" int tc_plan_commit(tc_plan* p) {
   if (!p) return TC_ERR_INVALID_ARG;
   if (p->committed) return TC_OK;
-  int st = tc_plan_build(p, &p->why);
-  if (st != TC_OK) return st;
   int dev = 0;
   TC_CUDA_OK(cudaGetDevice(&dev));
+  p->sm_count = device_sm_count(dev);  // the tile rules fill THIS device's multiprocessors
+  int st = tc_plan_build(p, &p->why);
+  if (st != TC_OK) return st;
   st = tc_kernels_prepare(p->choice);
   if (st != TC_OK) return st;
   // How the result reaches C (tc_options.c_path) and whether output tiles are prefetched into L2.
@@ -311,16 +364,24 @@ extern "C" int tc_plan_commit(tc_plan* p) {
   const bool bulk_out = p->args.c_mode == 2 && (persistent || p->args.epi_run > 0);
   // ... unless the whole problem is a fraction of one wave: then the tile is in flight anyway and the prefetch
   // only lengthens a latency-bound kernel (measured on the 64 x 48 x 32 configuration: 10.7 -> 9.4 us).
-  const bool tiny = (int64_t)p->args.tiles_m * p->args.tiles_n * p->args.ksplit < 148;
+  const bool tiny = (int64_t)p->args.tiles_m * p->args.tiles_n * p->args.ksplit < p->sm_count;
   const bool prefetch = p->opt.l2_prefetch == 2 || (p->opt.l2_prefetch == 0 && !bulk_out && !tiny);
   p->args.prefetch_dist = prefetch ? (uint32_t)resident_ctas(p->choice) : 0u;
+  p->args.spin_limit = p->opt.test_fault ? (1u << 14) : TC_SPIN_LIMIT;
+  p->args.test_fault = p->opt.test_fault;
   const size_t kb = p->h_koff_x.size() * sizeof(int64_t);
   TC_CUDA_OK(cudaMalloc(&p->d_koff, 2 * kb));
   TC_CUDA_OK(cudaMemcpy(p->d_koff, p->h_koff_x.data(), kb, cudaMemcpyHostToDevice));
   TC_CUDA_OK(cudaMemcpy(static_cast<char*>(p->d_koff) + kb, p->h_koff_y.data(), kb, cudaMemcpyHostToDevice));
   p->args.koff_x = static_cast<const int64_t*>(p->d_koff);
   p->args.koff_y = p->args.koff_x + p->h_koff_x.size();
-  if (p->ws_bytes) TC_CUDA_OK(cudaMalloc(&p->d_ws, p->ws_bytes));
+  if (p->ws_bytes) {
+    TC_CUDA_OK(cudaMalloc(&p->d_ws, p->ws_bytes));
+    if (p->ws_bytes <= (size_t)TC_NOALLOC_MAX_WORKSPACE_BYTES) {  // the plan may later run through tc_execute_noalloc
+      st = prepare_static_scratch(dev);
+      if (st != TC_OK) return st;
+    }
+  }
   TC_CUDA_OK(cudaMalloc(&p->d_status, sizeof(int)));
   TC_CUDA_OK(cudaMemset(p->d_status, 0, sizeof(int)));
   p->args.status = p->d_status;
@@ -338,6 +399,7 @@ extern "C" void tc_plan_destroy(tc_plan* p) {
   if (p->d_ws) cudaFree(p->d_ws);
   if (p->d_status) cudaFree(p->d_status);
   host_pipe_destroy(p->host);
+  delete p->host_mu;
   delete p;
 }
 
@@ -372,7 +434,17 @@ extern "C" int tc_plan_cost(const tc_plan* p, double* flops, double* bytes) {
 extern "C" int tc_plan_status(tc_plan* p, int* device_status) {
   if (!p || !device_status) return TC_ERR_INVALID_ARG;
   if (!p->committed) return TC_ERR_STATE;
+  // a plain cudaMemcpy is ordered after the legacy stream only: work on non-blocking streams needs this
+  TC_CUDA_OK(cudaDeviceSynchronize());
   TC_CUDA_OK(cudaMemcpy(device_status, p->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  return TC_OK;
+}
+
+extern "C" int tc_plan_status_reset(tc_plan* p) {
+  if (!p) return TC_ERR_INVALID_ARG;
+  if (!p->committed) return TC_ERR_STATE;
+  TC_CUDA_OK(cudaDeviceSynchronize());
+  TC_CUDA_OK(cudaMemset(p->d_status, 0, sizeof(int)));
   return TC_OK;
 }
 
@@ -403,9 +475,6 @@ static int execute_impl(tc_plan* p, void* C, const void* A, const void* B, void*
     if (!ws || ws_bytes < p->ws_bytes || (reinterpret_cast<uintptr_t>(ws) & 15)) return TC_ERR_WORKSPACE;
     a.ws = ws;
   }
-#ifdef TC_WS_TIMING
-  a.ws = ws;
-#endif
   const void* X = p->swapped ? B : A;
   const void* Y = p->swapped ? A : B;
   return tc_launch_contraction(*p, a, C, X, Y, static_cast<cudaStream_t>(stream));
@@ -424,27 +493,17 @@ extern "C" int tc_execute_ws(tc_plan* p, void* C, const void* A, const void* B, 
 }
 
 // ---------------------------------------------------- execute without allocating ----
-// K-slice scratch that lives in the library image instead of in allocated memory.  Every GPU that
-// loads the library carries these 8 MiB until the process exits.
-static __device__ __align__(256) unsigned char g_tc_static_ws[TC_NOALLOC_MAX_WORKSPACE_BYTES];
-
-namespace {
-constexpr int kMaxDevices = 64;
-// Device address of g_tc_static_ws per device.  In host code the array's name is only a handle for
-// the runtime, not an address a kernel can use; the real address comes from cudaGetSymbolAddress,
-// asked once per device with that device current.
-void* g_static_ws_addr[kMaxDevices] = {};
-}  // namespace
-
 // For callers that must not allocate device memory at call time and have none to lend: an application
 // whose own pool already owns the whole device (the reference's competitors pre-claim memory this way,
 // nwchem-tccg/memory.cu:74-163), or a latency-critical loop where cudaMalloc's implicit device-wide
 // synchronisation is not acceptable.  Same work as tc_execute on a committed plan; a plan that slices
-// the contraction takes its slice scratch from the static array above.
+// the contraction takes its slice scratch from the static array g_tc_static_ws.
 //   * The plan must already be committed (committing uploads tables, which allocates): TC_ERR_STATE otherwise.
 //   * Plans that need more than TC_NOALLOC_MAX_WORKSPACE_BYTES of scratch are refused with TC_ERR_WORKSPACE.
-//   * The first call on each device looks up the array's device address; make that call before any
-//     stream capture begins.
+//   * tc_plan_commit of a K-sliced plan has already looked up the array's device address and loaded the
+//     combine kernels, so this call finds everything resident.  Only if that address is missing (no
+//     K-sliced plan was committed on this device through this library image) is it looked up here;
+//     such a first call belongs before any stream capture.
 //   * All calls on a device share the one array and it keeps whatever the last call left in it.  Nothing
 //     in it has to start at zero: every slice overwrites its whole partial tile before the combine step
 //     reads it.  Two calls whose kernels overlap on the GPU (different streams) race on it: serialise them.
@@ -459,11 +518,9 @@ extern "C" int tc_execute_noalloc(tc_plan* p, void* C, const void* A, const void
   if (p->ws_bytes) {
     ws = __atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE);
     if (!ws) {
-      void* addr = nullptr;
-      TC_CUDA_OK(cudaGetSymbolAddress(&addr, g_tc_static_ws));
-      if (!addr) return TC_ERR_CUDA;
-      __atomic_store_n(&g_static_ws_addr[dev], addr, __ATOMIC_RELEASE);  // same value from every thread
-      ws = addr;
+      const int st = prepare_static_scratch(dev);
+      if (st != TC_OK) return st;
+      ws = __atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE);
     }
   }
   return execute_impl(p, C, A, B, ws, (size_t)TC_NOALLOC_MAX_WORKSPACE_BYTES, stream);
@@ -476,16 +533,113 @@ extern "C" int tc_execute_noalloc(tc_plan* p, void* C, const void* A, const void
 // PCIe instead of their sum.  Inputs that carry the cut index as THEIR slowest index travel slab by slab
 // too; the others go first, whole.  Device buffers, streams and the slab plans are created on the first
 // call and kept with the plan.
+//
+// Pageable host memory (plain malloc -- what the reference drivers pass, code_main_tccg_02.c:53-62) cannot
+// be copied asynchronously, so it travels through pinned bounce buffers owned by the plan: on the way in the
+// calling thread fills a bounce buffer (several helper threads share the memcpy) and enqueues its copy; on
+// the way out a drain thread enqueues the device-to-host copies behind each slab's kernel and empties the
+// bounce buffers into the caller's memory while the next slab is still being staged.
+#include <condition_variable>
+#include <deque>
+#include <map>
+#include <thread>
+
+namespace {
+
+// memcpy shared by a few persistent helper threads (one caller at a time per pool).
+class CopyPool {
+ public:
+  explicit CopyPool(int n) {
+    for (int i = 0; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
+  }
+  ~CopyPool() {
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      stop_ = true;
+      ++epoch_;
+    }
+    cv_.notify_all();
+    for (std::thread& t : workers_) t.join();
+  }
+  void copy(void* dst, const void* src, size_t bytes) {
+    const size_t n = workers_.size();
+    if (bytes < (1u << 20) || n == 0) { std::memcpy(dst, src, bytes); return; }
+    std::unique_lock<std::mutex> l(mu_);
+    dst_ = static_cast<char*>(dst);
+    src_ = static_cast<const char*>(src);
+    piece_ = ((bytes + n) / (n + 1) + 4095) / 4096 * 4096;
+    bytes_ = bytes;
+    pending_ = (int)n;
+    ++epoch_;
+    l.unlock();
+    cv_.notify_all();
+    part(n);  // the caller takes the last piece
+    l.lock();
+    done_.wait(l, [this] { return pending_ == 0; });
+  }
+
+ private:
+  void part(size_t i) {
+    const size_t lo = std::min(bytes_, i * piece_), hi = std::min(bytes_, lo + piece_);
+    if (hi > lo) std::memcpy(dst_ + lo, src_ + lo, hi - lo);
+  }
+  void loop(int i) {
+    uint64_t seen = 0;
+    for (;;) {
+      std::unique_lock<std::mutex> l(mu_);
+      cv_.wait(l, [&] { return epoch_ != seen; });
+      seen = epoch_;
+      if (stop_) return;
+      l.unlock();
+      part((size_t)i);
+      l.lock();
+      if (--pending_ == 0) done_.notify_all();
+    }
+  }
+  std::vector<std::thread> workers_;
+  std::mutex mu_;
+  std::condition_variable cv_, done_;
+  uint64_t epoch_ = 0;
+  bool stop_ = false;
+  int pending_ = 0;
+  char* dst_ = nullptr;
+  const char* src_ = nullptr;
+  size_t piece_ = 0, bytes_ = 0;
+};
+
+constexpr size_t kBounceBytes = size_t(8) << 20;
+constexpr int kBounceCount = 3;
+
+bool is_pageable(const void* ptr) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) { cudaGetLastError(); return true; }
+  return at.type == cudaMemoryTypeUnregistered;
+}
+
+}  // namespace
+
 struct TcHostPipe {
   void *dC = nullptr, *dA = nullptr, *dB = nullptr;
   cudaStream_t stream[2] = {nullptr, nullptr};
+  cudaStream_t out_stream = nullptr;  // device-to-host copies of pageable outputs
   cudaEvent_t inputs_ready = nullptr;
   int cut = -1;                 // position of the cut index in idx_names (-1: no slabs)
   int64_t extent = 1, slab = 1; // extent of the cut index, values per slab
-  int64_t step[3] = {0, 0, 0};  // elements per value of the cut index where the tensor travels slab by slab (0: whole, first)
+  int64_t step[3] = {0, 0, 0};  // element stride of the cut index where the tensor travels slab by slab (0: whole, first)
+  int64_t rest[3] = {0, 0, 0};  // elements one value of the cut index spans in such a tensor
   int64_t view[3] = {0, 0, 0};  // element stride of the cut index in C, A, B (0: the tensor does not carry it)
   tc_plan* plan_slab = nullptr; // slab-sized sub-plan (strides of the full tensors)
   tc_plan* plan_tail = nullptr; // last, shorter slab
+  int* h_status = nullptr;      // pinned: status words of the three plans after a call
+  // pageable staging
+  void* bounce_in[kBounceCount] = {};
+  void* bounce_out[kBounceCount] = {};
+  cudaEvent_t in_done[kBounceCount] = {};
+  cudaEvent_t out_done[kBounceCount] = {};
+  int in_next = 0;
+  CopyPool* pool_in = nullptr;
+  CopyPool* pool_out = nullptr;
+  std::vector<cudaEvent_t> slab_done;  // kernel of slab i finished (recorded on its stream)
 };
 
 static void host_pipe_destroy(TcHostPipe* h) {
@@ -495,14 +649,41 @@ static void host_pipe_destroy(TcHostPipe* h) {
   if (h->dB) cudaFree(h->dB);
   for (cudaStream_t s : h->stream)
     if (s) cudaStreamDestroy(s);
+  if (h->out_stream) cudaStreamDestroy(h->out_stream);
   if (h->inputs_ready) cudaEventDestroy(h->inputs_ready);
   if (h->plan_slab) tc_plan_destroy(h->plan_slab);
   if (h->plan_tail) tc_plan_destroy(h->plan_tail);
+  if (h->h_status) cudaFreeHost(h->h_status);
+  for (int i = 0; i < kBounceCount; ++i) {
+    if (h->bounce_in[i]) cudaFreeHost(h->bounce_in[i]);
+    if (h->bounce_out[i]) cudaFreeHost(h->bounce_out[i]);
+    if (h->in_done[i]) cudaEventDestroy(h->in_done[i]);
+    if (h->out_done[i]) cudaEventDestroy(h->out_done[i]);
+  }
+  for (cudaEvent_t e : h->slab_done) cudaEventDestroy(e);
+  delete h->pool_in;
+  delete h->pool_out;
   delete h;
 }
 
+// Element strides of tensor t (0 output, 1 left, 2 right) in written order: the caller's, or compact.
+static std::vector<int64_t> effective_strides(const tc_plan* p, int t) {
+  if (p->custom_strides[t]) return p->strides[t];
+  const std::vector<std::string>& idx = t == 0 ? p->expr.out_idx : t == 1 ? p->expr.left_idx : p->expr.right_idx;
+  std::vector<int64_t> s;
+  int64_t acc = 1;
+  for (const std::string& n : idx) {
+    s.push_back(acc);
+    for (size_t j = 0; j < p->idx_names.size(); ++j)
+      if (p->idx_names[j] == n) acc *= p->idx_extent[j];
+  }
+  return s;
+}
+
 static int make_slab_plan(const tc_plan* p, int cut, int64_t count, tc_plan** out) {
-  tc_plan* q = new (std::nothrow) tc_plan();
+  tc_plan* q = nullptr;
+  // same expression, options and strides; only the cut index is shorter
+  q = new (std::nothrow) tc_plan();
   if (!q) return TC_ERR_INVALID_ARG;
   q->expr = p->expr;
   q->dtype = p->dtype;
@@ -510,18 +691,12 @@ static int make_slab_plan(const tc_plan* p, int cut, int64_t count, tc_plan** ou
   q->idx_names = p->idx_names;
   q->idx_extent = p->idx_extent;
   q->idx_extent[cut] = count;
-  // views into the full (compact) device tensors
-  const std::vector<std::string>* tidx[3] = {&p->expr.out_idx, &p->expr.left_idx, &p->expr.right_idx};
+  q->host_mu = new (std::nothrow) std::mutex();
   for (int t = 0; t < 3; ++t) {
-    int64_t acc = 1;
-    for (const std::string& n : *tidx[t]) {
-      q->strides[t].push_back(acc);
-      for (size_t j = 0; j < p->idx_names.size(); ++j)
-        if (p->idx_names[j] == n) acc *= p->idx_extent[j];
-    }
+    q->strides[t] = effective_strides(p, t);
     q->custom_strides[t] = true;
   }
-  const int st = tc_plan_commit(q);
+  const int st = q->host_mu ? tc_plan_commit(q) : TC_ERR_INVALID_ARG;
   if (st != TC_OK) { tc_plan_destroy(q); return st; }
   *out = q;
   return TC_OK;
@@ -537,31 +712,44 @@ static int host_pipe_create(tc_plan* p) {
   TC_CUDA_OK(cudaMalloc(&h->dB, p->size_b * es));
   for (cudaStream_t& s : h->stream) TC_CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
   TC_CUDA_OK(cudaEventCreateWithFlags(&h->inputs_ready, cudaEventDisableTiming));
-  // Slabs only for compact tensors, outputs worth pipelining (>= 32 MB) and plans that do not slice K.
-  const bool compact = !p->custom_strides[0] && !p->custom_strides[1] && !p->custom_strides[2];
+  TC_CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&h->h_status), 4 * sizeof(int)));
+  // Slabs for outputs worth pipelining (>= 32 MB) and plans that do not slice K: the cut index is the output
+  // index with the largest stride, provided everything else of the output fits below that stride (then a range
+  // of its values is one contiguous range of addresses -- compact tensors and per-rank views alike).
   const TcExpr& e = p->expr;
-  if (!compact || e.out_idx.empty() || p->count_c * (int64_t)es < (32 << 20) || p->args.ksplit > 1) return TC_OK;
-  const std::string& name = e.out_idx.back();
+  if (e.out_idx.empty() || p->count_c * (int64_t)es < (32 << 20) || p->args.ksplit > 1) return TC_OK;
+  const std::vector<std::string>* tidx[3] = {&e.out_idx, &e.left_idx, &e.right_idx};
+  std::vector<int64_t> str[3], ext[3];
+  for (int t = 0; t < 3; ++t) {
+    str[t] = effective_strides(p, t);
+    for (const std::string& n : *tidx[t])
+      for (size_t j = 0; j < p->idx_names.size(); ++j)
+        if (p->idx_names[j] == n) ext[t].push_back(p->idx_extent[j]);
+  }
+  int pos = -1;
+  for (size_t i = 0; i < e.out_idx.size(); ++i)
+    if (ext[0][i] > 1 && (pos < 0 || str[0][i] > str[0][pos])) pos = (int)i;
+  if (pos < 0) return TC_OK;
+  const std::string& name = e.out_idx[pos];
   int cut = -1;
   for (size_t j = 0; j < p->idx_names.size(); ++j)
     if (p->idx_names[j] == name) cut = (int)j;
   const int64_t extent = p->idx_extent[cut];
   if (extent < 4) return TC_OK;
+  // per tensor: does it carry the cut index, and as its outermost one?
+  for (int t = 0; t < 3; ++t) {
+    int64_t rest = 1, sc = 0;
+    for (size_t i = 0; i < tidx[t]->size(); ++i) {
+      if ((*tidx[t])[i] == name) sc = str[t][i];
+      else rest += (ext[t][i] - 1) * str[t][i];
+    }
+    h->view[t] = sc;
+    if (sc > 0 && rest <= sc) { h->step[t] = sc; h->rest[t] = rest; }
+  }
+  if (!h->step[0]) { h->view[0] = h->view[1] = h->view[2] = 0; return TC_OK; }  // the output's slabs are not contiguous ranges
   const int64_t nslabs = std::min<int64_t>(extent, 12);
   h->slab = (extent + nslabs - 1) / nslabs;
   h->extent = extent;
-  h->step[0] = h->view[0] = p->count_c / extent;
-  if (!e.left_idx.empty() && e.left_idx.back() == name) h->step[1] = p->count_a / extent;
-  if (!e.right_idx.empty() && e.right_idx.back() == name) h->step[2] = p->count_b / extent;
-  const std::vector<std::string>* in_idx[2] = {&e.left_idx, &e.right_idx};
-  for (int t = 0; t < 2; ++t) {
-    int64_t acc = 1;
-    for (const std::string& n : *in_idx[t]) {
-      if (n == name) h->view[t + 1] = acc;
-      for (size_t j = 0; j < p->idx_names.size(); ++j)
-        if (p->idx_names[j] == n) acc *= p->idx_extent[j];
-    }
-  }
   int st = make_slab_plan(p, cut, h->slab, &h->plan_slab);
   if (st != TC_OK) return st;
   if (extent % h->slab) {
@@ -570,6 +758,193 @@ static int host_pipe_create(tc_plan* p) {
   }
   if (h->plan_slab->args.ksplit > 1 || (h->plan_tail && h->plan_tail->args.ksplit > 1)) return TC_OK;  // keep one stream
   h->cut = cut;
+  return TC_OK;
+}
+
+// Bounce buffers, helper threads and the drain stream: only plans that ever see pageable memory pay for them.
+static int host_pipe_enable_staging(TcHostPipe* h) {
+  if (h->pool_in) return TC_OK;
+  for (int i = 0; i < kBounceCount; ++i) {
+    TC_CUDA_OK(cudaMallocHost(&h->bounce_in[i], kBounceBytes));
+    TC_CUDA_OK(cudaMallocHost(&h->bounce_out[i], kBounceBytes));
+    TC_CUDA_OK(cudaEventCreateWithFlags(&h->in_done[i], cudaEventDisableTiming));
+    TC_CUDA_OK(cudaEventCreateWithFlags(&h->out_done[i], cudaEventDisableTiming));
+  }
+  TC_CUDA_OK(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+  const unsigned hw = std::max(2u, std::thread::hardware_concurrency());
+  const int helpers = (int)std::min(6u, std::max(1u, hw / 4));
+  h->pool_in = new CopyPool(helpers);
+  h->pool_out = new CopyPool(helpers);
+  return TC_OK;
+}
+
+// Host -> device on `s`: directly from pinned memory, through the bounce buffers otherwise.
+static int copy_in(TcHostPipe* h, char* dst, const char* src, size_t bytes, bool pageable, cudaStream_t s) {
+  if (!pageable) {
+    TC_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s));
+    return TC_OK;
+  }
+  for (size_t off = 0; off < bytes; off += kBounceBytes) {
+    const size_t n = std::min(kBounceBytes, bytes - off);
+    const int b = h->in_next;
+    h->in_next = (b + 1) % kBounceCount;
+    TC_CUDA_OK(cudaEventSynchronize(h->in_done[b]));  // the copy that last used this buffer has read it
+    h->pool_in->copy(h->bounce_in[b], src + off, n);
+    TC_CUDA_OK(cudaMemcpyAsync(dst + off, h->bounce_in[b], n, cudaMemcpyHostToDevice, s));
+    TC_CUDA_OK(cudaEventRecord(h->in_done[b], s));
+  }
+  return TC_OK;
+}
+
+namespace {
+// Device -> pageable host, run by the drain thread: ranges become ready in order (each behind an event).
+struct DrainJob { const char* src; char* dst; size_t bytes; cudaEvent_t after; };
+struct Drain {
+  TcHostPipe* h;
+  int device;
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<DrainJob> jobs;
+  bool closed = false;
+  int status = TC_OK;
+  void push(const DrainJob& j) { { std::lock_guard<std::mutex> l(mu); jobs.push_back(j); } cv.notify_one(); }
+  void close() { { std::lock_guard<std::mutex> l(mu); closed = true; } cv.notify_one(); }
+  int run_job(const DrainJob& j) {
+    TC_CUDA_OK(cudaStreamWaitEvent(h->out_stream, j.after, 0));
+    // two-deep: the copy of chunk c + 1 is in flight while chunk c is emptied into the caller's memory
+    size_t issued = 0, drained = 0;
+    int bi = 0, bd = 0;
+    size_t len[kBounceCount] = {};
+    while (drained < j.bytes) {
+      while (issued < j.bytes && bi - bd < kBounceCount - 1) {
+        const size_t n = std::min(kBounceBytes, j.bytes - issued);
+        const int b = bi % kBounceCount;
+        TC_CUDA_OK(cudaMemcpyAsync(h->bounce_out[b], j.src + issued, n, cudaMemcpyDeviceToHost, h->out_stream));
+        TC_CUDA_OK(cudaEventRecord(h->out_done[b], h->out_stream));
+        len[b] = n;
+        issued += n;
+        ++bi;
+      }
+      const int b = bd % kBounceCount;
+      TC_CUDA_OK(cudaEventSynchronize(h->out_done[b]));
+      h->pool_out->copy(j.dst + drained, h->bounce_out[b], len[b]);
+      drained += len[b];
+      ++bd;
+    }
+    return TC_OK;
+  }
+  void loop() {
+    if (cudaSetDevice(device) != cudaSuccess) { status = TC_ERR_CUDA; }
+    for (;;) {
+      std::unique_lock<std::mutex> l(mu);
+      cv.wait(l, [this] { return closed || !jobs.empty(); });
+      if (jobs.empty()) return;
+      DrainJob j = jobs.front();
+      jobs.pop_front();
+      l.unlock();
+      if (status == TC_OK) status = run_job(j);
+    }
+  }
+};
+}  // namespace
+
+static int execute_host_locked(tc_plan* p, void* C, const void* A, const void* B) {
+  if (!p->host) {
+    const int st = host_pipe_create(p);
+    if (st != TC_OK) { host_pipe_destroy(p->host); p->host = nullptr; return st; }
+  }
+  TcHostPipe* h = p->host;
+  const size_t es = p->dtype == TC_F64 ? 8 : 4;
+  char* hC = static_cast<char*>(C);
+  const char* hA = static_cast<const char*>(A);
+  const char* hB = static_cast<const char*>(B);
+  char *dC = static_cast<char*>(h->dC), *dA = static_cast<char*>(h->dA), *dB = static_cast<char*>(h->dB);
+  const bool page_c = is_pageable(C), page_a = is_pageable(A), page_b = is_pageable(B);
+  if (page_c || page_a || page_b) {
+    const int st = host_pipe_enable_staging(h);
+    if (st != TC_OK) return st;
+  }
+  const bool read_c = p->args.beta || p->size_c != p->count_c;
+  cudaStream_t s0 = h->stream[0];
+  tc_plan* used[3] = {p, nullptr, nullptr};
+  int st = TC_OK;
+
+  if (h->cut < 0) {  // one piece
+    st = copy_in(h, dA, hA, p->size_a * es, page_a, s0);
+    if (st == TC_OK) st = copy_in(h, dB, hB, p->size_b * es, page_b, s0);
+    if (st == TC_OK && read_c) st = copy_in(h, dC, hC, p->size_c * es, page_c, s0);
+    if (st == TC_OK) st = execute_impl(p, dC, dA, dB, p->d_ws, p->ws_bytes, s0);
+    if (st != TC_OK) return st;
+    TC_CUDA_OK(cudaMemcpyAsync(hC, dC, p->size_c * es, cudaMemcpyDeviceToHost, s0));  // pageable: the driver stages it
+  } else {
+    used[0] = nullptr;
+    used[1] = h->plan_slab;
+    used[2] = h->plan_tail;
+    // inputs that are not sliced go first, whole
+    if (!h->step[1]) st = copy_in(h, dA, hA, p->size_a * es, page_a, s0);
+    if (st == TC_OK && !h->step[2]) st = copy_in(h, dB, hB, p->size_b * es, page_b, s0);
+    if (st != TC_OK) return st;
+    TC_CUDA_OK(cudaEventRecord(h->inputs_ready, s0));
+    Drain drain;
+    std::thread drainer;
+    if (page_c) {
+      drain.h = h;
+      drain.device = p->device;
+      drainer = std::thread([&drain] { drain.loop(); });
+    }
+    auto finish = [&](int code) {
+      if (page_c) { drain.close(); drainer.join(); if (code == TC_OK) code = drain.status; }
+      return code;
+    };
+    int i = 0;
+    for (int64_t v = 0; v < h->extent; v += h->slab, ++i) {
+      const int64_t n = std::min(h->slab, h->extent - v);
+      tc_plan* q = n == h->slab ? h->plan_slab : h->plan_tail;
+      cudaStream_t s = h->stream[i & 1];
+      auto range = [&](int t, size_t* off, size_t* bytes) {
+        *off = (size_t)(v * h->step[t]) * es;
+        *bytes = (size_t)((n - 1) * h->step[t] + h->rest[t]) * es;
+      };
+      size_t oc, bc, oa, ba, ob, bb;
+      range(0, &oc, &bc);
+      range(1, &oa, &ba);
+      range(2, &ob, &bb);
+      if (read_c) st = copy_in(h, dC + oc, hC + oc, bc, page_c, s);
+      if (st == TC_OK && h->step[1]) st = copy_in(h, dA + oa, hA + oa, ba, page_a, s);
+      if (st == TC_OK && h->step[2]) st = copy_in(h, dB + ob, hB + ob, bb, page_b, s);
+      if (st != TC_OK) return finish(st);
+      if (s != s0) TC_CUDA_OK(cudaStreamWaitEvent(s, h->inputs_ready, 0));
+      st = execute_impl(q, dC + oc, dA + (size_t)(v * h->view[1]) * es, dB + (size_t)(v * h->view[2]) * es, q->d_ws,
+                        q->ws_bytes, s);
+      if (st != TC_OK) return finish(st);
+      if (!page_c) {
+        TC_CUDA_OK(cudaMemcpyAsync(hC + oc, dC + oc, bc, cudaMemcpyDeviceToHost, s));
+      } else {
+        if ((int)h->slab_done.size() <= i) {
+          cudaEvent_t ev;
+          TC_CUDA_OK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+          h->slab_done.push_back(ev);
+        }
+        TC_CUDA_OK(cudaEventRecord(h->slab_done[i], s));
+        drain.push(DrainJob{dC + oc, hC + oc, bc, h->slab_done[i]});
+      }
+    }
+    st = finish(TC_OK);
+    if (st != TC_OK) return st;
+  }
+  // Status words of the plans that ran: a wait that gave up leaves the output invalid.
+  int k = 0;
+  for (tc_plan* q : used)
+    if (q) { TC_CUDA_OK(cudaMemcpyAsync(h->h_status + k, q->d_status, sizeof(int), cudaMemcpyDeviceToHost, s0)); ++k; }
+  TC_CUDA_OK(cudaStreamSynchronize(h->stream[1]));
+  if (h->out_stream) TC_CUDA_OK(cudaStreamSynchronize(h->out_stream));
+  TC_CUDA_OK(cudaStreamSynchronize(s0));
+  for (int q = 0; q < k; ++q)
+    if (h->h_status[q] != 0) {
+      int code = h->h_status[q];
+      cudaMemcpy(p->d_status, &code, sizeof(int), cudaMemcpyHostToDevice);  // visible through tc_plan_status of the caller's plan
+      return TC_ERR_DEVICE_WAIT;
+    }
   return TC_OK;
 }
 
@@ -582,63 +957,33 @@ extern "C" int tc_execute_host(tc_plan* p, void* C, const void* A, const void* B
   int dev = 0;
   TC_CUDA_OK(cudaGetDevice(&dev));
   if (dev != p->device) return TC_ERR_STATE;
-  if (!p->host) {
-    const int st = host_pipe_create(p);
-    if (st != TC_OK) { host_pipe_destroy(p->host); p->host = nullptr; return st; }
-  }
-  TcHostPipe* h = p->host;
-  const size_t es = p->dtype == TC_F64 ? 8 : 4;
-  char* hC = static_cast<char*>(C);
-  const char* hA = static_cast<const char*>(A);
-  const char* hB = static_cast<const char*>(B);
-  char *dC = static_cast<char*>(h->dC), *dA = static_cast<char*>(h->dA), *dB = static_cast<char*>(h->dB);
-  const bool read_c = p->args.beta || p->size_c != p->count_c;
-  cudaStream_t s0 = h->stream[0];
-  if (h->cut < 0) {  // one piece
-    TC_CUDA_OK(cudaMemcpyAsync(dA, hA, p->size_a * es, cudaMemcpyHostToDevice, s0));
-    TC_CUDA_OK(cudaMemcpyAsync(dB, hB, p->size_b * es, cudaMemcpyHostToDevice, s0));
-    if (read_c) TC_CUDA_OK(cudaMemcpyAsync(dC, hC, p->size_c * es, cudaMemcpyHostToDevice, s0));
-    const int st = execute_impl(p, dC, dA, dB, p->d_ws, p->ws_bytes, s0);
-    if (st != TC_OK) return st;
-    TC_CUDA_OK(cudaMemcpyAsync(hC, dC, p->size_c * es, cudaMemcpyDeviceToHost, s0));
-    TC_CUDA_OK(cudaStreamSynchronize(s0));
-    return TC_OK;
-  }
-  // inputs that are not sliced go first, whole
-  if (!h->step[1]) TC_CUDA_OK(cudaMemcpyAsync(dA, hA, p->size_a * es, cudaMemcpyHostToDevice, s0));
-  if (!h->step[2]) TC_CUDA_OK(cudaMemcpyAsync(dB, hB, p->size_b * es, cudaMemcpyHostToDevice, s0));
-  TC_CUDA_OK(cudaEventRecord(h->inputs_ready, s0));
-  int i = 0;
-  for (int64_t v = 0; v < h->extent; v += h->slab, ++i) {
-    const int64_t n = std::min(h->slab, h->extent - v);
-    tc_plan* q = n == h->slab ? h->plan_slab : h->plan_tail;
-    cudaStream_t s = h->stream[i & 1];
-    const size_t oc = (size_t)(v * h->step[0]) * es, oa = (size_t)(v * h->step[1]) * es, ob = (size_t)(v * h->step[2]) * es;
-    if (read_c) TC_CUDA_OK(cudaMemcpyAsync(dC + oc, hC + oc, (size_t)(n * h->step[0]) * es, cudaMemcpyHostToDevice, s));
-    if (h->step[1]) TC_CUDA_OK(cudaMemcpyAsync(dA + oa, hA + oa, (size_t)(n * h->step[1]) * es, cudaMemcpyHostToDevice, s));
-    if (h->step[2]) TC_CUDA_OK(cudaMemcpyAsync(dB + ob, hB + ob, (size_t)(n * h->step[2]) * es, cudaMemcpyHostToDevice, s));
-    if (s != s0) TC_CUDA_OK(cudaStreamWaitEvent(s, h->inputs_ready, 0));
-    const int st = execute_impl(q, dC + oc, dA + (size_t)(v * h->view[1]) * es, dB + (size_t)(v * h->view[2]) * es, q->d_ws,
-                                q->ws_bytes, s);
-    if (st != TC_OK) return st;
-    TC_CUDA_OK(cudaMemcpyAsync(hC + oc, dC + oc, (size_t)(n * h->step[0]) * es, cudaMemcpyDeviceToHost, s));
-  }
-  TC_CUDA_OK(cudaStreamSynchronize(h->stream[0]));
-  TC_CUDA_OK(cudaStreamSynchronize(h->stream[1]));
-  return TC_OK;
+  std::lock_guard<std::mutex> lock(*p->host_mu);  // the plan's device buffers, streams and bounce buffers are shared
+  return execute_host_locked(p, C, A, B);
+}
+
+// Frees what the host-pointer path keeps on the device for this plan (it is rebuilt on the next call).
+static void host_pipe_release(tc_plan* p) {
+  std::lock_guard<std::mutex> lock(*p->host_mu);
+  host_pipe_destroy(p->host);
+  p->host = nullptr;
 }
 
 // ------------------------------------------- drop-in for sd_t_d2_fusion_ ----
-#include <map>
-#include <mutex>
 extern "C" int tc_sd_t_d2_fusion(const char* expr, int dtype, int n_sizes, const int* sizes, void* t3, const void* t2,
                                  const void* v2) {
   if (!expr || !sizes || !t3 || !t2 || !v2 || n_sizes < 0) return TC_ERR_INVALID_ARG;
+  // Plans are kept per (expression, dtype, sizes), like the generated code's statics; the device buffers of
+  // the host-pointer path are kept only for the most recently used plan, so a driver that sweeps many sizes
+  // holds one problem's tensors on the device at a time (the reference frees after every call,
+  // cogent/src/codes/others/tc_pre_CUDA_Malloc.py).
   static std::mutex mu;
-  static std::map<std::string, tc_plan*> cache;  // plans live for the process, like the generated code's statics
+  static std::map<std::string, tc_plan*> cache;
+  static tc_plan* last = nullptr;
+  constexpr size_t kMaxCached = 256;
   std::string key = std::string(expr) + "|" + std::to_string(dtype);
   for (int i = 0; i < n_sizes; ++i) key += "," + std::to_string(sizes[i]);
   tc_plan* plan = nullptr;
+  bool cached = true;
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -652,10 +997,23 @@ extern "C" int tc_sd_t_d2_fusion(const char* expr, int dtype, int n_sizes, const
     if (st == TC_OK) st = tc_plan_commit(plan);
     if (st != TC_OK) { tc_plan_destroy(plan); return st; }
     std::lock_guard<std::mutex> lock(mu);
-    auto ins = cache.emplace(key, plan);
-    if (!ins.second) { tc_plan_destroy(plan); plan = ins.first->second; }
+    if (cache.size() >= kMaxCached) cached = false;  // beyond that: plan, run, free, like the reference
+    else {
+      auto ins = cache.emplace(key, plan);
+      if (!ins.second) { tc_plan_destroy(plan); plan = ins.first->second; }
+    }
   }
-  return tc_execute_host(plan, t3, t2, v2);
+  if (cached) {
+    tc_plan* prev = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (last != plan) { prev = last; last = plan; }
+    }
+    if (prev) host_pipe_release(prev);
+  }
+  const int st = tc_execute_host(plan, t3, t2, v2);
+  if (!cached) tc_plan_destroy(plan);
+  return st;
 }
 
 // -------------------------------------------------------- seeded inputs ----
@@ -687,8 +1045,10 @@ __global__ void axpy_kernel(T* y, const T* x, int64_t count, T alpha) {
 }
 
 int grid_for(int64_t count) {
+  int dev = 0;
+  cudaGetDevice(&dev);
   int64_t g = (count + 255) / 256;
-  return (int)std::max<int64_t>(1, std::min<int64_t>(g, 148 * 16));
+  return (int)std::max<int64_t>(1, std::min<int64_t>(g, (int64_t)device_sm_count(dev) * 16));
 }
 
 }  // namespace

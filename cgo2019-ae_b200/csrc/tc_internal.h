@@ -4,6 +4,7 @@
 
 #include <stdint.h>
 #include <stddef.h>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -45,6 +46,9 @@ std::string tc_expr_to_json(const TcExpr& e);
 
 // ------------------------------------------------------------------ plan ----
 constexpr int TC_MAX_DIMS = 8;  // fused dimensions per index class
+constexpr int TC_DEFAULT_SMS = 148;   // B200; only used to describe a plan before a device is known
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
+constexpr int TC_TF32_CHAIN = 512;    // longest fp32 accumulation chain the tensor-core paths may run
 
 // One index class (rows of the left operand, rows of the right operand) as a
 // mixed-radix number: dimension 0 is the fastest digit of the flattened index.
@@ -84,6 +88,9 @@ struct TcKernelArgs {
   uint32_t prefetch_dist;  // blocks ahead whose output tile is prefetched into L2 (0 = off)
   uint32_t k_chunk;  // flattened contraction range per K slice (multiple of the K step)
   uint32_t ksplit;   // number of K slices (1 = the kernel applies the result to C itself)
+  uint32_t k_first;  // first flattened contraction index of this launch (plans that run K in sequential passes)
+  uint32_t spin_limit;  // polls a bounded wait may take before it gives up
+  int32_t test_fault;   // tests only: 1 = the persistent kernel's producers leave one stage unannounced
   const int64_t* koff_x;  // [Kflat] offset of flattened contraction index k inside X
   const int64_t* koff_y;  // [Kflat] the same inside Y
   int32_t lanes_k_x;  // element-wise loader: consecutive lanes that walk k (1 = lanes walk the external index)
@@ -144,6 +151,9 @@ struct tc_plan {
   int* d_status = nullptr;     // device status word
   struct TcHostPipe* host = nullptr;  // device buffers, streams and slab plans of the host-pointer path
   size_t ws_bytes = 0;
+  int sm_count = TC_DEFAULT_SMS;  // multiprocessors of the device the plan is committed on
+  int passes = 1;   // sequential launches over consecutive contraction ranges, each accumulating into C
+  std::mutex* host_mu = nullptr;  // serialises tc_execute_host on this plan (its device buffers are shared)
   int64_t size_c = 0, size_a = 0, size_b = 0;  // elements spanned (max offset + 1)
   int64_t count_c = 0, count_a = 0, count_b = 0;  // logical element counts
   double flops = 0, bytes = 0;

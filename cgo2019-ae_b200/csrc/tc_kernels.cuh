@@ -57,7 +57,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 // ---- mbarriers (shared memory), every wait bounded ----
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -74,9 +73,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false (and *status = code) if the phase never completes.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+// Bounded wait: false (and *status = code) if the phase does not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_wait(bar, parity)) return true;
   atomicCAS(status, 0, code);  // the first wait that gives up names the cause; the others follow from it
   return false;
@@ -412,7 +411,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
   const uint32_t tile_n = rest % p.tiles_n;
   const uint32_t slice = rest / p.tiles_n;
   const uint32_t m0 = tile_m * BM, n0 = tile_n * BN;
-  const uint32_t kbeg = slice * p.k_chunk;
+  const uint32_t kbeg = p.k_first + slice * p.k_chunk;
   const uint32_t kend = min(p.Kflat, kbeg + p.k_chunk);
 
   for (int i = tid; i < BM + BN; i += CF::THREADS) {
@@ -856,7 +855,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
     for (int it = 0; it < nk; ++it) {
       cp_async_wait<STAGES - 2>();
       // the MMAs of the previous step must have read the images before they are rewritten
-      if (tid == 0 && it > 0 && !mbar_wait(mbar, (uint32_t)(it - 1) & 1u, p.status, 8)) *flag = 1;
+      if (tid == 0 && it > 0 && !mbar_wait(mbar, (uint32_t)(it - 1) & 1u, p.status, 8, p.spin_limit)) *flag = 1;
       __syncthreads();
       if (*flag) { gave_up = true; break; }  // uniform
       issue_koff(it);
@@ -918,7 +917,7 @@ __global__ void __launch_bounds__(CF::THREADS, CF::MIN_CTAS) tc_contract_kernel(
     }
     cp_async_wait<0>();
     if (!gave_up) {
-      if (tid == 0 && nk > 0 && !mbar_wait(mbar, (uint32_t)(nk - 1) & 1u, p.status, 9)) *flag = 1;
+      if (tid == 0 && nk > 0 && !mbar_wait(mbar, (uint32_t)(nk - 1) & 1u, p.status, 9, p.spin_limit)) *flag = 1;
       __syncthreads();
       gave_up = *flag != 0;
     }

@@ -299,6 +299,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   //     64 or 96, whichever wastes less of Nflat (128 x 64 or 64 x 96 per consumer group);
   //   * vector pipe: 128 x 128;
   //   * anything that would leave most SMs without a tile: 64 x 64, one CTA per tile.
+  const int64_t sms = p->sm_count > 0 ? p->sm_count : TC_DEFAULT_SMS;
   int bm = 128, bn = 128, variant = 0;
   if (p->opt.tile_m > 0 || p->opt.tile_n > 0) {
     bm = p->opt.tile_m;
@@ -331,14 +332,14 @@ int tc_plan_build(tc_plan* p, std::string* why) {
         bulk_ok = e0 % 4 == 0 && (n_adjacent || e0 * es >= 256);
       }
       const int64_t ctas_tc = ((mf + bm - 1) / bm) * ((nf + 127) / 128);
-      if (bulk_ok && ctas_tc >= 2 * 148 && mostly_whole(mf, bm) && mostly_whole(nf, 128) &&
+      if (bulk_ok && ctas_tc >= 2 * sms && mostly_whole(mf, bm) && mostly_whole(nf, 128) &&
           tc_kernel_exists(TC_F32, TC_MATH_TF32TC, bm, 128, 0)) {
         c.math = TC_MATH_TF32TC;
         bn = 128;
       }
     }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
-    if (ctas < 2 * 148) {
+    if (ctas < 2 * sms) {
       bm = 64; bn = 64; variant = 0;
       if (c.math == TC_MATH_TF32TC) c.math = TC_MATH_TF32X3;  // no 64-wide tcgen05 tile: same arithmetic on mma.sync
     }
@@ -361,28 +362,40 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   const bool persistent = tc_kernel_is_persistent(c);  // these kernels do not split K
   if (persistent) ksplit = 1;
   else if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
-  else if (p->opt.split_k == 0 && tiles * 2 <= 148 && ksteps >= 16)
-    ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * 148) / tiles, ksteps / 8));
+  else if (p->opt.split_k == 0 && tiles * 2 <= sms && ksteps >= 16)
+    ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * sms) / tiles, ksteps / 8));
   // The tensor cores accumulate fp32 with truncation: measured against exact sums on B200 the relative error of
   // one accumulation chain grows linearly with its length (2e-6 at K = 256, 7e-6 at 1024, 3e-5 at 4096), for
-  // mma.sync and tcgen05 alike, while FFMA stays at 1e-6.  Chains are therefore cut at 512: longer contractions
-  // are sliced and the slices added by the combine kernel in round-to-nearest fp32 (tc_options.split_k >= 1
-  // overrides this, as does TC_PATH_FFMA).
-  // The slices' partial tiles live in plan-owned scratch; it is kept under 1 GiB, so very large outputs with very
-  // long contractions get longer chains (use TC_PATH_FFMA where that matters).
+  // mma.sync and tcgen05 alike, while FFMA stays at 1e-6.  No tensor-core plan therefore runs a chain longer
+  // than TC_TF32_CHAIN products (tc_options.split_k >= 1 overrides this, as does TC_PATH_FFMA):
+  //   * where the slices' partial tiles fit 1 GiB of plan-owned scratch, the contraction is K-sliced and the
+  //     combine kernel adds the slices in round-to-nearest fp32;
+  //   * larger outputs run the contraction as sequential PASSES over consecutive ranges of at most that many
+  //     products, every pass accumulating into the output itself (the first with the expression's operator,
+  //     the others with `+=`; the additions into C are round-to-nearest).  A pass re-reads and re-writes C,
+  //     which at 512 products per element is noise beside the arithmetic.
+  p->passes = 1;
   if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0) {
     const int64_t per_slice = tiles * bm * bn * (int64_t)es;
-    const int64_t cap = std::max<int64_t>(1, (int64_t(1) << 30) / std::max<int64_t>(per_slice, 1));
-    const int64_t want = std::min<int64_t>(std::min<int64_t>((kf + 511) / 512, ksteps), cap);
-    ksplit = std::max<int64_t>(ksplit, want);
+    const int64_t want = std::min<int64_t>((kf + TC_TF32_CHAIN - 1) / TC_TF32_CHAIN, ksteps);
+    if (want > 1 && want * per_slice > (int64_t(1) << 30) && ksplit == 1) p->passes = (int)std::min<int64_t>(want, 1 << 20);
+    else ksplit = std::max<int64_t>(ksplit, want);
   }
-  int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
-  ksplit = (ksteps + chunk_steps - 1) / chunk_steps;
-  a.ksplit = (uint32_t)ksplit;
-  a.k_chunk = (uint32_t)(chunk_steps * bk);
+  if (p->passes > 1) {
+    const int64_t steps_per_pass = (ksteps + p->passes - 1) / p->passes;
+    p->passes = (int)((ksteps + steps_per_pass - 1) / steps_per_pass);
+    a.k_chunk = (uint32_t)(steps_per_pass * bk);
+    a.ksplit = 1;
+  }
+  if (p->passes == 1) {
+    int64_t chunk_steps = (ksteps + ksplit - 1) / ksplit;
+    ksplit = (ksteps + chunk_steps - 1) / chunk_steps;
+    a.ksplit = (uint32_t)ksplit;
+    a.k_chunk = (uint32_t)(chunk_steps * bk);
+  }
   if (tiles * ksplit >= (int64_t(1) << 31)) { *why = "too many tiles"; return TC_ERR_UNSUPPORTED; }
   p->ws_bytes = ksplit > 1 ? (size_t)(ksplit * tiles * bm * bn) * es : 0;
-  p->launches = ksplit > 1 ? 2 : 1;
+  p->launches = ksplit > 1 ? 2 : p->passes;
 
   // Staged bulk epilogue of the vector-pipe kernels: the tile's rows split into runs of E0 elements
   // contiguous in the output; if the output's next index belongs to the other operand (its stride equals
@@ -476,7 +489,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
-      << ",\"k_chunk\":" << a.k_chunk << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
+      << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << std::min<uint32_t>(a.k_chunk, a.Kflat) << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
       << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false") << ",\"tma_ct\":" << (p.choice.tma_ct ? "true" : "false")

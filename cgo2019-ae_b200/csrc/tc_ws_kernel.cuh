@@ -25,7 +25,7 @@
 //     the instruction never completes).
 //
 // Every mbarrier wait is bounded: a wait that does not complete within
-// kSpinLimit polls records an error code in *args.status and the thread leaves
+// args.spin_limit polls records an error code in *args.status and the thread leaves
 // the kernel; its partners then run out of polls the same way, so the kernel
 // always terminates.  The host reads the status word after synchronising.
 #pragma once
@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       for (int g = 0; g < 2; ++g) {
         if (2u * blockIdx.x + g + t * step >= total) continue;
         any = true;
-        if (!mbar_wait(&staged[g], t & 1, p.status, 6)) return;
+        if (!mbar_wait(&staged[g], t & 1, p.status, 6, p.spin_limit)) return;
         const int* mb = mailbox + g * 8;
         if (accumulate)
           asm volatile(
@@ -359,7 +359,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       int64_t* offc_m = offx_m + BM;
       int64_t* offy_n = offc_m + BM;
       int64_t* offc_n = offy_n + BN;
-      if (!mbar_wait(&tab_empty[par], ((titer >> 1) & 1) ^ 1, p.status, 1)) return;
+      if (!mbar_wait(&tab_empty[par], ((titer >> 1) & 1) ^ 1, p.status, 1, p.spin_limit)) return;
       const uint32_t m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
       for (int i = ptid; i < BM + BN; i += CF::THREADS) {
         if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       if (pf && !p.c_stream) prefetch_c();
       for (int ks = 0; ks < nk; ++ks, ++it) {
         const uint32_t s = it % STAGES;
-        if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, 2)) return;
+        if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, 2, p.spin_limit)) return;
         double* xs = gstage + s * CF::STAGE_ELEMS;
         double* ys = xs + CF::XIMG;
         const uint32_t k0 = (uint32_t)ks * BK;
@@ -392,6 +392,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
         }
         ws_load<CF, BM, CF::MODEX>(xs, X, offx_m, p.koff_x, k0, kend, ptid, lgx);
         ws_load<CF, BN, CF::MODEY>(ys, Y, offy_n, p.koff_y, k0, kend, ptid, lgy);
+        // tests only: one producer thread of CTA 0 never announces its copies of one stage, so that stage stays
+        // "not full" and every thread that depends on it runs out of polls
+        if (p.test_fault == 1 && blockIdx.x == 0 && gi == 0 && it == 1 && ptid == 7) continue;
         mbar_arrive_on_copies(&full[s]);
       }
       if (pf && p.c_stream) prefetch_c();
@@ -408,12 +411,6 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const int wm0 = (cw % CF::WGM) * WM, wn0 = (cw / CF::WGM) * WN;
   const double alpha = p.alpha;
   uint32_t it = 0, titer = 0;
-#ifdef TC_WS_TIMING
-  long long tm_wait_ks[8] = {0, 0, 0, 0, 0, 0, 0, 0}, tm_fence = 0;
-  long long tm_wait = 0, tm_mma = 0, tm_epi = 0, tm_rd = 0, tm_tab = 0, tm_tiles = 0;
-  const long long tm_begin = clock64();
-#define TM_NOW() clock64()
-#endif
   for (uint32_t tile = first; tile < total; tile += step, ++titer) {
     const uint32_t par = titer & 1;
     const int64_t* offc_m = gtab + par * CF::TABLE_ELEMS + BM;
@@ -428,7 +425,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // the first stage; the epilogue is then stores only.
     const bool from_c = accumulate && p.c_mode == 1 && p.vec_c == 4;
     if (from_c) {
-      if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 5)) return;
+      if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 5, p.spin_limit)) return;
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
         const int64_t cn = offc_n[wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)];
@@ -448,17 +445,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 
     for (int ks = 0; ks < nk; ++ks, ++it) {
       const uint32_t s = it % STAGES;
-#ifdef TC_WS_TIMING
-      const long long tm0 = TM_NOW();
-      if (ks == 0 && p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
-        reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 0] = tm0;
-#endif
-      if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, 3)) return;
-#ifdef TC_WS_TIMING
-      const long long tm1 = TM_NOW();
-      tm_wait += tm1 - tm0;
-      if (ks < 8) tm_wait_ks[ks] += tm1 - tm0;
-#endif
+      if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, 3, p.spin_limit)) return;
       const double* xs = gstage + s * CF::STAGE_ELEMS;
       const double* ys = xs + CF::XIMG;
       const int kleft = (int)kend - ks * BK;
@@ -485,22 +472,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);  // this warp no longer reads the stage
-#ifdef TC_WS_TIMING
-      tm_mma += TM_NOW() - tm1;
-#endif
     }
-#ifdef TC_WS_TIMING
-    const long long tm2 = TM_NOW();
-    if (p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
-      reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 1] = tm2;
-#endif
 
     // ---- epilogue: read-modify-write of C (the tile was prefetched into L2 by the producers) ----
-    if (!from_c && !mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4)) return;
-#ifdef TC_WS_TIMING
-    const long long tm3 = TM_NOW();
-    tm_tab += tm3 - tm2;
-#endif
+    if (!from_c && !mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 4, p.spin_limit)) return;
     const bool rmw = accumulate && !from_c;
     // c_mode 2: the warp's tile leaves through shared memory as bulk asynchronous copies, one per output
     // row (WM contiguous elements): `+=`/`-=` become reduce-adds performed by the memory system, so the SM
@@ -522,8 +497,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       // before it).  One barrier per group keeps every waiter within one phase of what it waits for -- with a
       // single barrier a group that returns quickly (short contractions) could be two phases off, which a parity
       // wait cannot tell apart.
-      if (gi == 1) { if (!mbar_wait(&cfree[0], titer & 1, p.status, 7)) return; }
-      else if (titer > 0) { if (!mbar_wait(&cfree[1], (titer - 1) & 1, p.status, 7)) return; }
+      if (gi == 1) { if (!mbar_wait(&cfree[0], titer & 1, p.status, 7, p.spin_limit)) return; }
+      else if (titer > 0) { if (!mbar_wait(&cfree[1], (titer - 1) & 1, p.status, 7, p.spin_limit)) return; }
       double* tb = cstages;
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
@@ -583,14 +558,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const int nb = 2 * j + h;
-#ifdef TC_WS_TIMING
-            const long long tm4 = TM_NOW();
-#endif
             asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
             __syncwarp();
-#ifdef TC_WS_TIMING
-            tm_rd += TM_NOW() - tm4;
-#endif
             double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;  // dense rows of WM: the box image
 #pragma unroll
             for (int i = 0; i < MB2; ++i) {
@@ -598,14 +567,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
               dst[0] = make_double2(alpha * acc[nb][2 * i][0], alpha * acc[nb][2 * i + 1][0]);
               dst[1] = make_double2(alpha * acc[nb][2 * i][1], alpha * acc[nb][2 * i + 1][1]);
             }
-#ifdef TC_WS_TIMING
-            const long long tm5 = TM_NOW();
-#endif
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             __syncwarp();
-#ifdef TC_WS_TIMING
-            tm_fence += TM_NOW() - tm5;
-#endif
             if (lane == 0) {
               const uint32_t src = smem_u32(cbuf);
               if (accumulate)
@@ -629,14 +592,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
 #pragma unroll
       for (int nb = 0; nb < 2 * NB2; ++nb) {
         // the batch that last used this staging buffer must have been read out of it
-#ifdef TC_WS_TIMING
-        const long long tm4 = TM_NOW();
-#endif
         asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(CF::CBUF - 1) : "memory");
         __syncwarp();
-#ifdef TC_WS_TIMING
-        tm_rd += TM_NOW() - tm4;
-#endif
         double* cbuf = cst + (nb % CF::CBUF) * CF::CBATCH_ELEMS;
 #pragma unroll
         for (int i = 0; i < MB2; ++i) {
@@ -731,24 +688,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&tab_empty[par]);  // the producers may overwrite this table set
-#ifdef TC_WS_TIMING
-    tm_epi += TM_NOW() - tm3;
-    if (p.ws && blockIdx.x == 0 && cw == 0 && lane == 0 && titer < 40)
-      reinterpret_cast<long long*>(p.ws)[148 * 64 + (gi * 40 + titer) * 3 + 2] = TM_NOW();
-    ++tm_tiles;
-#endif
   }
-#ifdef TC_WS_TIMING
-  if (p.ws && lane == 0 && cw < 4) {
-    long long* o = reinterpret_cast<long long*>(p.ws) + ((blockIdx.x * 2 + gi) * 4 + cw) * 8;
-    o[0] = TM_NOW() - tm_begin; o[1] = tm_wait; o[2] = tm_mma; o[3] = tm_epi; o[4] = tm_rd; o[5] = tm_tab; o[6] = tm_tiles;
-    o[7] = tm_fence;
-    if (blockIdx.x == 0 && cw == 0) {
-      long long* w = reinterpret_cast<long long*>(p.ws) + 148 * 64 + 240 + gi * 8;
-      for (int i = 0; i < 8; ++i) w[i] = tm_wait_ks[i];
-    }
-  }
-#endif
   asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");  // outstanding bulk copies of this thread
 }
 

@@ -1,4 +1,5 @@
-// Arithmetic-pipe peak probes for the roofline denominators.
+// Arithmetic-pipe peak probes for the roofline denominators (bench infrastructure: built into its own
+// library, libtc_probes.so, which the product library and its users never load).
 //
 // The driver-measured peak file only carries HBM copy bandwidth and a bf16
 // GEMM rate.  The contraction kernels are bounded by the FP64 tensor pipe
@@ -10,7 +11,15 @@
 // running `iters` rounds of independent accumulation chains.
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include "tc_internal.h"
+
+#define TC_OK 0
+#define TC_ERR_INVALID_ARG 2
+#define TC_ERR_CUDA 5
+#define TC_ERR_DEVICE_WAIT 9
+#define TC_CUDA_OK(call)                        \
+  do {                                          \
+    if ((call) != cudaSuccess) return TC_ERR_CUDA; \
+  } while (0)
 
 namespace {
 
@@ -42,7 +51,7 @@ __device__ __forceinline__ void mma_tf32_1688(float (&d)[4], const uint32_t (&a)
 }
 
 // which: 0 DMMA m8n8k4, 1 DMMA m16n8k4, 2 DMMA m16n8k8, 3 DMMA m16n8k16,
-//        4 DFMA, 5 FFMA, 6 TF32 mma.sync m16n8k8
+//        4 DFMA, 5 FFMA, 6 TF32 mma.sync m16n8k8   (7, TF32 on tcgen05, has its own kernel below)
 template <int WHICH>
 __global__ void __launch_bounds__(256) peak_kernel(int iters, double* sink) {
   const double seed = 1.0 + 1e-9 * threadIdx.x;
@@ -143,10 +152,111 @@ __global__ void __launch_bounds__(256) rmw_kernel(double2* p, int64_t n16, doubl
   }
 }
 
+
+// ---- TF32 on the 5th-generation tensor cores: tcgen05.mma.kind::tf32, operands in shared memory, a
+// 128 x 256 fp32 accumulator in tensor memory.  One CTA per SM (its shared-memory request keeps a second one
+// out); one thread issues `batch` MMAs of 128 x 256 x 8, commits them to an mbarrier and waits (bounded)
+// before the next batch.  Operand contents do not matter for the rate; they are zero.
+__device__ __forceinline__ uint32_t probe_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t probe_desc_k(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  // no swizzle, K-major: 16 bytes = 4 consecutive k of one row, 8 rows form a 128-byte core matrix
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+         (1ull << 46);
+}
+constexpr int kTcM = 128, kTcN = 256, kTcK = 8;
+__global__ void __launch_bounds__(128, 1) tcgen05_tf32_peak_kernel(int batches, int batch, int* status) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  float* a = reinterpret_cast<float*>(smem);                       // 128 rows x 8 k
+  float* b = a + kTcM * kTcK;                                      // 256 rows x 8 k
+  uint64_t* bar = reinterpret_cast<uint64_t*>(b + kTcN * kTcK);
+  uint32_t* slot = reinterpret_cast<uint32_t*>(bar + 1);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  for (int i = tid; i < (kTcM + kTcN) * kTcK; i += blockDim.x) a[i] = 0.f;
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(probe_smem_u32(slot)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(probe_smem_u32(bar)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+  const uint32_t tmem = *slot;
+  if (tid == 0) {
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcN >> 3) << 17) | ((uint32_t)(kTcM >> 4) << 24);
+    const uint64_t ad = probe_desc_k(probe_smem_u32(a), 128, 256), bd = probe_desc_k(probe_smem_u32(b), 128, 256);
+    bool ok = true;
+    for (int r = 0; r < batches && ok; ++r) {
+      for (int i = 0; i < batch; ++i) {
+        const uint32_t acc = (r > 0 || i > 0) ? 1u : 0u;
+        asm volatile(
+            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+            " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n}\n" ::"r"(tmem),
+            "l"(ad), "l"(bd), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0)
+            : "memory");
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(probe_smem_u32(bar)) : "memory");
+      ok = false;
+      for (uint32_t spin = 0; spin < (1u << 22) && !ok; ++spin) {  // bounded: gives up instead of hanging
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(probe_smem_u32(bar)), "r"((uint32_t)r & 1u)
+            : "memory");
+        ok = done != 0;
+      }
+      if (!ok) atomicCAS(status, 0, 1);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256) : "memory");
+}
+
 }  // namespace
 
+static int measure_tcgen05_tf32(int iters, double* tflops) {
+  int dev = 0, sms = 0;
+  TC_CUDA_OK(cudaGetDevice(&dev));
+  TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  constexpr int kSmem = 120 * 1024;  // more than half an SM's shared memory: one CTA per SM
+  TC_CUDA_OK(cudaFuncSetAttribute(tcgen05_tf32_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  int* status = nullptr;
+  TC_CUDA_OK(cudaMalloc(&status, sizeof(int)));
+  TC_CUDA_OK(cudaMemset(status, 0, sizeof(int)));
+  cudaEvent_t e0, e1;
+  TC_CUDA_OK(cudaEventCreate(&e0));
+  TC_CUDA_OK(cudaEventCreate(&e1));
+  const int batch = 64, batches = iters / batch > 0 ? iters / batch : 1;
+  tcgen05_tf32_peak_kernel<<<sms, 128, kSmem>>>(2, batch, status);  // warm-up
+  float best_ms = 1e30f;
+  for (int rep = 0; rep < 5; ++rep) {
+    TC_CUDA_OK(cudaEventRecord(e0));
+    tcgen05_tf32_peak_kernel<<<sms, 128, kSmem>>>(batches, batch, status);
+    TC_CUDA_OK(cudaEventRecord(e1));
+    TC_CUDA_OK(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    TC_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+    if (ms < best_ms) best_ms = ms;
+  }
+  TC_CUDA_OK(cudaGetLastError());
+  int h = 0;
+  TC_CUDA_OK(cudaMemcpy(&h, status, sizeof(int), cudaMemcpyDeviceToHost));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(status);
+  if (h != 0) return TC_ERR_DEVICE_WAIT;
+  *tflops = 2.0 * kTcM * kTcN * kTcK * (double)batch * batches * sms / (best_ms * 1e-3) * 1e-12;
+  return TC_OK;
+}
+
 extern "C" int tc_peak_measure(int which, int iters, int ctas_per_sm, double* tflops) {
-  if (!tflops || which < 0 || which > 6 || iters <= 0 || ctas_per_sm <= 0) return TC_ERR_INVALID_ARG;
+  if (!tflops || which < 0 || which > 7 || iters <= 0 || ctas_per_sm <= 0) return TC_ERR_INVALID_ARG;
+  if (which == 7) return measure_tcgen05_tf32(iters, tflops);
   int dev = 0, sms = 0;
   TC_CUDA_OK(cudaGetDevice(&dev));
   TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));

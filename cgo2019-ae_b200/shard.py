@@ -179,15 +179,23 @@ class ContractionShard:
         return lo, min(lo + self.chunk, n)
 
     def execute(self, C, A, B, group=None, stream=None):
+        import contextlib
         import torch
         g = self.geom
-        if self._partial is None:
-            self._partial = torch.zeros(self.padded, dtype=C.dtype, device=C.device)
-        if g.empty:
-            self._partial.zero_()
-        else:
-            self.plan.execute(self._partial, _view(A, g.offsets[1]), _view(B, g.offsets[2]), stream=stream)
-        self.combine(C, self._partial, group=group, stream=stream)
+        # The kernels run on `stream`; the collective and the copies around it are torch operations and run on
+        # torch's current stream.  Make the two the same stream, or the exchange could read the partial result
+        # before the kernel has written it.
+        ctx = contextlib.nullcontext()
+        if stream and C.is_cuda and stream != torch.cuda.current_stream(C.device).cuda_stream:
+            ctx = torch.cuda.stream(torch.cuda.ExternalStream(stream, device=C.device))
+        with ctx:
+            if self._partial is None:
+                self._partial = torch.zeros(self.padded, dtype=C.dtype, device=C.device)
+            if g.empty:
+                self._partial.zero_()
+            else:
+                self.plan.execute(self._partial, _view(A, g.offsets[1]), _view(B, g.offsets[2]), stream=stream)
+            self.combine(C, self._partial, group=group, stream=stream)
 
     def combine(self, C, partial, group=None, stream=None):
         """The exchange step: sum the ranks' partial outputs, add this rank's chunk into C.

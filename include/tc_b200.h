@@ -33,7 +33,9 @@ typedef enum tc_status {
   TC_ERR_CUDA = 5,         /* a CUDA runtime call failed (tc_last_cuda_error has it)   */
   TC_ERR_ALIGNMENT = 6,    /* a tensor base pointer is not aligned to its element size */
   TC_ERR_STATE = 7,        /* call order violated (e.g. changing a committed plan)     */
-  TC_ERR_WORKSPACE = 8     /* workspace too small or missing                           */
+  TC_ERR_WORKSPACE = 8,    /* workspace too small or missing                           */
+  TC_ERR_DEVICE_WAIT = 9   /* a bounded wait inside a kernel gave up: the output of that
+                              execute is invalid (tc_plan_status has the wait's code)  */
 } tc_status;
 
 typedef enum tc_dtype { TC_F64 = 0, TC_F32 = 1 } tc_dtype;
@@ -64,6 +66,9 @@ typedef struct tc_options {
   int tma;         /* tiled TMA copies in the persistent fp64 kernel (operand tiles that are plain 2-D boxes;
                       output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
                       2 = operands only, 3 = output only, 4 = both but the output per warp, never per tile */
+  int test_fault;  /* tests only, 0 in production.  1: the persistent fp64 kernel's producers leave one stage
+                      unannounced and every device-side wait gives up after 2^14 polls instead of 2^24, so the
+                      give-up path (status word, TC_ERR_DEVICE_WAIT) can be exercised without a long stall */
 } tc_options;
 
 typedef struct tc_plan tc_plan;
@@ -114,10 +119,12 @@ int tc_plan_describe(const tc_plan* plan, char* buf, size_t cap);
 int tc_plan_cost(const tc_plan* plan, double* flops, double* bytes);
 /* Kernel launches one tc_execute enqueues. */
 int tc_plan_launches(const tc_plan* plan);
-/* Blocks until the device is idle for this plan's status word and reads it: 0 = every kernel of the
- * plan ran to completion; non-zero = a bounded wait inside a persistent kernel gave up (the output
- * of that execute is invalid).  No counterpart in the reference. */
+/* Synchronises the whole device (cudaDeviceSynchronize, so work on non-blocking streams is covered too)
+ * and reads this plan's status word: 0 = every kernel of the plan ran to completion; non-zero = the code
+ * of the first bounded wait inside a kernel that gave up (the output of that execute is invalid).  The
+ * word is sticky until tc_plan_status_reset.  No counterpart in the reference. */
 int tc_plan_status(tc_plan* plan, int* device_status);
+int tc_plan_status_reset(tc_plan* plan);
 /* Bytes of caller-provided workspace tc_execute_ws needs (0 when the plan does not split K). */
 int tc_plan_workspace_bytes(const tc_plan* plan, size_t* bytes);
 
@@ -142,16 +149,24 @@ int tc_execute_ws(tc_plan* plan, void* C, const void* A, const void* B, void* wo
  * The scratch of K-sliced plans comes from a fixed array inside the library image
  * (TC_NOALLOC_MAX_WORKSPACE_BYTES, held by every GPU that loads the library until exit); the call
  * itself never allocates or frees.  The plan must already be committed (TC_ERR_STATE otherwise);
- * plans needing more scratch than the array return TC_ERR_WORKSPACE.  The first call on a device
- * resolves the array's device address: issue it before any stream capture.  Calls on one device
- * share the array, so calls whose kernels may overlap on the GPU must be serialised by the caller. */
+ * plans needing more scratch than the array return TC_ERR_WORKSPACE.  tc_plan_commit of a K-sliced plan
+ * resolves the array's device address and loads the kernels of the combine step, so that nothing is
+ * loaded or looked up at call time; should a plan committed by an older code path lack the address,
+ * the first call on that device resolves it, so issue one call before any stream capture.  Calls on
+ * one device share the array, so calls whose kernels may overlap on the GPU must be serialised by the
+ * caller. */
 #define TC_NOALLOC_MAX_WORKSPACE_BYTES (8u << 20)
 int tc_execute_noalloc(tc_plan* plan, void* C, const void* A, const void* B, void* stream);
 
 /* Blocking convenience over HOST pointers: allocate, copy in (C too), run,
  * copy C back, free -- what the reference's sd_t_d2_fusion does around its
  * kernel (cogent/src/codes/others/tc_pre_CUDA_Malloc.py:6-47,
- * cogent/src/codes/kernels/tc_interface.py:1368-1388). */
+ * cogent/src/codes/kernels/tc_interface.py:1368-1388).  The output's slowest index is cut into slabs
+ * that are pipelined over two streams.  Pinned (page-locked) host buffers are copied from directly;
+ * pageable ones (plain malloc, what the reference drivers pass) travel through two plan-owned pinned
+ * bounce buffers per direction.  Calls on one plan are serialised by a lock inside the plan (they share
+ * its device buffers); use one plan per thread to run them concurrently.  Returns TC_ERR_DEVICE_WAIT
+ * when a kernel of the call reported a wait that gave up. */
 int tc_execute_host(tc_plan* plan, void* C, const void* A, const void* B);
 
 /* ---- drop-in for the reference's generated entry ------------------------------------
@@ -177,13 +192,6 @@ int tc_fill_uniform(void* dst, int64_t count, int dtype, uint64_t seed, int tens
                     int64_t first_index, void* stream);
 /* y[i] += alpha * x[i] on device (combines reduce-scattered partial sums into C). */
 int tc_axpy(void* y, const void* x, int64_t count, int dtype, double alpha, void* stream);
-
-/* ---- arithmetic peaks (roofline denominators) -------------------------------------
- * which: 0 DMMA m8n8k4, 1 DMMA m16n8k4, 2 DMMA m16n8k8, 3 DMMA m16n8k16,
- *        4 DFMA, 5 FFMA, 6 TF32 mma.sync m16n8k8.  Register-only loops. */
-int tc_peak_measure(int which, int iters, int ctas_per_sm, double* tflops);
-/* Streaming 16-byte read-modify-write over `bytes` of device memory (GB/s, read+write). */
-int tc_peak_measure_rmw(int64_t bytes, double* gbs);
 
 #ifdef __cplusplus
 }

@@ -7,7 +7,14 @@
                                only when that tree is present
   oracle/_ref/ref_nests.json   what each compiled nest computes, recovered from
                                its code (not from its comments, which disagree
-                               with the code in places)
+                               with the code in places), plus the problem sizes
+                               the reference's bench script runs it with
+  oracle/_ref/k_<tag>          the reference's UNMODIFIED drivers compiled with
+                               -DDEBUG_CORRECTNESS (their own checker switched
+                               on) and linked against the product library
+                               through include/tc_b200_shim.h, so that the
+                               drop-in symbol is exercised by the reference's
+                               own main() and judged by its own report
 
 No reference source is copied: every driver is compiled in place with its
 `main`, `post_Correctness` and `pre_Initializing_Input_Tensors` renamed through
@@ -104,10 +111,65 @@ def build_ref(reference=REF_DEFAULT):
     return LIB_REF
 
 
+def bench_sizes(reference):
+    """Problem sizes per item from the reference's bench script (cogent/bench_tccg.sh:5-54): item number -> ints."""
+    path = os.path.join(reference, "cogent", "bench_tccg.sh")
+    if not os.path.exists(path):
+        return {}
+    out = {}
+    for m in re.finditer(r'"([\d ]+)"\s*\)?\s*#\s*(\d+)', open(path).read()):
+        out[int(m.group(2))] = [int(x) for x in m.group(1).split()]
+    return out
+
+
+def build_drivers(reference=REF_DEFAULT):
+    """Links every reference driver, unchanged and with its own correctness check enabled, against the product
+    library: one generated translation unit per driver defines sd_t_d2_fusion_ through the shim header."""
+    if not os.path.exists(JSON_REF):
+        return []
+    root = os.path.dirname(HERE)
+    libdir = os.path.join(root, "cgo2019-ae_b200")
+    if not os.path.exists(os.path.join(libdir, "libtc_b200.so")):
+        return []
+    table = json.load(open(JSON_REF))
+    sizes = bench_sizes(reference)
+    built = []
+    for tag, info in sorted(table.items()):
+        src = os.path.join(reference, info["source"])
+        n = len(info["size_args"])
+        # the driver passes its sizes in the order of its own call; recover that order from the call site
+        call = re.search(r"sd_t_d2_fusion_\(([^;]*?)\);", open(src).read(), re.S).group(1)
+        order = re.findall(r"size_idx_(\w+)", call)
+        p_out = re.findall(r"(\w+),16", info["expr"].split("sum(")[0])
+        p_sum = re.findall(r"(\w+),16", info["expr"].split("sum(")[1].split(")")[0])
+        assert order == p_out + p_sum, (tag, order, p_out, p_sum)  # output indices in written order, then sum(...)
+        ctype, dt = ("float", "TC_F32") if info["dtype"] == "f32" else ("double", "TC_F64")
+        unit = os.path.join(REF_OUT, "entry_%s.c" % tag)
+        with open(unit, "w") as f:
+            f.write('/* generated */\n#include "tc_b200_shim.h"\nTC_DEFINE_SD_T_D2_FUSION_%d("%s", %s, %s)\n'
+                    % (n, info["expr"], ctype, dt))
+        exe = os.path.join(REF_OUT, "k_" + tag)
+        cmd = ["gcc", "-std=gnu89", "-w", "-O2", "-DDEBUG_CORRECTNESS", "-I", os.path.join(root, "include"), src, unit,
+               "-L", libdir, "-ltc_b200", "-Wl,-rpath,$ORIGIN/../../cgo2019-ae_b200", "-o", exe]
+        subprocess.run(cmd, check=True)
+        os.remove(unit)
+        info["driver"] = "k_" + tag
+        num = int(tag.split("_")[1])
+        if info["dtype"] == "f64" and num in sizes and len(sizes[num]) == n:
+            info["bench_sizes"] = sizes[num]
+        elif info["dtype"] == "f32" and num in sizes and len(sizes[num]) == n:
+            info["bench_sizes"] = sizes[num]   # the fp32 items 40-48 run with the sizes of the fp64 items of the same number
+        built.append(exe)
+    with open(JSON_REF, "w") as f:
+        json.dump(table, f, indent=1, sort_keys=True)
+    return built
+
+
 def build_all(reference=REF_DEFAULT):
     out = [build_oracle()]
     if os.path.isdir(reference):
         out.append(build_ref(reference))
+        out += build_drivers(reference)
     return out
 
 

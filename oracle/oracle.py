@@ -123,6 +123,17 @@ def uniform(seed, tensor_id, count, dtype=np.float64, first=0):
             - np.float32(1.0)).astype(np.float32)
 
 
+def uniform_at(seed, tensor_id, indices, dtype=np.float64):
+    """The same stream at scattered element indices (sampled-coordinate checks of tensors too large to hold)."""
+    with np.errstate(over="ignore"):
+        key = (np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15)) ^ (np.uint64(tensor_id) << np.uint64(60))
+        x = _splitmix64(key ^ np.asarray(indices, dtype=np.int64).astype(np.uint64))
+    if np.dtype(dtype) == np.float64:
+        return (x >> np.uint64(11)).astype(np.float64) * (1.0 / 9007199254740992.0) * 2.0 - 1.0
+    return ((x >> np.uint64(40)).astype(np.float32) * np.float32(1.0 / 16777216.0) * np.float32(2.0)
+            - np.float32(1.0)).astype(np.float32)
+
+
 def fill_c(arr, seed, tensor_id, first=0):
     """Same stream, produced by the C restatement (cross-checks the numpy one)."""
     dt = 0 if arr.dtype == np.float64 else 1

@@ -32,7 +32,7 @@ def test_python_bindings_cover_the_header(pkg):
 def test_status_strings_and_version(pkg):
     lib = pkg.lib()
     assert lib.tc_status_string(0) == b"ok"
-    for s in range(1, 9):
+    for s in range(1, 10):
         assert lib.tc_status_string(s) not in (b"", b"unknown status")
     assert lib.tc_status_string(99) == b"unknown status"
     assert b"sm_100a" in lib.tc_version()

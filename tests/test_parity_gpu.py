@@ -97,7 +97,7 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
             assert err <= TOL[dt], (expr, kw, err)
 
 
-def _slab_check(pkg, orc, torch, expr, dtype, seed, fixes, device_inputs=False):
+def _slab_check(pkg, orc, torch, expr, dtype, seed, fixes, keep=None, **plan_kw):
     """Full-size run; the checker recomputes only slabs (some output indices fixed)."""
     p = orc.parse(expr)
     ext = dict(zip(p["out_idx"] + p["sum_idx"], p["out_ext"] + p["sum_ext"]))
@@ -109,9 +109,12 @@ def _slab_check(pkg, orc, torch, expr, dtype, seed, fixes, device_inputs=False):
     pkg.fill_uniform(dc, seed, 0)
     pkg.fill_uniform(da, seed, 1)
     pkg.fill_uniform(db, seed, 2)
-    plan = pkg.Plan(expr, _dt(pkg, dtype))
+    plan = pkg.Plan(expr, _dt(pkg, dtype), **plan_kw)
     plan.execute(dc, da, db)
     torch.cuda.synchronize()
+    assert plan.status() == 0
+    if keep is not None:
+        keep["desc"] = plan.describe()
     a, b = orc.uniform(seed, 1, na, dtype), orc.uniform(seed, 2, nb, dtype)
 
     def strides(idx):
@@ -139,6 +142,8 @@ def _slab_check(pkg, orc, torch, expr, dtype, seed, fixes, device_inputs=False):
         # elements outside the slab inside the span must not be compared against the slab's reference
         worst = max(worst, orc.rel_error(got[touched], c_ref[touched]))
     plan.close()
+    if keep is not None:
+        keep["dc"] = dc
     del dc, da, db
     torch.cuda.empty_cache()
     return worst
@@ -170,6 +175,62 @@ def test_config5_one_eighth_slabs(pkg, orc, torch_cuda):
     err = _slab_check(pkg, orc, torch_cuda, expr, dt, seed,
                       [{"d": 0, "e": 0, "f": 0}, {"d": 39, "e": 39, "f": 4}, {"a": 3, "b": 1, "f": 2, "e": 7}])
     assert err <= TOL[dt]
+
+
+def _sampled_check(orc, torch, dc, expr, dtype, seed, count, rng_seed):
+    """`count` uniformly sampled output coordinates of a full-size run, recomputed on the host from the
+    counter-based inputs (the whole output need not exist on the host).  Returns max|got-ref| / max|ref|."""
+    p = orc.parse(expr)
+    names = p["out_idx"] + p["sum_idx"]
+    ext = dict(zip(names, p["out_ext"] + p["sum_ext"]))
+    nc, na, nb = orc.sizes(expr)
+    a = orc.uniform(seed, 1, na, dtype)
+    b = orc.uniform(seed, 2, nb, dtype)
+    rng = np.random.default_rng(rng_seed)
+    lin = np.sort(rng.integers(0, nc, size=count, dtype=np.int64))
+    coord, r = {}, lin.copy()
+    for i in p["out_idx"]:
+        coord[i] = r % ext[i]
+        r //= ext[i]
+
+    def offsets(idx, fixed):
+        off, acc = np.zeros(count, dtype=np.int64), 1
+        for i in idx:
+            off = off + (coord[i] if i in coord else fixed[i]) * acc
+            acc *= ext[i]
+        return off
+
+    ref = orc.uniform_at(seed, 0, lin, dtype).astype(np.float64)
+    sign = -1.0 if p["op"] == "-=" else 1.0
+    if p["op"] == "=":
+        ref[:] = 0.0
+    ks = [ext[i] for i in p["sum_idx"]]
+    for flat in range(int(np.prod(ks))):
+        fixed, q = {}, flat
+        for i, e in zip(p["sum_idx"], ks):
+            fixed[i] = q % e
+            q //= e
+        ref += sign * a[offsets(p["left_idx"], fixed)].astype(np.float64) * b[offsets(p["right_idx"], fixed)].astype(np.float64)
+    got = dc[torch.from_numpy(lin).cuda()].cpu().numpy().astype(np.float64)
+    return float(np.max(np.abs(got - ref)) / np.max(np.abs(ref)))
+
+
+def test_config5_full_size(pkg, orc, torch_cuda):
+    """The large configuration at its full extents on one GPU: 4.096e9 output elements (32.8 GB), offsets beyond
+    2^31 elements, 500 x 1000 tiles.  Checked on slabs at both ends and inside, and on 2e5 sampled coordinates."""
+    torch = torch_cuda
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * (1 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    expr, dt, seed = CONFIGS[4]
+    fixes = [{"d": 0, "e": 0, "f": 0}, {"d": 39, "e": 39, "f": 39}, {"d": 17, "e": 3, "f": 22}, {"a": 39, "b": 0, "c": 21, "e": 5, "f": 31}]
+    keep = {}
+    err = _slab_check(pkg, orc, torch, expr, dt, seed, fixes, keep=keep)
+    assert err <= TOL[dt], err
+    serr = _sampled_check(orc, torch, keep["dc"], expr, dt, seed, 200000, 5)
+    keep.clear()
+    torch.cuda.empty_cache()
+    assert serr <= TOL[dt], serr
 
 
 # ------------------------------------------------------- random expressions ----
@@ -400,6 +461,54 @@ def test_fp32_long_contractions_stay_within_tolerance(pkg, orc, torch_cuda, path
     err, d = _run(pkg, orc, torch_cuda, expr, "float32", 31, **kw)
     assert d["ksplit"] >= 16, d
     assert err <= TOL["float32"], (path, err, d)
+
+
+@pytest.mark.parametrize("n_b,mode", [(4096, "slices"), (8192, "passes")])
+def test_fp32_long_contractions_on_large_outputs(pkg, orc, torch_cuda, n_b, mode):
+    """K = 8192 under the default path on outputs of 64 MB (16 K slices fill the 1 GiB of slice scratch exactly) and
+    128 MB (slices would not fit: the contraction runs as 16 sequential passes of 512 products into C).  Either way
+    no tensor-core chain is longer than 512 and the result stays inside the fp32 gate."""
+    expr = "C [a,4096,b,%d] += sum(c,8192) * A [c,a] * B [c,b];" % n_b
+    keep = {}
+    err = _slab_check(pkg, orc, torch_cuda, expr, "float32", 33, [{"b": 0}, {"b": n_b - 1}, {"b": 1234}, {"a": 4095}], keep=keep)
+    d = keep["desc"]
+    keep.clear()
+    assert d["math"].startswith("tf32x3") and d["chain"] <= 512, d
+    assert (d["ksplit"] == 16 and d["passes"] == 1) if mode == "slices" else (d["passes"] == 16 and d["ksplit"] == 1), d
+    assert err <= TOL["float32"], (err, d)
+
+
+def test_a_wait_that_gives_up_is_reported_and_the_context_survives(pkg, orc, torch_cuda):
+    """Failure detection without a fault: with tc_options.test_fault the persistent kernel's producers leave one
+    stage unannounced and waits give up after 2^14 polls.  The kernel must end by itself, the status word must
+    name a wait, the host-pointer entry must return TC_ERR_DEVICE_WAIT, and a fresh plan must then run correctly."""
+    torch = torch_cuda
+    expr = "C [a,256,b,64,c,96] += sum(e,40) * A [e,a,b] * B [e,c];"
+    c0, a, b = orc.make_inputs(expr, 91)
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    for tile in ((128, 64), (64, 96)):
+        bad = pkg.Plan(expr, tile=tile, variant=3, test_fault=1)
+        dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+        bad.execute(dc, da, db)
+        torch.cuda.synchronize()          # returns: every wait is bounded
+        assert bad.status() in (1, 2, 3, 4, 5, 6, 7), "the skipped stage must make a wait give up"
+        bad.status_reset()
+        assert bad.status() == 0
+        bad.close()
+        good = pkg.Plan(expr, tile=tile, variant=3)
+        dc = torch.from_numpy(c0).cuda()
+        good.execute(dc, da, db)
+        torch.cuda.synchronize()
+        assert good.status() == 0 and orc.rel_error(dc.cpu().numpy(), ref) <= 1e-12
+        good.close()
+    # through the host-pointer entry the failure is a status code, not a silent wrong answer
+    big = "C [a,256,b,64,c,96,d,4] += sum(e,40) * A [e,a,b] * B [e,c,d];"   # 50 MB of output: slabs over two streams
+    c0, a, b = orc.make_inputs(big, 92)
+    bad = pkg.Plan(big, tile=(128, 64), variant=3, test_fault=1)
+    with pytest.raises(pkg.TcError) as e:
+        bad.execute_host(c0.copy(), a, b)
+    assert e.value.status == 9
+    bad.close()
 
 
 def test_tcgen05_small_problems_use_the_mma_sync_kernel(pkg):

@@ -91,3 +91,71 @@ def test_batched_index_is_unsupported_not_a_crash(pkg):
     with pytest.raises(pkg.TcError) as e:
         pkg.parse("t3 [a,4,b,4] += sum(d,4) * t2 [d,a,b] * v2 [b,d];")
     assert e.value.status == 3  # TC_ERR_UNSUPPORTED
+
+
+# ----------------------------------------------- pinned to the reference's own parser ----
+def _golden():
+    import json
+    import os
+    with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "grammar.json")) as f:
+        return json.load(f)
+
+
+def _same_record(mine, ref):
+    """The C++ parser's record against the reference's `temp_target` (tc_gen_inputs.py:108)."""
+    assert [mine["out"], mine["left"], mine["right"], mine["op"]] == [ref["out"], ref["left"], ref["right"], ref["op"]]
+    for k in ("out_idx", "sum_idx", "left_idx", "right_idx"):
+        assert mine[k] == ref[k], k
+    assert mine["out_ext"] + mine["sum_ext"] == ref["sizes"]
+    assert [[i, e] for i, e in zip(mine["out_idx"] + mine["sum_idx"], mine["out_ext"] + mine["sum_ext"])] == ref["size_pairs"]
+
+
+def test_every_benchmark_line_parses_as_the_reference_parser_does(pkg, orc):
+    """tests/golden/grammar.json holds what tc_gen_Outer_Group (cogent/src/algs/bases/tc_gen_inputs.py:15-147)
+    returned for the expression line of each of its 48 input files (made by tests/golden/make_grammar_golden.py)."""
+    g = _golden()
+    assert len(g["tccg"]) == 48
+    for tag, item in sorted(g["tccg"].items()):
+        _same_record(pkg.parse(item["line"]), item["parsed"])
+        _same_record(orc.parse(item["line"]), item["parsed"])   # the checker's restatement is pinned by the same records
+        pkg.Plan(item["line"]).close()
+
+
+def test_accept_and_reject_where_the_reference_parser_does(pkg):
+    for item in _golden()["forms"]:
+        ref = item["parsed"]
+        if "raises" in ref:   # the reference crashes (IndexError / ValueError): a parse-error status here
+            with pytest.raises(pkg.TcError) as e:
+                pkg.parse(item["line"])
+            assert e.value.status == 1, item["line"]
+        else:
+            _same_record(pkg.parse(item["line"]), ref)
+
+
+def test_live_reference_parser_where_its_tree_is_present(pkg):
+    """Where the reference tree lies beside the repository, regenerate the records from its parser and compare
+    them with the committed file and, on random well-formed lines, with the C++ parser directly."""
+    import contextlib
+    import importlib.util
+    import io
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_grammar_golden", os.path.join(here, "golden", "make_grammar_golden.py"))
+    mk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mk)
+    cogent = os.path.join(mk.REF_DEFAULT, "cogent")
+    if not os.path.isdir(cogent):
+        pytest.skip("reference tree not present")
+    import sys
+    sys.path.insert(0, cogent)
+    try:
+        import src.algs.bases.tc_gen_inputs as tgi
+    finally:
+        sys.path.remove(cogent)
+    g = _golden()
+    for tag, item in g["tccg"].items():
+        assert mk.reference_parse(tgi, item["line"]) == item["parsed"], tag
+    rng = random.Random(17)
+    for n in range(200):
+        expr = _random_expr(rng, multi_char=(n % 3 == 0))
+        _same_record(pkg.parse(expr), mk.reference_parse(tgi, expr))

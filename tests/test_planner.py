@@ -195,3 +195,27 @@ def test_index_classes_reproduce_the_contraction(pkg, orc):
         assert orc.rel_error(got, want) <= 1e-12, (expr, d["M"], d["N"], d["K"])
         seen_split += any(dd["extent"] == 4 and dd["s_out"] != 1 for dd in d["M"][1:2])
     assert seen_split > 0  # the digit re-ordering was exercised
+
+
+def test_no_default_fp32_plan_runs_a_tensor_core_chain_longer_than_512(pkg):
+    """fp32 on the tensor cores accumulates with truncation, so the planner bounds every accumulation chain:
+    K slices where their scratch fits 1 GiB, sequential passes into C beyond that."""
+    import random
+    rng = random.Random(9)
+    seen = set()
+    for n in range(300):
+        m = rng.choice([64, 96, 500, 4096, 20000, 60000])
+        nn = rng.choice([64, 128, 1000, 4096, 30000])
+        k = rng.choice([16, 500, 512, 513, 1024, 4100, 8192, 50000])
+        expr = "C [a,%d,b,%d] %s sum(c,%d) * A [c,a] * B [c,b];" % (m, nn, rng.choice(["+=", "-=", "="]), k)
+        for path in (pkg.PATH_AUTO, pkg.PATH_TCGEN05, pkg.PATH_3XTF32):
+            d = _plan(pkg, expr, "float32", path=path).describe()
+            assert d["math"].startswith("tf32x3")
+            assert d["chain"] <= 512, (expr, d)
+            assert d["passes"] == 1 or d["ksplit"] == 1
+            assert d["workspace_bytes"] <= (1 << 30) + 128 * 128 * 4 * d["ksplit"] * 148, (expr, d)
+            seen.add("passes" if d["passes"] > 1 else "slices" if d["ksplit"] > 1 else "single")
+    assert seen == {"passes", "slices", "single"}
+    # the caller may override the rule explicitly, and FFMA never needs it
+    assert _plan(pkg, "C [a,4096,b,8192] += sum(c,8192) * A [c,a] * B [c,b];", "float32", split_k=1).describe()["chain"] == 8192
+    assert _plan(pkg, "C [a,4096,b,8192] += sum(c,8192) * A [c,a] * B [c,b];", "float32", path=pkg.PATH_FFMA).describe()["passes"] == 1
