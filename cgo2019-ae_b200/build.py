@@ -46,7 +46,17 @@ def _generate_kernel_units():
             with open(path, "w") as f:
                 f.write(body)
         units.append(path)
-    ws = text[text.index("#define TC_WS_KERNEL_LIST"):]
+    wc = text[text.index("#define TC_WC_KERNEL_LIST"):]
+    for m in re.finditer(r"^\s*X\((\w+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", wc, re.M):
+        name, bm, groups, wgm, wgn, st, _variant = m.groups()
+        body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'
+                "TC_DEFINE_WC_INST(tc_inst_%s, %s, %s, %s, %s, %s)\n" % (name, bm, groups, wgm, wgn, st))
+        path = os.path.join(OBJ, "gen_%s.cu" % name)
+        if not os.path.exists(path) or open(path).read() != body:
+            with open(path, "w") as f:
+                f.write(body)
+        units.append(path)
+    ws = text[text.index("#define TC_WS_KERNEL_LIST"):text.index("#define TC_WC_KERNEL_LIST")]
     for m in re.finditer(r"^\s*X\((\w+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", ws, re.M):
         name, bm, bn, st, _variant = m.groups()
         body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'

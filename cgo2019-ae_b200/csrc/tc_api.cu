@@ -67,6 +67,10 @@ TC_KERNEL_LIST(TC_DECLARE)
   extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 TC_WS_KERNEL_LIST(TC_DECLARE_WS)
 #undef TC_DECLARE_WS
+#define TC_DECLARE_WC(NAME, BM, GROUPS, WGM, WGN, STAGES, VARIANT) \
+  extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+TC_WC_KERNEL_LIST(TC_DECLARE_WC)
+#undef TC_DECLARE_WC
 
 namespace {
 struct KernelEntry {
@@ -77,9 +81,11 @@ struct KernelEntry {
 template <typename T> constexpr int dtype_of() { return sizeof(T) == 8 ? TC_F64 : TC_F32; }
 #define TC_ENTRY(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB, VARIANT) {#NAME, dtype_of<T>(), MATH, BM, BN, VARIANT, tc_inst_##NAME},
 #define TC_WS_ENTRY(NAME, BM, BN, STAGES, VARIANT) {#NAME, TC_F64, TC_MATH_DMMA, BM, BN, VARIANT, tc_inst_##NAME},
-const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY) TC_WS_KERNEL_LIST(TC_WS_ENTRY)};
+#define TC_WC_ENTRY(NAME, BM, GROUPS, WGM, WGN, STAGES, VARIANT) {#NAME, TC_F64, TC_MATH_DMMA, BM, 64, VARIANT, tc_inst_##NAME},
+const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY) TC_WS_KERNEL_LIST(TC_WS_ENTRY) TC_WC_KERNEL_LIST(TC_WC_ENTRY)};
 #undef TC_ENTRY
 #undef TC_WS_ENTRY
+#undef TC_WC_ENTRY
 
 const KernelEntry* find_kernel(int dtype, int math, int bm, int bn, int variant) {
   for (const KernelEntry& k : kKernels)
@@ -171,7 +177,17 @@ int tc_kernel_shape(const TcKernelChoice& c, int* threads, int* smem_bytes, int*
   return fn(mode_of(c.vec_x, c.kvec_x), mode_of(c.vec_y, c.kvec_y), nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_QUERY, threads, smem_bytes);
 }
 
+static int kernels_prepare_one(const TcKernelChoice& c);
 int tc_kernels_prepare(const TcKernelChoice& c) {
+  int st = kernels_prepare_one(c);
+  if (st == TC_OK && tc_kernel_is_c_resident(c)) {  // its stand-in for outputs the copy engine cannot address as boxes
+    TcKernelChoice alt = c;
+    alt.variant = 2;
+    st = kernels_prepare_one(alt);
+  }
+  return st;
+}
+static int kernels_prepare_one(const TcKernelChoice& c) {
   // Both loader variants of each operand: a misaligned base pointer at execute
   // time demotes 16-byte loads to element loads.
   tc_inst_fn fn = pick_inst(c);
@@ -217,6 +233,18 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
       a.c_tensor = 2;
   }
   tc_inst_fn fn = pick_inst(c);
+  if (tc_kernel_is_c_resident(c)) {
+    // The C-resident kernel moves whole output tiles as boxes of the rank-5 view of C: the view must exist and the
+    // base must be 16-byte aligned.  Otherwise the same tiles run on the persistent kernel that reaches C through
+    // reduce-adds or plain read-modify-writes.
+    const bool ok = c.tma_ct && p.opt.tma != 1 && p.opt.tma != 2 &&
+                    encode_output_map(&a.tmap_ct, C, a.cmap, (uint32_t)a.bm, 2, (uint32_t)a.bn / 2);
+    if (!ok) {
+      TcKernelChoice alt = c;
+      alt.variant = 2;
+      fn = pick_inst(alt);
+    }
+  }
   if (!fn) return TC_ERR_UNSUPPORTED;
   // Plans whose contraction runs as sequential passes (fp32 tensor-core chains kept short on outputs too large
   // for slice scratch): one launch per range of k, the first with the expression's operator, the rest adding.

@@ -6,6 +6,7 @@
 #pragma once
 #include "tc_kernels.cuh"
 #include "tc_ws_kernel.cuh"
+#include "tc_wc_kernel.cuh"
 
 enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3 };
 
@@ -65,8 +66,8 @@ int run_persistent(Kern kern, const TcKernelArgs* a, void* C, const void* X, con
   int dev = 0, sms = 0;
   TC_CUDA_OK(cudaGetDevice(&dev));
   TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const unsigned tiles = a->tiles_m * a->tiles_n;
-  const unsigned grid = (tiles + 1) / 2 < (unsigned)sms ? (tiles + 1) / 2 : (unsigned)sms;  // one persistent CTA per SM
+  const unsigned tiles = a->tiles_m * a->tiles_n, per_cta = CF::GROUPS;  // a CTA's groups take consecutive tiles
+  const unsigned grid = (tiles + per_cta - 1) / per_cta < (unsigned)sms ? (tiles + per_cta - 1) / per_cta : (unsigned)sms;  // one persistent CTA per SM
   kern<<<grid, CF::CTA_THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<T*>(C), static_cast<const T*>(X),
                                                            static_cast<const T*>(Y));
   TC_CUDA_OK(cudaGetLastError());
@@ -78,7 +79,25 @@ int run_ws_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
                    int* threads, int* smem_bytes) {
   return run_persistent<CF>(tc_ws_dmma_kernel<CF>, a, C, X, Y, stream, mode, threads, smem_bytes);
 }
+template <class CF>
+int run_wc_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
+                   int* threads, int* smem_bytes) {
+  return run_persistent<CF>(tc_wc_dmma_kernel<CF>, a, C, X, Y, stream, mode, threads, smem_bytes);
+}
 }  // namespace tck
+
+#define TC_WC_CASE(MX, MY, BM, GROUPS, WGM, WGN, STAGES) \
+  if (vx == MX && vy == MY) return tck::run_wc_variant<tck::WcCfg<BM, GROUPS, WGM, WGN, STAGES, MX, MY>>(a, C, X, Y, s, mode, threads, smem);
+#define TC_WC_ROW(MX, BM, GROUPS, WGM, WGN, STAGES) \
+  TC_WC_CASE(MX, 0, BM, GROUPS, WGM, WGN, STAGES) TC_WC_CASE(MX, 1, BM, GROUPS, WGM, WGN, STAGES) \
+  TC_WC_CASE(MX, 2, BM, GROUPS, WGM, WGN, STAGES) TC_WC_CASE(MX, 3, BM, GROUPS, WGM, WGN, STAGES)
+#define TC_DEFINE_WC_INST(NAME, BM, GROUPS, WGM, WGN, STAGES)                                               \
+  extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,         \
+                      cudaStream_t s, int mode, int* threads, int* smem) {                                  \
+    TC_WC_ROW(0, BM, GROUPS, WGM, WGN, STAGES) TC_WC_ROW(1, BM, GROUPS, WGM, WGN, STAGES)                   \
+    TC_WC_ROW(2, BM, GROUPS, WGM, WGN, STAGES) TC_WC_ROW(3, BM, GROUPS, WGM, WGN, STAGES)                   \
+    return TC_ERR_INVALID_ARG;                                                                              \
+  }
 
 #define TC_WS_CASE(MX, MY, BM, BN, STAGES) \
   if (vx == MX && vy == MY) return tck::run_ws_variant<tck::WsCfg<BM, BN, STAGES, MX, MY>>(a, C, X, Y, s, mode, threads, smem);

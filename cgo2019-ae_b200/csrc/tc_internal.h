@@ -81,6 +81,7 @@ struct TcKernelArgs {
   TcDims M, N;
   uint32_t Mflat, Nflat, Kflat;
   uint32_t tiles_m, tiles_n;
+  uint32_t mblock_w;  // persistent kernels walk the tiles in column blocks of this many M tiles (0: M fastest over all of M)
   int32_t bm, bn;    // CTA tile of the chosen kernel
   int32_t c_mode;    // 0: read-modify-write epilogue, 1: accumulators start from C,
                      // 2: bulk asynchronous reduce-add from shared memory (persistent kernels)
@@ -179,7 +180,9 @@ bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant);
 const char* tc_kernel_name(const TcKernelChoice& c);
 inline bool tc_kernel_is_persistent(const TcKernelChoice& c) {
   return c.math == TC_MATH_DMMA && c.variant >= 2;
-}  // registry name, "?" if absent
+}
+// ... and keeps its output tile resident in shared memory (tc_wc_kernel.cuh)
+inline bool tc_kernel_is_c_resident(const TcKernelChoice& c) { return c.math == TC_MATH_DMMA && c.variant == 3; }
 constexpr int TC_BK = 16;  // contraction step of every kernel
 
 #endif  // TC_INTERNAL_H_

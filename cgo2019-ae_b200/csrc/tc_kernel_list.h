@@ -40,4 +40,10 @@
   X(dmma_ws_64x96, 64, 96, 3, 2)       \
   X(dmma_ws_64x64, 64, 64, 4, 2)
 
+// Persistent fp64 kernels that keep the output tile resident in shared memory (tc_wc_kernel.cuh): GROUPS consumer
+// groups of WGM x WGN warps, each on its own BM x 64 tile.
+//   X(name, BM, GROUPS, WGM, WGN, STAGES, VARIANT)
+#define TC_WC_KERNEL_LIST(X)            \
+  X(dmma_wc_128x64, 128, 1, 4, 2, 3, 3)
+
 #endif  // TC_KERNEL_LIST_H_

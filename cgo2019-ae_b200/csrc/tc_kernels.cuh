@@ -226,6 +226,23 @@ __device__ __forceinline__ void decode(const TcDims& d, uint32_t flat, uint32_t 
   *off_out = oo;
 }
 
+// Tile number -> tile coordinates for the persistent kernels.  Plain order: M fastest over all of M.  With
+// mblock_w = w > 0 the tiles are walked in column blocks of w M tiles: inside a block M is fastest, then N, and a
+// block is finished over all of N before the next begins.  The tiles in flight at any time (one per consumer group
+// and SM, consecutive numbers) then share a handful of operand tiles -- w tiles of X that stay hot in L2 for the
+// whole sweep over N, and a few tiles of Y -- instead of sweeping ALL of X once per row of tiles, which for large
+// outputs pushes the operands out of L2 behind the stream of C (measured: 26.6 -> 22.2 TFLOP/s as the output grew
+// from 4 to 33 GB).
+__device__ __forceinline__ void tile_coords(const TcKernelArgs& p, uint32_t tile, uint32_t* tm, uint32_t* tn) {
+  const uint32_t w = p.mblock_w;
+  if (w == 0) { *tm = tile % p.tiles_m; *tn = tile / p.tiles_m; return; }
+  const uint32_t per_block = w * p.tiles_n;
+  const uint32_t blk = tile / per_block, r = tile - blk * per_block;
+  const uint32_t left = p.tiles_m - blk * w, wb = left < w ? left : w;  // the last block may be narrower
+  *tn = r / wb;
+  *tm = blk * w + (r - *tn * wb);
+}
+
 // ------------------------------------------------------------- loaders ----
 // 16-byte loads along the external index: thread -> (vector of VW externals, k).
 template <class CF, int ROWS, int LD>

@@ -84,6 +84,50 @@ int64_t span(const std::vector<int64_t>& ext, const std::vector<int64_t>& str) {
   return s;
 }
 
+// A consumer warp's batch of 8 output rows (n = base + 2g + parity, WM consecutive m) of the persistent fp64
+// kernels is one box of a rank-5 view of C when, with each class's dimensions fused as far as they are
+// contiguous IN C (the flattened index does not change by that),
+//   * the warp's WM outputs of a row sit inside one contiguous run: the fastest fused M dimension has
+//     stride 1 and is the only one, or a multiple of the tile,
+//   * the 16 rows of two batches stay inside N's fastest fused dimension (the only one, or a multiple of
+//     16), which must be even so that n splits into (parity, n / 2),
+//   * what is left of both classes fits the two remaining tensor dimensions, and every stride keeps
+//     16-byte alignment.
+// Then one tiled TMA reduce-add (or store) replaces eight per-row bulk copies (*per_warp); a whole bm x bn tile
+// is a box too when its bn rows stay inside N's fastest fused dimension (*per_tile).
+void out_box_view(const TcKernelArgs& a, int es, int bm, int bn, TcOutMap* map, bool* per_warp, bool* per_tile) {
+  *per_warp = false;
+  *per_tile = false;
+  *map = TcOutMap{};
+  if (!(es == 8 && a.vec_c == 4 && a.M.n >= 1 && a.N.n >= 1 && a.M.s_out[0] == 1)) return;
+  auto fuse_out = [](const TcDims& cls, std::vector<int64_t>* ext, std::vector<int64_t>* str) {
+    for (int d = 0; d < cls.n; ++d) {
+      if (!ext->empty() && cls.s_out[d] == str->back() * ext->back()) ext->back() *= cls.extent[d];
+      else { ext->push_back(cls.extent[d]); str->push_back(cls.s_out[d]); }
+    }
+  };
+  std::vector<int64_t> me, ms, ne, ns;
+  fuse_out(a.M, &me, &ms);
+  fuse_out(a.N, &ne, &ns);
+  bool ok = (me.size() == 1 || me[0] % bm == 0) && ne[0] % 2 == 0 && (ne.size() == 1 || ne[0] % 16 == 0) &&
+            (me.size() - 1) + (ne.size() - 1) <= 2;
+  for (size_t d = 0; d < ne.size(); ++d) ok = ok && ns[d] % 2 == 0 && ns[d] > 0 && ns[d] < (int64_t(1) << 36) && ne[d] < (int64_t(1) << 31);
+  for (size_t d = 1; d < me.size(); ++d) ok = ok && ms[d] % 2 == 0 && ms[d] > 0 && ms[d] < (int64_t(1) << 36) && me[d] < (int64_t(1) << 31);
+  ok = ok && me[0] < (int64_t(1) << 31);
+  if (!ok) return;
+  TcOutMap& o = *map;
+  o.e0 = (uint32_t)me[0];
+  o.f0 = (uint32_t)ne[0];
+  o.stride_n = ns[0];
+  o.ne = (int32_t)ne.size() - 1;
+  o.me = (int32_t)me.size() - 1;
+  int r = 0;
+  for (size_t d = 1; d < ne.size(); ++d, ++r) { o.ext[r] = (uint32_t)ne[d]; o.stride[r] = ns[d]; }
+  for (size_t d = 1; d < me.size(); ++d, ++r) { o.ext[r] = (uint32_t)me[d]; o.stride[r] = ms[d]; }
+  *per_warp = true;
+  *per_tile = ne.size() == 1 || ne[0] % bn == 0;
+}
+
 }  // namespace
 
 int tc_plan_build(tc_plan* p, std::string* why) {
@@ -311,6 +355,18 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       if (waste(nf, 96) + 0.02 < waste(nf, 64)) { bm = 64; bn = 96; }
       else { bm = 128; bn = 64; }
       variant = 2;
+      // Short contractions are bound by the read and write of C, not by the tensor pipe: per output element the
+      // memory system moves 16 bytes (HBM, ~6.5 TB/s) while the pipe does 2 K flops (~37 TFLOP/s), so below
+      // K ~ 46 the output traffic is the longer of the two.  There the kernel that keeps the output tile resident
+      // in shared memory (tiled loads and stores of C instead of reduce-adds) measured 10-15 % faster; it needs whole tiles to be boxes of a rank-5 view of C.
+      TcOutMap view;
+      bool per_warp = false, per_tile = false;
+      out_box_view(a, es, 128, 64, &view, &per_warp, &per_tile);
+      const double t_out = 2.0 * es / 6.5e12, t_pipe = 2.0 * (double)kf / 37.0e12;  // per output element
+      if (per_tile && t_out >= 0.85 * t_pipe && p->opt.tma != 1 && p->opt.tma != 2 && p->opt.c_path == 0 &&
+          waste(nf, 64) <= 1.1 && waste(mf, 128) <= 1.1) {
+        bm = 128; bn = 64; variant = 3;
+      }
     }
     if (c.math != TC_MATH_DMMA && c.dtype == TC_F32) {
       // fp32: 96 rows instead of 128 when that makes the tile a whole number of the output's contiguous
@@ -355,6 +411,10 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   a.tiles_n = (uint32_t)((nf + bn - 1) / bn);
   const int64_t tiles = (int64_t)a.tiles_m * a.tiles_n;
   const int bk = TC_BK;
+  // Persistent kernels: walk the tiles in column blocks of 32 M tiles when one sweep over all of M would drag more
+  // than a few MB of X through L2 per row of tiles (see tile_coords in tc_kernels.cuh).
+  a.mblock_w = 0;
+  if (tc_kernel_is_persistent(c) && a.tiles_m > 64 && a.tiles_n > 1 && (double)mf * (double)kf * es > 4.0e6) a.mblock_w = 32;
 
   // K split: only when the tile count cannot fill the GPU and K is long.
   int64_t ksplit = 1;
@@ -415,49 +475,11 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     }
   }
 
-  // Persistent fp64 kernel: a consumer warp's batch of 8 output rows (n = base + 2g + parity, WM consecutive
-  // m) is one box of a rank-5 view of C when, with each class's dimensions fused as far as they are
-  // contiguous IN C (the flattened index does not change by that),
-  //   * the warp's WM outputs of a row sit inside one contiguous run: the fastest fused M dimension has
-  //     stride 1 and is the only one, or a multiple of the tile,
-  //   * the 16 rows of two batches stay inside N's fastest fused dimension (the only one, or a multiple of
-  //     16), which must be even so that n splits into (parity, n / 2),
-  //   * what is left of both classes fits the two remaining tensor dimensions, and every stride keeps
-  //     16-byte alignment.
-  // Then one tiled TMA reduce-add (or store) replaces eight per-row bulk copies.
+  // Persistent fp64 kernels: which output batches / tiles are boxes of a rank-5 view of C (see out_box_view).
   c.tma_c = false;
   c.tma_ct = false;
   a.cmap = TcOutMap{};
-  if (persistent && es == 8 && a.vec_c == 4 && a.M.n >= 1 && a.N.n >= 1 && a.M.s_out[0] == 1) {
-    auto fuse_out = [](const TcDims& cls, std::vector<int64_t>* ext, std::vector<int64_t>* str) {
-      for (int d = 0; d < cls.n; ++d) {
-        if (!ext->empty() && cls.s_out[d] == str->back() * ext->back()) ext->back() *= cls.extent[d];
-        else { ext->push_back(cls.extent[d]); str->push_back(cls.s_out[d]); }
-      }
-    };
-    std::vector<int64_t> me, ms, ne, ns;
-    fuse_out(a.M, &me, &ms);
-    fuse_out(a.N, &ne, &ns);
-    bool ok = (me.size() == 1 || me[0] % bm == 0) && ne[0] % 2 == 0 && (ne.size() == 1 || ne[0] % 16 == 0) &&
-              (me.size() - 1) + (ne.size() - 1) <= 2;
-    for (size_t d = 0; d < ne.size(); ++d) ok = ok && ns[d] % 2 == 0 && ns[d] > 0 && ns[d] < (int64_t(1) << 36) && ne[d] < (int64_t(1) << 31);
-    for (size_t d = 1; d < me.size(); ++d) ok = ok && ms[d] % 2 == 0 && ms[d] > 0 && ms[d] < (int64_t(1) << 36) && me[d] < (int64_t(1) << 31);
-    ok = ok && me[0] < (int64_t(1) << 31);
-    if (ok) {
-      TcOutMap& o = a.cmap;
-      o.e0 = (uint32_t)me[0];
-      o.f0 = (uint32_t)ne[0];
-      o.stride_n = ns[0];
-      o.ne = (int32_t)ne.size() - 1;
-      o.me = (int32_t)me.size() - 1;
-      int r = 0;
-      for (size_t d = 1; d < ne.size(); ++d, ++r) { o.ext[r] = (uint32_t)ne[d]; o.stride[r] = ns[d]; }
-      for (size_t d = 1; d < me.size(); ++d, ++r) { o.ext[r] = (uint32_t)me[d]; o.stride[r] = ms[d]; }
-      c.tma_c = true;
-      // a whole tile is a box too when its bn rows stay inside N's fastest fused dimension
-      c.tma_ct = ne.size() == 1 || ne[0] % bn == 0;
-    }
-  }
+  if (persistent) out_box_view(a, es, bm, bn, &a.cmap, &c.tma_c, &c.tma_ct);
 
   double prod = 1.0;
   for (int64_t x : p->idx_extent) prod *= (double)x;
@@ -488,7 +510,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
-      << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"ksplit\":" << a.ksplit
+      << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"mblock_w\":" << a.mblock_w << ",\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << std::min<uint32_t>(a.k_chunk, a.Kflat) << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")

@@ -360,7 +360,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       int64_t* offy_n = offc_m + BM;
       int64_t* offc_n = offy_n + BN;
       if (!mbar_wait(&tab_empty[par], ((titer >> 1) & 1) ^ 1, p.status, 1, p.spin_limit)) return;
-      const uint32_t m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+      uint32_t tm, tn;
+      tile_coords(p, tile, &tm, &tn);
+      const uint32_t m0 = tm * BM, n0 = tn * BN;
       for (int i = ptid; i < BM + BN; i += CF::THREADS) {
         if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
         else decode(p.N, n0 + (i - BM), p.Nflat, &offy_n[i - BM], &offc_n[i - BM]);
@@ -488,7 +490,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // Tensor form of the same idea: a batch of 8 rows is one box of the rank-5 descriptor of C, so one tiled
     // TMA reduce-add (or store) per batch replaces eight per-row copies.  Rows and columns beyond the tensor are
     // clipped by the copy engine; boxes that lie outside altogether are not issued.
-    const uint32_t m_idx = (tile % p.tiles_m) * BM + wm0, n_base = (tile / p.tiles_m) * BN + wn0;
+    uint32_t tm, tn;
+    tile_coords(p, tile, &tm, &tn);
+    const uint32_t m_idx = tm * BM + wm0, n_base = tn * BN + wn0;
     if (tile_out) {
       // Whole tile through the shared staging area, filled in the order g0, g1, g0, ...: use number u may start
       // once use u - 1 has been read out.  After the first wait the two groups stay out of phase.

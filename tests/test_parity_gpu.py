@@ -62,7 +62,7 @@ def test_config1_full_size_all_paths(pkg, orc, torch_cuda):
     for kw in ({}, {"path": pkg.PATH_DFMA}, {"tile": (128, 128)}, {"tile": (128, 64), "variant": 2},
                {"tile": (64, 96)}, {"tile": (64, 64), "split_k": 2}, {"tile": (128, 64), "variant": 3},
                {"tile": (64, 96), "variant": 3}, {"tile": (64, 64), "variant": 3},
-               {"tile": (128, 64), "variant": 3, "c_path": 1}):
+               {"tile": (128, 64), "variant": 3, "c_path": 1}, {"tile": (128, 64), "variant": 4}):
         err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
         assert err <= TOL[dt], (kw, err)
 
@@ -92,7 +92,8 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
                    {"tile": (64, 64), "l2_prefetch": 1}, {"tile": (64, 64), "c_path": 2},
                    {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3},
                    {"tile": (64, 64), "variant": 3, "c_path": 2}, {"tile": (128, 64), "variant": 3, "c_path": 1},
-                   {"tile": (64, 96), "variant": 3, "c_path": 1, "l2_prefetch": 2}, {"tile": (128, 64), "variant": 3, "tma": 1}):
+                   {"tile": (64, 96), "variant": 3, "c_path": 1, "l2_prefetch": 2}, {"tile": (128, 64), "variant": 3, "tma": 1},
+                   {"tile": (128, 64), "variant": 4}, {"tile": (128, 64), "variant": 4, "tma": 3}):
             err, _ = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
             assert err <= TOL[dt], (expr, kw, err)
 
@@ -265,6 +266,8 @@ def test_random_midsize_contractions_with_forced_kernels_and_options(pkg, orc, t
         expr = orc.with_extents(expr, ext)
         kw64 = {"tile": rng.choice([(64, 96), (128, 64), (64, 64)]), "variant": 3, "c_path": rng.choice([0, 1, 2, 3]),
                 "tma": rng.choice([0, 1, 2, 3, 4]), "l2_prefetch": rng.choice([0, 1, 2])}
+        if done % 3 == 2:  # the output-resident kernel (falls back to the 128 x 64 persistent kernel where C is no box tensor)
+            kw64 = {"tile": (128, 64), "variant": 4, "tma": rng.choice([0, 3, 4])}
         kw32 = rng.choice([
             {"path": pkg.PATH_TCGEN05, "tile": rng.choice([(96, 128), (128, 128)]), "c_path": rng.choice([0, 1, 3]),
              "split_k": rng.choice([0, 1, 3])},
@@ -424,6 +427,37 @@ def test_persistent_tensor_box_epilogue(pkg, orc, torch_cuda, expr):
         assert np.array_equal(outs[0], outs[1]), (expr, tile)
 
 
+@pytest.mark.parametrize("expr", TENSOR_OUT + [
+    "C [a,40,b,40,c,40,d,40,e,10,f,2] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];",   # the large configuration's shape, reduced
+    "C [a,40,b,40,c,40,d,40,e,10,f,2] -= sum(g,7) * A [g,a,b,c] * B [d,e,f,g];",
+    "C [a,200,b,70] = sum(c,40) * A [c,a] * B [c,b];",                               # overwrite: no loads of C
+])
+@pytest.mark.parametrize("tile", [(128, 64)])
+def test_output_resident_kernel(pkg, orc, torch_cuda, expr, tile):
+    """The persistent kernel that keeps the output tile in shared memory (tiled TMA load of C, add in shared memory,
+    tiled TMA store) against the checker; where whole tiles are not boxes of C it must fall back and still be right."""
+    torch = torch_cuda
+    c0, a, b = orc.make_inputs(expr, 78, "float64")
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    ref2 = orc.contract(expr, ref.copy(), a, b, threads=orc.max_threads())
+    plan = pkg.Plan(expr, pkg.F64, tile=tile, variant=4)
+    dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+    plan.execute(dc, da, db)
+    torch.cuda.synchronize()
+    d = plan.describe()
+    assert d["kernel"] == "dmma_wc_%dx%d" % tile and plan.status() == 0
+    assert orc.rel_error(dc.cpu().numpy(), ref) <= TOL["float64"], (expr, d)
+    plan.execute(dc, da, db)       # a second pass over the result of the first
+    torch.cuda.synchronize()
+    assert plan.status() == 0 and orc.rel_error(dc.cpu().numpy(), ref2) <= TOL["float64"], (expr, d)
+    # off 16-byte alignment the copy engine cannot address C: same plan, stand-in kernel
+    pad = torch.cat([torch.zeros(1, dtype=torch.float64), torch.from_numpy(c0)]).cuda()
+    plan.execute(pad[1:], da, db)
+    torch.cuda.synchronize()
+    assert plan.status() == 0 and orc.rel_error(pad[1:].cpu().numpy(), ref) <= TOL["float64"], (expr, "unaligned")
+    plan.close()
+
+
 TCGEN05 = [
     ("C [a,96,b,128] = sum(c,8) * A [a,c] * B [b,c];", (96, 128)),                 # one tile, one group of 8 k
     ("C [a,96,b,128] += sum(c,16) * A [a,c] * B [b,c];", (96, 128)),               # one full K step
@@ -486,8 +520,8 @@ def test_a_wait_that_gives_up_is_reported_and_the_context_survives(pkg, orc, tor
     expr = "C [a,256,b,64,c,96] += sum(e,40) * A [e,a,b] * B [e,c];"
     c0, a, b = orc.make_inputs(expr, 91)
     ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
-    for tile in ((128, 64), (64, 96)):
-        bad = pkg.Plan(expr, tile=tile, variant=3, test_fault=1)
+    for tile, variant in (((128, 64), 3), ((64, 96), 3), ((128, 64), 4)):
+        bad = pkg.Plan(expr, tile=tile, variant=variant, test_fault=1)
         dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
         bad.execute(dc, da, db)
         torch.cuda.synchronize()          # returns: every wait is bounded
@@ -495,7 +529,7 @@ def test_a_wait_that_gives_up_is_reported_and_the_context_survives(pkg, orc, tor
         bad.status_reset()
         assert bad.status() == 0
         bad.close()
-        good = pkg.Plan(expr, tile=tile, variant=3)
+        good = pkg.Plan(expr, tile=tile, variant=variant)
         dc = torch.from_numpy(c0).cuda()
         good.execute(dc, da, db)
         torch.cuda.synchronize()

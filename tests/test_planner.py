@@ -54,7 +54,10 @@ def test_tile_choices(pkg):
     # fp64 with enough tiles: the persistent warp-specialised kernel (variant 2)
     assert d[1]["kernel"] == "dmma_ws_64x96" and d[1]["tiles"] == [13824, 1]   # N = 96 is exactly one tile wide
     assert d[2]["kernel"] == "dmma_ws_128x64" and d[2]["tiles"] == [32, 64]
-    assert d[4]["kernel"] == "dmma_ws_128x64" and d[4]["tiles"] == [500, 1000]
+    # output-bound fp64 (K = 40): the kernel that keeps the output tile resident in shared memory
+    assert d[4]["kernel"] == "dmma_wc_128x64" and d[4]["tiles"] == [500, 1000] and d[4]["tma_ct"] and d[4]["mblock_w"] == 32
+    longer = _plan(pkg, CONFIGS[4][0].replace("g,40", "g,96")).describe()
+    assert longer["kernel"] == "dmma_ws_128x64" and longer["tiles"] == [500, 1000]   # pipe-bound again
     # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
     # (default: the tcgen05 form of the three-TF32 product; the mma.sync form on request or for small problems)
     assert d[3]["math"] == "tf32x3_tcgen05" and d[3]["kernel"] == "tf32tc_96x128"
