@@ -27,6 +27,8 @@ plain malloc memory (what the reference's drivers pass) on configuration 2.
 
 --workload tccg (N = 1) times the reference's own benchmark list at its own sizes
 (read from baseline/_ref/tccg_items.json, made by baseline/make_tccg_table.py).
+--workload fused (N = 1) runs nine contractions that share one output as one fused pass
+and one by one.
 
 --impl reference times the reference's CPU loop-nest path (its restatement in
 oracle/, OpenMP over the outermost output loop on all host cores) on a bounded
@@ -63,6 +65,7 @@ TOL = {"f64": 1e-12, "f32": 1e-5}
 NCU_TRAFFIC_BYTES = {
     ("dmma_ws_64x96", "cfg2"): 1984793088, ("dmma_ws_128x64", "cfg3"): 1341919744, ("tf32tc_96x128", "cfg4"): 1472193280,
     ("dmma_ws_128x64", "cfg5_shard8"): 8369612032, ("dmma_ws_128x64", "cfg5"): 8 * 8369612032,
+    ("dmma_wc_128x64", "cfg5_shard8"): 8197418496, ("dmma_wc_128x64", "cfg5"): 8 * 8197418496,
 }
 
 
@@ -512,6 +515,65 @@ def run_tccg(args):
                                   "f64_min_gflops": f64[0] if f64 else None}}))
 
 
+# the nine CCSD(T) doubles terms in the expression grammar: (operator, left indices, right indices); every term has its
+# own pair of inputs and all accumulate into t3[h3,h2,h1,p6,p5,p4]
+FUSED_TERMS = [("-=", "p7,p4,h1,h2", "p7,h3,p6,p5"), ("-=", "p7,p4,h2,h3", "p7,h1,p6,p5"), ("+=", "p7,p4,h1,h3", "p7,h2,p6,p5"),
+               ("+=", "p7,p5,h1,h2", "p7,h3,p6,p4"), ("+=", "p7,p5,h2,h3", "p7,h1,p6,p4"), ("-=", "p7,p5,h1,h3", "p7,h2,p6,p4"),
+               ("-=", "p7,p6,h1,h2", "p7,h3,p5,p4"), ("-=", "p7,p6,h2,h3", "p7,h1,p5,p4"), ("+=", "p7,p6,h1,h3", "p7,h2,p5,p4")]
+
+
+def run_fused(args):
+    """Nine contractions into one output: one fused pass (tc_execute_fused) beside the same terms run one by one."""
+    import numpy as np
+    import torch
+    pkg, orc = entry.load_package(), entry.load_oracle()
+    torch.cuda.set_device(0)
+    E = 24
+    out = "t3 [h3,%d,h2,%d,h1,%d,p6,%d,p5,%d,p4,%d]" % ((E,) * 6)
+    lines = ["%s %s sum(p7,%d) * t2_%d [%s] * v2_%d [%s];" % (out, op, E, k + 1, l, k + 1, r) for k, (op, l, r) in enumerate(FUSED_TERMS)]
+    n_out, na, nb = orc.sizes(lines[0])
+    dc = torch.empty(n_out, dtype=torch.float64, device="cuda")
+    pkg.fill_uniform(dc, 9, 0)
+    das = [pkg.fill_uniform(torch.empty(na, dtype=torch.float64, device="cuda"), 10 + k, 1) for k in range(9)]
+    dbs = [pkg.fill_uniform(torch.empty(nb, dtype=torch.float64, device="cuda"), 10 + k, 2) for k in range(9)]
+    fused = pkg.FusedPlan(lines).commit()
+    plans = [pkg.Plan(l).commit() for l in lines]
+    # parity of the fused pass on a slab (p6, p5, p4 fixed): the nine loop nests of the checker, one after another
+    fused.execute(dc, das, dbs)
+    torch.cuda.synchronize()
+    worst = 0.0
+    for fix in ({"p6": 0, "p5": 0, "p4": 0}, {"p6": E - 1, "p5": 7, "p4": E - 1}):
+        idx = ["h3", "h2", "h1", "p6", "p5", "p4"]
+        st = {i: E ** n for n, i in enumerate(idx)}
+        oc = sum(fix[i] * st[i] for i in fix)
+        ref = orc.uniform(9, 0, E ** 3, np.float64, first=oc)
+        for k, line in enumerate(lines):
+            p = orc.parse(line)
+            a, b = orc.uniform(10 + k, 1, na), orc.uniform(10 + k, 2, nb)
+            strides, offs = {0: [st[i] for i in idx]}, {}
+            for t, key in ((1, "left_idx"), (2, "right_idx")):
+                s_, acc = [], 1
+                for i in p[key]:
+                    s_.append(acc)
+                    acc *= E
+                strides[t] = s_
+                offs[t] = sum(fix.get(i, 0) * x for i, x in zip(p[key], s_))
+            orc.contract(orc.with_extents(line, {i: 1 for i in fix}), ref, a[offs[1]:], b[offs[2]:], threads=host_threads(orc), strides=strides)
+        worst = max(worst, orc.rel_error(dc[oc:oc + E ** 3].cpu().numpy(), ref))
+    stream = torch.cuda.current_stream().cuda_stream
+    steps = max(1, args.steps)
+    t_f = time_passes(torch, lambda: fused.execute(dc, das, dbs, stream=stream), steps, max(1, args.warmup)) / steps
+    t_s = time_passes(torch, lambda: [q.execute(dc, a, b, stream=stream) for q, a, b in zip(plans, das, dbs)], steps, max(1, args.warmup)) / steps
+    d = fused.describe()
+    print(json.dumps({"workload": "fused: nine CCSD(T) doubles terms into one 6-D output, extents %d" % E, "metric": METRIC, "unit": "GFLOP/s",
+                      "n_gpus": 1, "dtype": "f64", "fused": {"gflops": d["flops"] / t_f * 1e-9, "ms": t_f * 1e3, "launches": 1,
+                                                               "algorithmic_bytes": d["bytes"], "kernel": d["kernel"], "box": d["box"]},
+                      "term_by_term": {"gflops": d["flops"] / t_s * 1e-9, "ms": t_s * 1e3, "launches": 9,
+                                       "algorithmic_bytes": d["bytes_term_by_term"], "kernel": plans[0].describe()["kernel"]},
+                      "parity": {"max_rel_err": worst, "tolerance": 1e-12, "ok": bool(worst <= 1e-12),
+                                 "how": "two slabs of the fused result against the nine loop nests applied in order"}}))
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -519,6 +581,8 @@ def run_ours(args):
 
     if args.workload == "tccg":
         return run_tccg(args)
+    if args.workload == "fused":
+        return run_fused(args)
     pkg, orc = entry.load_package(), entry.load_oracle()
     shard = __import__("importlib").import_module("cgo2019_ae_b200.shard")
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -800,7 +864,7 @@ def main():
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["tccg"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["tccg", "fused"])
     ap.add_argument("--path", default="auto", choices=["auto", "dmma", "dfma", "ffma", "3xtf32", "tcgen05"])
     args = ap.parse_args()
     if args.impl == "reference":

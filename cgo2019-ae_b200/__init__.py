@@ -69,6 +69,15 @@ _SIGNATURES = {
                                      ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
     "tc_execute_noalloc": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                           ctypes.c_void_p]),
+    "tc_plan_create_fused": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(ctypes.c_char_p), ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_void_p)]),
+    "tc_fused_set_extents": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                            ctypes.POINTER(ctypes.c_int64)]),
+    "tc_fused_commit": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_fused_describe": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]),
+    "tc_execute_fused": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                        ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
+    "tc_fused_destroy": (None, [ctypes.c_void_p]),
     "tc_execute_host": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]),
     "tc_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "tc_last_cuda_error": (ctypes.c_char_p, []),
@@ -238,6 +247,53 @@ class Plan:
     def close(self):
         if self._h:
             lib().tc_plan_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class FusedPlan:
+    """Several contractions accumulated into one output in a single pass over it (e.g. the nine CCSD(T) terms
+    of cogent/input_strings/ccsd_t/original-expressions/sd_t_d2.in); fp64."""
+
+    def __init__(self, exprs, dtype=F64, extents=None):
+        self._h = ctypes.c_void_p()
+        self.exprs = list(exprs)
+        arr = (ctypes.c_char_p * len(self.exprs))(*[e.encode() for e in self.exprs])
+        _check(lib().tc_plan_create_fused(len(self.exprs), arr, dtype, ctypes.byref(self._h)), "tc_plan_create_fused")
+        if extents:
+            names = list(extents)
+            an = (ctypes.c_char_p * len(names))(*[n.encode() for n in names])
+            ae = (ctypes.c_int64 * len(names))(*[int(extents[n]) for n in names])
+            _check(lib().tc_fused_set_extents(self._h, len(names), an, ae), "tc_fused_set_extents")
+
+    def commit(self):
+        _check(lib().tc_fused_commit(self._h), "tc_fused_commit")
+        return self
+
+    def describe(self):
+        buf = ctypes.create_string_buffer(8192)
+        st = lib().tc_fused_describe(self._h, buf, len(buf))
+        if st != 0:
+            raise TcError(st, "tc_fused_describe", json.loads(buf.value.decode() or "{}").get("error", ""))
+        return json.loads(buf.value.decode())
+
+    def execute(self, C, As, Bs, stream=None):
+        """C: the output; As[k], Bs[k]: left / right input of term k (torch CUDA tensors or device addresses)."""
+        n = len(self.exprs)
+        if len(As) != n or len(Bs) != n:
+            raise ValueError("one left and one right input per term")
+        pa = (ctypes.c_void_p * n)(*[_ptr(x) for x in As])
+        pb = (ctypes.c_void_p * n)(*[_ptr(x) for x in Bs])
+        _check(lib().tc_execute_fused(self._h, _ptr(C), pa, pb, _stream(stream, C)), "tc_execute_fused")
+
+    def close(self):
+        if self._h:
+            lib().tc_fused_destroy(self._h)
             self._h = ctypes.c_void_p()
 
     def __del__(self):

@@ -169,6 +169,26 @@ int tc_execute_noalloc(tc_plan* plan, void* C, const void* A, const void* B, voi
  * when a kernel of the call reported a wait that gave up. */
 int tc_execute_host(tc_plan* plan, void* C, const void* A, const void* B);
 
+/* ---- several contractions into one output ----------------------------------------------
+ * n expression lines that accumulate (+= / -=) into the SAME output tensor -- same name, same indices in the same
+ * order -- each with its own two inputs and its own assignment of the output's indices to them: the CCSD(T)
+ * triples terms (cogent/input_strings/ccsd_t/original-expressions/sd_t_d2.in:4-30; checker
+ * cogent/drivers/ccsd_t/code_main_sd2_1.c:561-613).  The reference meant to fuse such terms in one kernel but only
+ * stubbed it (cogent/src/codes/kernels/tc_code_kernel_fusion.py:6-205).  Here one kernel keeps a box of the output in
+ * shared memory, runs every term's product for that box on the FP64 tensor pipe and adds the box to C once: the
+ * output is read and written once instead of n times.  fp64; at most 16 terms; every input of a term may carry at
+ * most as many output indices as fit 64 rows of a box (TC_ERR_UNSUPPORTED otherwise).  Extents written in the
+ * first line are the defaults; index names are shared by all lines.
+ * A[k], B[k]: device pointers to the left / right input of term k (compact column-major). */
+typedef struct tc_fused_plan tc_fused_plan;
+int tc_plan_create_fused(int n, const char* const* exprs, int dtype, tc_fused_plan** out);
+int tc_fused_set_extents(tc_fused_plan* plan, int n, const char* const* index_names, const int64_t* extents);
+int tc_fused_commit(tc_fused_plan* plan);
+/* JSON: box shape, boxes, rows x cols per term, flops, bytes moved fused and term by term. */
+int tc_fused_describe(tc_fused_plan* plan, char* buf, size_t cap);
+int tc_execute_fused(tc_fused_plan* plan, void* C, const void* const* A, const void* const* B, void* stream);
+void tc_fused_destroy(tc_fused_plan* plan);
+
 /* ---- drop-in for the reference's generated entry ------------------------------------
  * What the generated sd_t_d2_fusion_ does for ONE expression (cogent/src/codes/kernels/tc_interface.py:
  * 1444-1598 -> 10-101): sizes in the order above, host pointers t3 (in/out), t2, v2; allocate, copy in,
