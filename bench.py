@@ -54,6 +54,9 @@ WORKLOADS = {
     "cfg5": ("C [a,40,b,40,c,40,d,40,e,40,f,40] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];", "f64", 4),
     # what one GPU runs when cfg5 is cut 8 ways along f (4.1 GB of output): small enough to profile
     "cfg5_shard8": ("C [a,40,b,40,c,40,d,40,e,40,f,5] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];", "f64", 4),
+    # small cases that run the kernels the five configurations do not reach (one CTA per tile, K slices + combine)
+    "kslices_f64": ("C [a,320,b,288] += sum(c,256,d,320) * A [a,c,d] * B [d,b,c];", "f64", 6),
+    "small_f32": ("C [a,48,b,40,c,36] += sum(d,64) * A [d,c,a] * B [b,d];", "f32", 7),
 }
 # contraction-split case for N > 1: small output, one long contraction index cut across the ranks
 KSPLIT_CASE = ("C [a,312,b,296] += sum(c,4096,d,312) * A [a,c,d] * B [d,b,c];", "f64", 13)

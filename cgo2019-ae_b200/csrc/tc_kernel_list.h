@@ -37,8 +37,7 @@
 //   X(name, BM, BN, STAGES, VARIANT)
 #define TC_WS_KERNEL_LIST(X) \
   X(dmma_ws_128x64, 128, 64, 3, 2)     \
-  X(dmma_ws_64x96, 64, 96, 3, 2)       \
-  X(dmma_ws_64x64, 64, 64, 4, 2)
+  X(dmma_ws_64x96, 64, 96, 3, 2)
 
 // Persistent fp64 kernels that keep the output tile resident in shared memory (tc_wc_kernel.cuh): GROUPS consumer
 // groups of WGM x WGN warps, each on its own BM x 64 tile.
