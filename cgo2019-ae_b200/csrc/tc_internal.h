@@ -158,6 +158,7 @@ struct tc_plan {
   int64_t size_c = 0, size_a = 0, size_b = 0;  // elements spanned (max offset + 1)
   int64_t count_c = 0, count_a = 0, count_b = 0;  // logical element counts
   double flops = 0, bytes = 0;
+  double estimate_s = 0;  // the planner's own estimate of one execute (persistent fp64 kernels; 0: none made)
   int launches = 1;
   std::string why;  // last planner message
 };

@@ -37,6 +37,7 @@
 //   X(name, BM, BN, STAGES, VARIANT)
 #define TC_WS_KERNEL_LIST(X) \
   X(dmma_ws_128x64, 128, 64, 3, 2)     \
+  X(dmma_ws_128x32, 128, 32, 4, 2)     \
   X(dmma_ws_64x96, 64, 96, 3, 2)
 
 // Persistent fp64 kernels that keep the output tile resident in shared memory (tc_wc_kernel.cuh): GROUPS consumer

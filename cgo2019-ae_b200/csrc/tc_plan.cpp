@@ -17,6 +17,7 @@
 // makes the same choice when it maps the input holding the output's fastest
 // index to the thread-block X dimension (enumeration.py:72-100).
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <numeric>
 #include <sstream>
@@ -352,21 +353,38 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   } else {
     auto waste = [&](int64_t n, int64_t b) { return (double)(((n + b - 1) / b) * b) / (double)n; };
     if (c.math == TC_MATH_DMMA) {
-      if (waste(nf, 96) + 0.02 < waste(nf, 64)) { bm = 64; bn = 96; }
-      else { bm = 128; bn = 64; }
-      variant = 2;
-      // Short contractions are bound by the read and write of C, not by the tensor pipe: per output element the
-      // memory system moves 16 bytes (HBM, ~6.5 TB/s) while the pipe does 2 K flops (~37 TFLOP/s), so below
-      // K ~ 46 the output traffic is the longer of the two.  There the kernel that keeps the output tile resident
-      // in shared memory (tiled loads and stores of C instead of reduce-adds) measured 10-15 % faster; it needs whole tiles to be boxes of a rank-5 view of C.
-      TcOutMap view;
-      bool per_warp = false, per_tile = false;
-      out_box_view(a, es, 128, 64, &view, &per_warp, &per_tile);
-      const double t_out = 2.0 * es / 6.5e12, t_pipe = 2.0 * (double)kf / 37.0e12;  // per output element
-      if (per_tile && t_out >= 0.85 * t_pipe && p->opt.tma != 1 && p->opt.tma != 2 && p->opt.c_path == 0 &&
-          waste(nf, 64) <= 1.1 && waste(mf, 128) <= 1.1) {
-        bm = 128; bn = 64; variant = 3;
+      // fp64 on the tensor pipe: the persistent kernels, chosen by a small cost model (this takes the place of the
+      // reference's ranking of mappings by estimated DRAM transactions, cogent/src/algs/bases/cost_models.py:191-574).
+      // Per candidate (tile, kernel) the time of one SM is  tiles per SM  x  max(products + idle, output bytes / rate):
+      //   products   2 bm bn K / (DMMA rate of one SM x the share of it the kernel's main loop reaches), K rounded up to 4;
+      //   idle       cycles per tile during which the pipe waits (epilogue, hand-overs), measured per kernel;
+      //   rate       what the kernel's way of reaching C sustains: reduce-adds of the copy engine 0.76 of the
+      //              measured copy bandwidth, tiled loads + stores of a resident tile 0.92;
+      //   tiles per SM is rounded up (wave quantisation) and edge tiles count in full (waste).
+      // Constants come from the B200 measurements recorded beside the kernels; the device's SM count is the plan's.
+      struct Cand { int bm, bn, variant; double idle, rate, eff; };  // eff: share of the DMMA rate its main loop reaches
+      const Cand cands[] = {{128, 64, 2, 2100.0, 0.76, 0.90}, {64, 96, 2, 800.0, 0.76, 0.86}, {128, 32, 2, 1500.0, 0.76, 0.84},
+                            {128, 64, 3, 1450.0, 0.92, 0.92}};
+      const double clk = 1.9e9, flop_per_clk = 37.0e12 / 148.0 / clk, byte_per_clk = 6.5e12 / 148.0 / clk;
+      const double kpad = (double)((kf + 3) / 4 * 4);
+      double best = 0;
+      p->why.clear();
+      for (const Cand& k : cands) {
+        if (!tc_kernel_exists(TC_F64, TC_MATH_DMMA, k.bm, k.bn, k.variant)) continue;
+        if (k.variant == 3) {  // needs whole tiles to be boxes of a rank-5 view of C, and nothing that pins the epilogue
+          TcOutMap view;
+          bool per_warp = false, per_tile = false;
+          out_box_view(a, es, k.bm, k.bn, &view, &per_warp, &per_tile);
+          if (!per_tile || p->opt.tma == 1 || p->opt.tma == 2 || p->opt.c_path != 0) continue;
+        }
+        const double tiles_c = (double)((mf + k.bm - 1) / k.bm) * (double)((nf + k.bn - 1) / k.bn);
+        const double products = 2.0 * k.bm * k.bn * kpad / (flop_per_clk * k.eff);
+        const double out_bytes = (e.op == 0 ? 1.0 : 2.0) * k.bm * k.bn * es;
+        const double per_tile = std::max(products + k.idle, out_bytes / (byte_per_clk * k.rate));
+        const double t = std::ceil(tiles_c / (double)sms) * per_tile / clk;
+        if (best == 0 || t < best * 0.98) { best = t; bm = k.bm; bn = k.bn; variant = k.variant; }
       }
+      p->estimate_s = best;
     }
     if (c.math != TC_MATH_DMMA && c.dtype == TC_F32) {
       // fp32: 96 rows instead of 128 when that makes the tile a whole number of the output's contiguous
@@ -510,7 +528,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
     o << ",\"Mflat\":" << a.Mflat << ",\"Nflat\":" << a.Nflat << ",\"Kflat\":" << a.Kflat
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
-      << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"mblock_w\":" << a.mblock_w << ",\"ksplit\":" << a.ksplit
+      << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"estimate_us\":" << p.estimate_s * 1e6 << ",\"mblock_w\":" << a.mblock_w << ",\"ksplit\":" << a.ksplit
       << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << std::min<uint32_t>(a.k_chunk, a.Kflat) << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")

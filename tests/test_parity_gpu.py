@@ -76,6 +76,10 @@ def test_reduced_configs(pkg, orc, torch_cuda, idx, extent):
     if idx == 4:
         expr = expr.replace("sum(g,10)", "sum(g,40)")
     tiles = [None, (128, 128), (64, 64)] + ([(128, 64), (128, 96), (64, 96)] if dt == "float64" else [(96, 128)])
+    if dt == "float64":
+        for kw in ({"tile": (128, 32), "variant": 3}, {"tile": (128, 32), "variant": 3, "c_path": 1}, {"tile": (128, 32), "variant": 3, "tma": 1}):
+            err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, **kw)
+            assert err <= TOL[dt] and d["kernel"] == "dmma_ws_128x32", (expr, kw, err)
     for tile in tiles:
         err, d = _run(pkg, orc, torch_cuda, expr, dt, seed, **({"tile": tile} if tile else {}))
         assert err <= TOL[dt], (expr, tile, err)
@@ -264,7 +268,7 @@ def test_random_midsize_contractions_with_forced_kernels_and_options(pkg, orc, t
         if np.prod([float(v) for v in ext.values()]) > 1.5e8:
             continue
         expr = orc.with_extents(expr, ext)
-        kw64 = {"tile": rng.choice([(64, 96), (128, 64)]), "variant": 3, "c_path": rng.choice([0, 1, 2, 3]),
+        kw64 = {"tile": rng.choice([(64, 96), (128, 64), (128, 32)]), "variant": 3, "c_path": rng.choice([0, 1, 2, 3]),
                 "tma": rng.choice([0, 1, 2, 3, 4]), "l2_prefetch": rng.choice([0, 1, 2])}
         if done % 3 == 2:  # the output-resident kernel (falls back to the 128 x 64 persistent kernel where C is no box tensor)
             kw64 = {"tile": (128, 64), "variant": 4, "tma": rng.choice([0, 3, 4])}
@@ -379,7 +383,8 @@ def test_edge_shapes(pkg, orc, torch_cuda, expr):
         assert err <= TOL[dt], (expr, dt, err, d)
     err, d = _run(pkg, orc, torch_cuda, expr, "float32", 42, path=pkg.PATH_FFMA)
     assert err <= TOL["float32"], (expr, err, d)
-    for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "c_path": 1}):
+    for kw in ({"path": pkg.PATH_DFMA}, {"tile": (128, 64), "variant": 3}, {"tile": (64, 96), "variant": 3, "c_path": 1},
+               {"tile": (128, 32), "variant": 3}, {"tile": (128, 64), "variant": 4}):
         err, _ = _run(pkg, orc, torch_cuda, expr, "float64", 42, **kw)
         assert err <= TOL["float64"], (expr, kw, err)
 
@@ -409,7 +414,7 @@ def test_persistent_tensor_box_epilogue(pkg, orc, torch_cuda, expr):
     """Output batches as tiled TMA reduce/store boxes agree with the checker and, bit for bit, with the per-row
     bulk copies they replace (both add the same products to the same words)."""
     torch = torch_cuda
-    for tile in ((128, 64), (64, 96)):
+    for tile in ((128, 64), (64, 96), (128, 32)):
         outs = []
         for tma in (0, 2):
             c0, a, b = orc.make_inputs(expr, 77, "float64")

@@ -57,7 +57,10 @@ def test_tile_choices(pkg):
     # output-bound fp64 (K = 40): the kernel that keeps the output tile resident in shared memory
     assert d[4]["kernel"] == "dmma_wc_128x64" and d[4]["tiles"] == [500, 1000] and d[4]["tma_ct"] and d[4]["mblock_w"] == 32
     longer = _plan(pkg, CONFIGS[4][0].replace("g,40", "g,96")).describe()
-    assert longer["kernel"] == "dmma_ws_128x64" and longer["tiles"] == [500, 1000]   # pipe-bound again
+    assert longer["kernel"].startswith("dmma_w") and longer["estimate_us"] > 2 * d[4]["estimate_us"]   # pipe-bound: time follows K
+    # a skinny right operand (one external index of 24): the 32-wide tile wastes a quarter of its columns, not five eighths
+    skinny = _plan(pkg, "t3 [a,312,b,24,c,296] += sum(d,312) * t2 [d,c,a] * v2 [b,d];").describe()
+    assert skinny["kernel"] == "dmma_ws_128x32" and skinny["tiles"] == [722, 1] and skinny["estimate_us"] > 0
     # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
     # (default: the tcgen05 form of the three-TF32 product; the mma.sync form on request or for small problems)
     assert d[3]["math"] == "tf32x3_tcgen05" and d[3]["kernel"] == "tf32tc_96x128"
