@@ -60,11 +60,14 @@ extern "C" int cogent_last_error(void) { return (int)cudaGetLastError(); }
 '''
 
 
-def build(reference=REF_DEFAULT):
+def build(reference=REF_DEFAULT, force=True):
     gen = os.path.join(reference, "cogent")
     if not os.path.isdir(gen):
         return []
     os.makedirs(OUT, exist_ok=True)
+    libs = [os.path.join(OUT, "libcogent_%s.so" % name) for name in sorted(CONFIGS)]
+    if not force and os.path.exists(os.path.join(OUT, "cogent_kernels.json")) and all(os.path.exists(x) for x in libs):
+        return libs
     built, table = [], {}
     with tempfile.TemporaryDirectory(prefix="cogent_gen_") as scratch:
         work = os.path.join(scratch, "cogent")
