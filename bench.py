@@ -56,6 +56,7 @@ WORKLOADS = {
     "cfg5_shard8": ("C [a,40,b,40,c,40,d,40,e,40,f,5] += sum(g,40) * A [g,a,b,c] * B [d,e,f,g];", "f64", 4),
     # small cases that run the kernels the five configurations do not reach (one CTA per tile, K slices + combine)
     "kslices_f64": ("C [a,320,b,288] += sum(c,256,d,320) * A [a,c,d] * B [d,b,c];", "f64", 6),
+    "gemm_f32": ("C [a,4096,b,4096] += sum(c,2048) * A [c,a] * B [c,b];", "f32", 8),
     "small_f32": ("C [a,48,b,40,c,36] += sum(d,64) * A [d,c,a] * B [b,d];", "f32", 7),
 }
 # contraction-split case for N > 1: small output, one long contraction index cut across the ranks
@@ -292,10 +293,10 @@ def cogent_kernel_gflops(name, orc, flops, reps=3):
                            "-arch=sm_100; kernel-only time (CUDA events), best of %d" % reps}
 
 
-def quick_config(pkg, orc, torch, name, steps=5, path="auto", cogent=False):
+def quick_config(pkg, orc, torch, name, steps=5, path="auto", cogent=False, label=None, **plan_kw):
     expr, dtype, seed = WORKLOADS[name]
     dc, da, db = device_tensors(pkg, torch, expr, dtype, seed, orc.sizes(expr))
-    plan = pkg.Plan(expr, pkg.F64 if dtype == "f64" else pkg.F32, path=path_code(pkg, path)).commit()
+    plan = pkg.Plan(expr, pkg.F64 if dtype == "f64" else pkg.F32, path=path_code(pkg, path), **plan_kw).commit()
     stream = torch.cuda.current_stream().cuda_stream
     sec = time_passes(torch, lambda: plan.execute(dc, da, db, stream=stream), steps, 3)
     status = plan.status()
@@ -304,7 +305,7 @@ def quick_config(pkg, orc, torch, name, steps=5, path="auto", cogent=False):
     plan.close()
     del dc, da, db
     torch.cuda.empty_cache()
-    row = {"workload": name, "dtype": dtype, "path": path, "gflops": flops * steps / sec * 1e-9, "ms": sec / steps * 1e3,
+    row = {"workload": name, "dtype": dtype, "path": label or path, "gflops": flops * steps / sec * 1e-9, "ms": sec / steps * 1e3,
            "algorithmic_gbs": nbytes * steps / sec * 1e-9, "kernel": d["kernel"], "device_status": status}
     if cogent:
         extra = cogent_kernel_gflops(name, orc, flops)
@@ -751,6 +752,7 @@ def run_ours(args):
             rows = [quick_config(pkg, orc, torch, n, cogent=True) for n in ("cfg1", "cfg2", "cfg3")]
             # configuration 4 compares its arithmetic paths
             rows.append(quick_config(pkg, orc, torch, "cfg4", path="tcgen05", cogent=True))
+            rows.append(quick_config(pkg, orc, torch, "cfg4", path="tcgen05", label="tcgen05, one CTA per tile", tile=(96, 128), variant=1))
             rows.append(quick_config(pkg, orc, torch, "cfg4", path="3xtf32"))
             rows.append(quick_config(pkg, orc, torch, "cfg4", path="ffma"))
             line["configs"] = rows

@@ -46,7 +46,17 @@ def _generate_kernel_units():
             with open(path, "w") as f:
                 f.write(body)
         units.append(path)
-    wc = text[text.index("#define TC_WC_KERNEL_LIST"):]
+    wt = text[text.index("#define TC_WT_KERNEL_LIST"):]
+    for m in re.finditer(r"^\s*X\((\w+),\s*(\d+),\s*(\d+)\)", wt, re.M):
+        name, bm, _variant = m.groups()
+        body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'
+                "TC_DEFINE_WT_INST(tc_inst_%s, %s)\n" % (name, bm))
+        path = os.path.join(OBJ, "gen_%s.cu" % name)
+        if not os.path.exists(path) or open(path).read() != body:
+            with open(path, "w") as f:
+                f.write(body)
+        units.append(path)
+    wc = text[text.index("#define TC_WC_KERNEL_LIST"):text.index("#define TC_WT_KERNEL_LIST")]
     for m in re.finditer(r"^\s*X\((\w+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+),\s*(\d+)\)", wc, re.M):
         name, bm, groups, wgm, wgn, st, _variant = m.groups()
         body = ('// generated from tc_kernel_list.h by build.py\n#include "../tc_inst.cuh"\n'

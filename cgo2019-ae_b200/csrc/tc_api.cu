@@ -71,6 +71,10 @@ TC_WS_KERNEL_LIST(TC_DECLARE_WS)
   extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
 TC_WC_KERNEL_LIST(TC_DECLARE_WC)
 #undef TC_DECLARE_WC
+#define TC_DECLARE_WT(NAME, BM, VARIANT) \
+  extern "C" int tc_inst_##NAME(int, int, const TcKernelArgs*, void*, const void*, const void*, cudaStream_t, int, int*, int*);
+TC_WT_KERNEL_LIST(TC_DECLARE_WT)
+#undef TC_DECLARE_WT
 
 namespace {
 struct KernelEntry {
@@ -82,7 +86,10 @@ template <typename T> constexpr int dtype_of() { return sizeof(T) == 8 ? TC_F64 
 #define TC_ENTRY(NAME, T, MATH, BM, BN, WMN, WNN, STAGES, MINB, VARIANT) {#NAME, dtype_of<T>(), MATH, BM, BN, VARIANT, tc_inst_##NAME},
 #define TC_WS_ENTRY(NAME, BM, BN, STAGES, VARIANT) {#NAME, TC_F64, TC_MATH_DMMA, BM, BN, VARIANT, tc_inst_##NAME},
 #define TC_WC_ENTRY(NAME, BM, GROUPS, WGM, WGN, STAGES, VARIANT) {#NAME, TC_F64, TC_MATH_DMMA, BM, 64, VARIANT, tc_inst_##NAME},
-const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY) TC_WS_KERNEL_LIST(TC_WS_ENTRY) TC_WC_KERNEL_LIST(TC_WC_ENTRY)};
+#define TC_WT_ENTRY(NAME, BM, VARIANT) {#NAME, TC_F32, TC_MATH_TF32TC, BM, 128, VARIANT, tc_inst_##NAME},
+const KernelEntry kKernels[] = {TC_KERNEL_LIST(TC_ENTRY) TC_WS_KERNEL_LIST(TC_WS_ENTRY) TC_WC_KERNEL_LIST(TC_WC_ENTRY)
+                                TC_WT_KERNEL_LIST(TC_WT_ENTRY)};
+#undef TC_WT_ENTRY
 #undef TC_ENTRY
 #undef TC_WS_ENTRY
 #undef TC_WC_ENTRY
@@ -185,6 +192,11 @@ int tc_kernels_prepare(const TcKernelChoice& c) {
     alt.variant = 2;
     st = kernels_prepare_one(alt);
   }
+  if (st == TC_OK && tc_kernel_is_tmem_persistent(c)) {  // its stand-in for outputs without 16-byte alignment
+    TcKernelChoice alt = c;
+    alt.variant = 0;
+    st = kernels_prepare_one(alt);
+  }
   return st;
 }
 static int kernels_prepare_one(const TcKernelChoice& c) {
@@ -233,6 +245,7 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
       a.c_tensor = 2;
   }
   tc_inst_fn fn = pick_inst(c);
+  int passes = p.passes;
   if (tc_kernel_is_c_resident(c)) {
     // The C-resident kernel moves whole output tiles as boxes of the rank-5 view of C: the view must exist and the
     // base must be 16-byte aligned.  Otherwise the same tiles run on the persistent kernel that reaches C through
@@ -245,12 +258,41 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
       fn = pick_inst(alt);
     }
   }
+  if (tc_kernel_is_tmem_persistent(c) && ((cu & 15) != 0 || p.opt.c_path != 0)) {
+    // The persistent tcgen05 kernel moves its output tiles as bulk copies of 16-byte aligned chunks; an output
+    // without that alignment (or a forced output path) runs the same tiles one CTA per tile.
+    TcKernelChoice alt = c;
+    alt.variant = 0;
+    fn = pick_inst(alt);
+    // ... as sequential passes where the persistent kernel would have cut the accumulation chain itself
+    const int64_t steps = (a.Kflat + TC_BK - 1) / TC_BK, want = (steps + 31) / 32;
+    if (want > 1) {
+      passes = (int)want;
+      a.k_chunk = (uint32_t)(((steps + want - 1) / want) * TC_BK);
+    }
+  } else if (tc_kernel_is_tmem_persistent(c)) {
+    // How the kernel's shared memory is carved.  Short contractions are bound by the output stream: tile buffers,
+    // so that enough of C is in flight.  Long ones are bound by the MMAs: one tile buffer, a second image set and
+    // every operand stage that fits.
+    const int64_t steps = (a.Kflat + TC_BK - 1) / TC_BK;
+    a.out_bufs = steps >= 16 ? 1 : (a.bm <= 96 ? 3 : 2);
+    a.img_sets = steps >= 16 ? 2 : 1;
+    if (const char* e = getenv("TC_WT_BUFS")) a.out_bufs = atoi(e);
+    if (const char* e = getenv("TC_WT_IMGS")) a.img_sets = atoi(e);
+    int stages = 0;
+    const int st = fn(vx, vy, &a, nullptr, nullptr, nullptr, nullptr, TC_INST_CARVE, &stages, nullptr);
+    if (st != TC_OK) return st;
+    if (const char* e = getenv("TC_WT_STAGES")) stages = std::min(stages, std::max(2, atoi(e)));
+    a.ring_stages = stages;
+    if (const char* e = getenv("TC_WT_DEBUG_PTR")) a.ws = reinterpret_cast<void*>(strtoull(e, nullptr, 0));
+    if (const char* e = getenv("TC_WT_DEBUG_FAULT")) a.test_fault = atoi(e);
+  }
   if (!fn) return TC_ERR_UNSUPPORTED;
   // Plans whose contraction runs as sequential passes (fp32 tensor-core chains kept short on outputs too large
   // for slice scratch): one launch per range of k, the first with the expression's operator, the rest adding.
-  for (int pass = 0; pass < p.passes; ++pass) {
+  for (int pass = 0; pass < passes; ++pass) {
     TcKernelArgs b = a;
-    if (p.passes > 1) {
+    if (passes > 1) {
       b.k_first = (uint32_t)pass * a.k_chunk;
       b.Kflat = std::min<uint32_t>(a.Kflat, b.k_first + a.k_chunk);
       if (pass > 0) b.beta = 1;

@@ -7,8 +7,11 @@
 #include "tc_kernels.cuh"
 #include "tc_ws_kernel.cuh"
 #include "tc_wc_kernel.cuh"
+#include "tc_wt_kernel.cuh"
 
-enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3 };
+// TC_INST_CARVE (persistent tcgen05 kernel): *threads = operand stages that fit beside args->out_bufs output tile
+// buffers and args->img_sets image sets.
+enum TcInstMode { TC_INST_LAUNCH = 0, TC_INST_PREPARE = 1, TC_INST_QUERY = 2, TC_INST_OCCUPANCY = 3, TC_INST_CARVE = 4 };
 
 // mode_x / mode_y: 0 element loads, 1 16-byte loads along the external index, 2 16-byte loads along the
 // contraction index, 3 one tiled TMA copy per stage (kernels without these images treat 2 and 3 as 0).
@@ -84,7 +87,30 @@ int run_wc_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
                    int* threads, int* smem_bytes) {
   return run_persistent<CF>(tc_wc_dmma_kernel<CF>, a, C, X, Y, stream, mode, threads, smem_bytes);
 }
+template <class CF>
+int run_wt_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y, cudaStream_t stream, int mode,
+                   int* threads, int* smem_bytes) {
+  if (mode == TC_INST_CARVE) {
+    if (!a || !threads || a->out_bufs < 1 || a->out_bufs > CF::MAX_CBUFS || a->img_sets < 1 || a->img_sets > CF::MAX_IMGS) return TC_ERR_INVALID_ARG;
+    *threads = CF::stages_for(a->out_bufs, a->img_sets);
+    return *threads >= 2 ? TC_OK : TC_ERR_UNSUPPORTED;
+  }
+  return run_persistent<CF>(tc_wt_tf32_kernel<CF>, a, C, X, Y, stream, mode, threads, smem_bytes);
+}
 }  // namespace tck
+
+// Persistent fp32 kernel: loader modes 0 element, 1 external vector, 2 contraction vector per operand.
+#define TC_WT_CASE(MX, MY, BM) \
+  if (vx == MX && vy == MY) return tck::run_wt_variant<tck::WtCfg<BM, MX, MY>>(a, C, X, Y, s, mode, threads, smem);
+#define TC_DEFINE_WT_INST(NAME, BM)                                                                          \
+  extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,         \
+                      cudaStream_t s, int mode, int* threads, int* smem) {                                  \
+    if (vx > 2) vx = 0;                                                                                     \
+    if (vy > 2) vy = 0;                                                                                     \
+    TC_WT_CASE(0, 0, BM) TC_WT_CASE(0, 1, BM) TC_WT_CASE(0, 2, BM) TC_WT_CASE(1, 0, BM) TC_WT_CASE(1, 1, BM) \
+    TC_WT_CASE(1, 2, BM) TC_WT_CASE(2, 0, BM) TC_WT_CASE(2, 1, BM) TC_WT_CASE(2, 2, BM)                     \
+    return TC_ERR_INVALID_ARG;                                                                              \
+  }
 
 #define TC_WC_CASE(MX, MY, BM, GROUPS, WGM, WGN, STAGES) \
   if (vx == MX && vy == MY) return tck::run_wc_variant<tck::WcCfg<BM, GROUPS, WGM, WGN, STAGES, MX, MY>>(a, C, X, Y, s, mode, threads, smem);

@@ -92,6 +92,7 @@ struct TcKernelArgs {
   uint32_t k_first;  // first flattened contraction index of this launch (plans that run K in sequential passes)
   uint32_t spin_limit;  // polls a bounded wait may take before it gives up
   int32_t test_fault;   // tests only: 1 = the persistent kernel's producers leave one stage unannounced
+  int32_t out_bufs, img_sets, ring_stages;  // persistent tcgen05 kernel: how its shared memory is carved (set at launch)
   const int64_t* koff_x;  // [Kflat] offset of flattened contraction index k inside X
   const int64_t* koff_y;  // [Kflat] the same inside Y
   int32_t lanes_k_x;  // element-wise loader: consecutive lanes that walk k (1 = lanes walk the external index)
@@ -179,8 +180,10 @@ int tc_kernels_prepare(const TcKernelChoice& c);  // opt-in shared memory attrib
 // Compiled kernels (registry built from tc_kernel_list.h).
 bool tc_kernel_exists(int dtype, int math, int bm, int bn, int variant);
 const char* tc_kernel_name(const TcKernelChoice& c);
+// fp32 on tcgen05 with the output tile resident in shared memory (tc_wt_kernel.cuh)
+inline bool tc_kernel_is_tmem_persistent(const TcKernelChoice& c) { return c.math == TC_MATH_TF32TC && c.variant == 1; }
 inline bool tc_kernel_is_persistent(const TcKernelChoice& c) {
-  return c.math == TC_MATH_DMMA && c.variant >= 2;
+  return (c.math == TC_MATH_DMMA && c.variant >= 2) || tc_kernel_is_tmem_persistent(c);
 }
 // ... and keeps its output tile resident in shared memory (tc_wc_kernel.cuh)
 inline bool tc_kernel_is_c_resident(const TcKernelChoice& c) { return c.math == TC_MATH_DMMA && c.variant == 3; }

@@ -46,4 +46,11 @@
 #define TC_WC_KERNEL_LIST(X)            \
   X(dmma_wc_128x64, 128, 1, 4, 2, 3, 3)
 
+// Persistent fp32 kernels on tcgen05 (tc_wt_kernel.cuh): BM x 128 tiles, two accumulators in tensor memory, the
+// output tile resident in shared memory.
+//   X(name, BM, VARIANT)
+#define TC_WT_KERNEL_LIST(X)   \
+  X(tf32wt_96x128, 96, 1)      \
+  X(tf32wt_128x128, 128, 1)
+
 #endif  // TC_KERNEL_LIST_H_

@@ -129,6 +129,25 @@ void out_box_view(const TcKernelArgs& a, int es, int bm, int bn, TcOutMap* map, 
   *per_tile = ne.size() == 1 || ne[0] % bn == 0;
 }
 
+// The staged output layout of the fp32 kernels: a tile's rows split into runs of E0 elements that are contiguous in
+// the output (E0 a multiple of 4, tiles 16-byte aligned); `n_adjacent`: consecutive n are adjacent in the output
+// inside blocks of N's fastest extent, so a run and its n leave as one chunk.  Returns E0, or 0 where bulk copies do
+// not pay (chunks under 256 bytes) or are not possible.
+int64_t staged_run(const TcKernelArgs& a, int bm, int bn, int es, bool* n_adjacent) {
+  const int V = 16 / es;
+  *n_adjacent = false;
+  if (!(a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= V)) return 0;
+  const int64_t e = a.M.extent[0];
+  const int64_t e0 = e % bm == 0 ? bm : (bm % e == 0 ? e : std::gcd<int64_t>(bm, e));
+  if (e0 % V != 0 || e0 < V) return 0;
+  *n_adjacent = e0 == e && a.N.n > 0 && a.N.s_out[0] == e && (int64_t)a.N.extent[0] >= bn;
+  return (*n_adjacent || e0 * es >= 256) ? e0 : 0;
+}
+bool wt_eligible(const TcKernelArgs& a, int bm, int es) {
+  bool adj;
+  return es == 4 && staged_run(a, bm, 128, es, &adj) > 0;
+}
+
 }  // namespace
 
 int tc_plan_build(tc_plan* p, std::string* why) {
@@ -419,6 +438,12 @@ int tc_plan_build(tc_plan* p, std::string* why) {
         bn = 128;
       }
     }
+    if (c.math == TC_MATH_TF32TC && p->opt.split_k == 0 && p->opt.c_path == 0) {
+      // ... as the persistent kernel (two accumulators in tensor memory, output tile resident in shared memory)
+      // wherever its tile buffers can hold the output in runs that leave as bulk copies.
+      const int tbm = (bm == 96 || bm == 128) ? bm : 128;
+      if (wt_eligible(a, tbm, es) && tc_kernel_exists(TC_F32, TC_MATH_TF32TC, tbm, 128, 1)) { bm = tbm; bn = 128; variant = 1; }
+    }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
     if (ctas < 2 * sms) {
       bm = 64; bn = 64; variant = 0;
@@ -429,6 +454,10 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   c.bm = bm;
   c.bn = bn;
   c.variant = variant;
+  if (tc_kernel_is_tmem_persistent(c) && !wt_eligible(a, bm, es)) {
+    *why = "the persistent tcgen05 kernel needs an output whose tile rows are 16-byte aligned contiguous runs";
+    return TC_ERR_UNSUPPORTED;
+  }
   if (!tc_kernel_exists(c.dtype, c.math, bm, bn, c.variant)) { *why = "requested CTA tile / variant is not compiled in"; return TC_ERR_UNSUPPORTED; }
   a.bm = bm;
   a.bn = bn;
@@ -460,7 +489,9 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   //     the others with `+=`; the additions into C are round-to-nearest).  A pass re-reads and re-writes C,
   //     which at 512 products per element is noise beside the arithmetic.
   p->passes = 1;
-  if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0) {
+  // (the persistent tcgen05 kernel cuts its chains itself: segments of at most 32 K steps that alternate between
+  // two accumulators and are added into the output tile in shared memory)
+  if ((c.math == TC_MATH_TF32X3 || c.math == TC_MATH_TF32TC) && p->opt.split_k == 0 && !persistent) {
     const int64_t per_slice = tiles * bm * bn * (int64_t)es;
     const int64_t want = std::min<int64_t>((kf + TC_TF32_CHAIN - 1) / TC_TF32_CHAIN, ksteps);
     if (want > 1 && want * per_slice > (int64_t(1) << 30) && ksplit == 1) p->passes = (int)std::min<int64_t>(want, 1 << 20);
@@ -487,16 +518,13 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // the extent of the fastest one), consecutive n are adjacent too within blocks of that index's extent.
   a.epi_run = 0;
   a.epi_n_span = 0;
-  if (c.math != TC_MATH_DMMA && ksplit == 1 && a.M.n > 0 && a.M.s_out[0] == 1 && a.vec_c >= V) {
-    const int64_t e = a.M.extent[0];
-    int64_t e0 = e % bm == 0 ? bm : (bm % e == 0 ? e : std::gcd<int64_t>(bm, e));
-    if (e0 % V == 0 && e0 >= V) {
-      const bool n_adjacent = e0 == e && a.N.n > 0 && a.N.s_out[0] == e && (int64_t)a.N.extent[0] >= bn;
-      // bulk copies pay off from a few hundred bytes per chunk; shorter runs keep the read-modify-write
-      if (n_adjacent || e0 * es >= 256) {
-        a.epi_run = (int32_t)e0;
-        if (n_adjacent) a.epi_n_span = (int32_t)a.N.extent[0];
-      }
+  if (c.math != TC_MATH_DMMA && ksplit == 1) {
+    // bulk copies pay off from a few hundred bytes per chunk; shorter runs keep the read-modify-write
+    bool n_adjacent = false;
+    const int64_t e0 = staged_run(a, bm, bn, es, &n_adjacent);
+    if (e0 > 0) {
+      a.epi_run = (int32_t)e0;
+      if (n_adjacent) a.epi_n_span = (int32_t)a.N.extent[0];
     }
   }
 
@@ -525,6 +553,12 @@ std::string tc_plan_to_json(const tc_plan& p) {
   };
   o << "{\"expr\":" << tc_expr_to_json(p.expr) << ",\"dtype\":\"" << (p.dtype == TC_F64 ? "f64" : "f32")
     << "\",\"committed\":" << (p.committed ? "true" : "false");
+  // longest tensor-core accumulation chain of the plan
+  uint32_t chain = std::min<uint32_t>(a.k_chunk, a.Kflat);
+  if (tc_kernel_is_tmem_persistent(p.choice)) {
+    const uint32_t steps = (a.Kflat + TC_BK - 1) / TC_BK, segs = (steps + 31) / 32;
+    chain = std::min<uint32_t>(a.Kflat, ((steps + segs - 1) / segs) * TC_BK);
+  }
   if (p.committed) {
     o << ",\"swapped\":" << (p.swapped ? "true" : "false") << ",\"M\":";
     dims(a.M);
@@ -536,7 +570,7 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"math\":\"" << (p.choice.math == TC_MATH_DMMA ? "dmma" : p.choice.math == TC_MATH_TF32X3 ? "tf32x3" : p.choice.math == TC_MATH_TF32TC ? "tf32x3_tcgen05" : (p.dtype == TC_F64 ? "dfma" : "ffma"))
       << "\",\"kernel\":\"" << tc_kernel_name(p.choice) << "\",\"tile\":[" << p.choice.bm << "," << p.choice.bn << "," << TC_BK
       << "],\"variant\":" << p.choice.variant << ",\"tiles\":[" << a.tiles_m << "," << a.tiles_n << "],\"estimate_us\":" << p.estimate_s * 1e6 << ",\"mblock_w\":" << a.mblock_w << ",\"ksplit\":" << a.ksplit
-      << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << std::min<uint32_t>(a.k_chunk, a.Kflat) << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
+      << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << chain << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
       << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false") << ",\"tma_ct\":" << (p.choice.tma_ct ? "true" : "false")

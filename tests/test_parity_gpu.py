@@ -490,6 +490,80 @@ def test_tcgen05_three_tf32_products(pkg, orc, torch_cuda, expr, tile):
     assert err <= TOL["float32"], (expr, "c_path 1", err, d)
 
 
+WT = [
+    ("C [a,96,b,128] = sum(c,8) * A [a,c] * B [b,c];", (96, 128)),                    # one tile, half a K step
+    ("C [a,128,b,256] += sum(c,16) * A [a,c] * B [b,c];", (128, 128)),                # two tiles, one K step
+    ("C [a,256,b,384] -= sum(c,40) * A [c,a] * B [c,b];", (128, 128)),                # contraction-major operands
+    ("C [a,512,b,640] += sum(c,300) * A [a,c] * B [c,b];", (128, 128)),               # more tiles than buffers; E0 = 128
+    ("C [a,512,b,640] = sum(c,300) * A [c,a] * B [b,c];", (128, 128)),                # `=`: nothing fetched
+    ("C [a,200,b,300] -= sum(c,37) * A [c,a] * B [b,c];", (128, 128)),                # ragged tiles: E0 = 8, per-n chunks refused
+    ("C [a,192,b,300] += sum(c,37) * A [c,a] * B [b,c];", (96, 128)),                 # ragged in n only; E0 = 96
+    ("C [a,320,b,300] += sum(c,37) * A [c,a] * B [b,c];", (128, 128)),                # E0 = 64: two runs, last tile half empty
+    ("C [a,24,b,24,c,24,i,8,j,8,k,8] += sum(l,24) * A [l,a,i,j] * B [b,c,k,l];", (96, 128)),   # configuration 4's shape: dense runs
+    ("C [a,24,b,24,c,24,i,8,j,8,k,8] -= sum(l,24) * A [l,a,i,j] * B [b,c,k,l];", None),
+    ("C [a,48,b,40,c,16,d,6] += sum(e,20,f,3) * A [a,f,d,e] * B [e,b,c,f];", (96, 128)),      # element gathers of X
+    ("C [a,256,b,8,c,48] += sum(d,1000,e,3) * A [a,e,d] * B [d,b,c,e];", (128, 128)),          # 188 K steps: six segments
+    ("C [a,384,b,256] = sum(c,2100) * A [c,a] * B [c,b];", (128, 128)),                        # segments with `=`
+    ("C [a,2048,b,2048] += sum(c,512) * A [c,a] * B [c,b];", (128, 128)),     # long K, several tiles per CTA: one tile buffer
+    ("C [a,1536,b,2048] -= sum(c,72) * A [a,c] * B [b,c];", (96, 128)),       # short K, several tiles per CTA: three buffers
+]
+
+
+@pytest.mark.parametrize("expr,tile", WT)
+def test_persistent_tcgen05_kernel(pkg, orc, torch_cuda, expr, tile):
+    """The persistent fp32 kernel (two accumulators in tensor memory, output tile resident in shared memory, chains cut
+    into segments inside the kernel) against the loop nest; where its output layout is not possible the plan is refused."""
+    kw = {"path": pkg.PATH_TCGEN05}
+    if tile:
+        kw.update(tile=tile, variant=2)
+    if "a,200" in expr:
+        with pytest.raises(pkg.TcError):
+            pkg.Plan(expr, pkg.F32, **kw).commit()
+        return
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 24, **kw)
+    assert d["kernel"].startswith("tf32wt_") and d["chain"] <= 512 and d["ksplit"] == 1 and d["passes"] == 1, d
+    assert err <= TOL["float32"], (expr, err, d)
+
+
+def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):
+    """The same failure drill as for the fp64 kernels: one loader thread leaves one stage unannounced; every role's
+    waits run out, tensor memory is freed, the status names a wait of this kernel, and the next plan runs correctly."""
+    torch = torch_cuda
+    expr = "C [a,512,b,640] += sum(c,300) * A [a,c] * B [c,b];"
+    c0, a, b = orc.make_inputs(expr, 26, "float32")
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    kw = dict(path=pkg.PATH_TCGEN05, tile=(128, 128), variant=2)
+    bad = pkg.Plan(expr, pkg.F32, test_fault=1, **kw)
+    dc, da, db = (torch.from_numpy(x).cuda() for x in (c0, a, b))
+    bad.execute(dc, da, db)
+    torch.cuda.synchronize()
+    assert bad.status() in range(10, 18)
+    bad.close()
+    for _ in range(2):   # tensor memory was released: the kernel can be resident again, twice
+        good = pkg.Plan(expr, pkg.F32, **kw)
+        dc = torch.from_numpy(c0).cuda()
+        good.execute(dc, da, db)
+        torch.cuda.synchronize()
+        assert good.status() == 0 and orc.rel_error(dc.cpu().numpy(), ref) <= TOL["float32"]
+        good.close()
+
+
+def test_persistent_tcgen05_kernel_on_an_unaligned_output(pkg, orc, torch_cuda):
+    """An output without 16-byte alignment cannot leave as bulk copies: the same plan runs one CTA per tile, as
+    sequential passes where the persistent kernel would have cut the chain itself."""
+    torch = torch_cuda
+    expr = "C [a,256,b,384] += sum(c,1100) * A [c,a] * B [c,b];"
+    c0, a, b = orc.make_inputs(expr, 25, "float32")
+    ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+    plan = pkg.Plan(expr, pkg.F32, path=pkg.PATH_TCGEN05, tile=(128, 128), variant=2)
+    pad = torch.zeros(c0.size + 1, dtype=torch.float32, device="cuda")
+    pad[1:] = torch.from_numpy(c0).cuda()
+    plan.execute(pad[1:], torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda())
+    torch.cuda.synchronize()
+    assert plan.status() == 0 and orc.rel_error(pad[1:].cpu().numpy(), ref) <= TOL["float32"]
+    plan.close()
+
+
 @pytest.mark.parametrize("path", ["tcgen05", "mma.sync", "auto"])
 def test_fp32_long_contractions_stay_within_tolerance(pkg, orc, torch_cuda, path):
     """Tensor-core fp32 accumulation truncates, so one chain of 8192 products would be off by 7e-5; the planner

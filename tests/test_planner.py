@@ -62,8 +62,11 @@ def test_tile_choices(pkg):
     skinny = _plan(pkg, "t3 [a,312,b,24,c,296] += sum(d,312) * t2 [d,c,a] * v2 [b,d];").describe()
     assert skinny["kernel"] == "dmma_ws_128x32" and skinny["tiles"] == [722, 1] and skinny["estimate_us"] > 0
     # fp32: 96 rows = 4 whole runs of the 24-long fastest output index; (a, bc) blocks leave as bulk chunks
-    # (default: the tcgen05 form of the three-TF32 product; the mma.sync form on request or for small problems)
-    assert d[3]["math"] == "tf32x3_tcgen05" and d[3]["kernel"] == "tf32tc_96x128"
+    # (default: the tcgen05 form of the three-TF32 product as the persistent kernel; one CTA per tile or the mma.sync
+    # form on request or for small problems)
+    assert d[3]["math"] == "tf32x3_tcgen05" and d[3]["kernel"] == "tf32wt_96x128" and d[3]["ksplit"] == 1
+    per_tile = _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_TCGEN05, tile=(96, 128), variant=1).describe()
+    assert per_tile["kernel"] == "tf32tc_96x128"
     sync = _plan(pkg, CONFIGS[3][0], "float32", path=pkg.PATH_3XTF32).describe()
     assert sync["math"] == "tf32x3" and sync["kernel"] == "tf32_96x128"
     # a 96-wide N leaves a quarter of a 128-wide tcgen05 tile empty and every tile ragged: mma.sync form
