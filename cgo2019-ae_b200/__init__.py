@@ -44,6 +44,16 @@ _lib = None
 
 # name -> (restype, argtypes); every symbol include/tc_b200.h declares.
 _SIGNATURES = {
+    "tc_plan_create_sharded": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int),
+                                              ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "tc_sharded_set_extents": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_char_p),
+                                              ctypes.POINTER(ctypes.c_int64)]),
+    "tc_sharded_describe": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]),
+    "tc_sharded_commit": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_execute_sharded": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                          ctypes.POINTER(ctypes.c_void_p), ctypes.c_int]),
+    "tc_sharded_synchronize": (ctypes.c_int, [ctypes.c_void_p]),
+    "tc_sharded_destroy": (None, [ctypes.c_void_p]),
     "tc_expr_describe": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_size_t]),
     "tc_plan_create": (ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(Options),
                                       ctypes.POINTER(ctypes.c_void_p)]),
@@ -247,6 +257,59 @@ class Plan:
     def close(self):
         if self._h:
             lib().tc_plan_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+SHARD_EXTERNAL, SHARD_CONTRACTION, SHARD_C_IS_SLAB = 0, 1, 1
+
+
+class ShardedPlan:
+    """One contraction over several GPUs driven by this process (tc_plan_create_sharded): `kind` SHARD_EXTERNAL cuts
+    an output index (no communication), SHARD_CONTRACTION a contraction index (NCCL reduce-scatter)."""
+
+    def __init__(self, expr, dtype=F64, devices=(0,), kind=SHARD_EXTERNAL, index=None, extents=None):
+        self._h = ctypes.c_void_p()
+        self.devices = list(devices)
+        ids = (ctypes.c_int * len(self.devices))(*self.devices)
+        _check(lib().tc_plan_create_sharded(expr.encode(), dtype, len(self.devices), ids, kind,
+                                            index.encode() if index else None, ctypes.byref(self._h)), "tc_plan_create_sharded")
+        if extents:
+            names = list(extents)
+            an = (ctypes.c_char_p * len(names))(*[n.encode() for n in names])
+            ae = (ctypes.c_int64 * len(names))(*[int(extents[n]) for n in names])
+            _check(lib().tc_sharded_set_extents(self._h, len(names), an, ae), "tc_sharded_set_extents")
+
+    def describe(self):
+        buf = ctypes.create_string_buffer(1 << 16)
+        st = lib().tc_sharded_describe(self._h, buf, len(buf))
+        if st != 0:
+            raise TcError(st, "tc_sharded_describe", json.loads(buf.value.decode() or "{}").get("error", ""))
+        return json.loads(buf.value.decode())
+
+    def commit(self):
+        _check(lib().tc_sharded_commit(self._h), "tc_sharded_commit")
+        return self
+
+    def execute(self, Cs, As, Bs, c_is_slab=False):
+        """Cs[d], As[d], Bs[d]: the tensors in device d's memory (torch CUDA tensors or device addresses)."""
+        n = len(self.devices)
+        if not (len(Cs) == len(As) == len(Bs) == n):
+            raise ValueError("one output and two inputs per device")
+        arr = lambda xs: (ctypes.c_void_p * n)(*[_ptr(x) for x in xs])
+        _check(lib().tc_execute_sharded(self._h, arr(Cs), arr(As), arr(Bs), SHARD_C_IS_SLAB if c_is_slab else 0), "tc_execute_sharded")
+
+    def synchronize(self):
+        _check(lib().tc_sharded_synchronize(self._h), "tc_sharded_synchronize")
+
+    def close(self):
+        if self._h:
+            lib().tc_sharded_destroy(self._h)
             self._h = ctypes.c_void_p()
 
     def __del__(self):

@@ -189,6 +189,35 @@ int tc_fused_describe(tc_fused_plan* plan, char* buf, size_t cap);
 int tc_execute_fused(tc_fused_plan* plan, void* C, const void* const* A, const void* const* B, void* stream);
 void tc_fused_destroy(tc_fused_plan* plan);
 
+/* ---- one contraction over several GPUs from one process ----------------------------------
+ * One plan, one stream and (contraction kind) one NCCL communicator per device; the calling thread drives all
+ * devices.  The reference is single-GPU (nwchem-tccg/tccg_kernels.cu:228 is the only stream it creates), so
+ * nothing there is replaced; the geometry is the one cgo2019-ae_b200/shard.py uses with one process per GPU.
+ *   TC_SHARD_EXTERNAL     an output index (`index`, NULL = the largest, ties to the slowest) is cut into contiguous
+ *                         ranges, one per device: no communication.
+ *   TC_SHARD_CONTRACTION  a contraction index (NULL = the largest) is cut: every device writes a full-size partial
+ *                         result into scratch the plan owns, one reduce-scatter (NCCL, found at run time as
+ *                         libnccl.so.2; TC_ERR_UNSUPPORTED at commit if absent) sums them, and device d adds chunk d
+ *                         (ceil(|C| / n_devices) elements) into chunk d of its output.
+ * device_ids NULL means 0 .. n_devices - 1.  tc_sharded_describe works before commit and without a GPU (JSON:
+ * kind, index, per-device range, element offsets of the device's views, local expression, chunk).
+ * tc_execute_sharded: C[d], A[d], B[d] are pointers in device d's memory to the FULL tensors (compact, column-
+ * major); with TC_SHARD_C_IS_SLAB (external kind, cut along the output's slowest index) C[d] is only device d's
+ * contiguous slab.  The call is asynchronous on the plan's streams; tc_sharded_synchronize waits for all of them and
+ * returns TC_ERR_DEVICE_WAIT if a kernel reported a wait that gave up. */
+#define TC_SHARD_EXTERNAL 0
+#define TC_SHARD_CONTRACTION 1
+#define TC_SHARD_C_IS_SLAB 1
+typedef struct tc_sharded_plan tc_sharded_plan;
+int tc_plan_create_sharded(const char* expr, int dtype, int n_devices, const int* device_ids, int kind,
+                           const char* index, tc_sharded_plan** out);
+int tc_sharded_set_extents(tc_sharded_plan* plan, int n, const char* const* index_names, const int64_t* extents);
+int tc_sharded_describe(tc_sharded_plan* plan, char* buf, size_t cap);
+int tc_sharded_commit(tc_sharded_plan* plan);
+int tc_execute_sharded(tc_sharded_plan* plan, void* const* C, const void* const* A, const void* const* B, int flags);
+int tc_sharded_synchronize(tc_sharded_plan* plan);
+void tc_sharded_destroy(tc_sharded_plan* plan);
+
 /* ---- drop-in for the reference's generated entry ------------------------------------
  * What the generated sd_t_d2_fusion_ does for ONE expression (cogent/src/codes/kernels/tc_interface.py:
  * 1444-1598 -> 10-101): sizes in the order above, host pointers t3 (in/out), t2, v2; allocate, copy in,
