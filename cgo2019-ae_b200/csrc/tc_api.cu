@@ -277,15 +277,10 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
     const int64_t steps = (a.Kflat + TC_BK - 1) / TC_BK;
     a.out_bufs = steps >= 16 ? 1 : (a.bm <= 96 ? 3 : 2);
     a.img_sets = steps >= 16 ? 2 : 1;
-    if (const char* e = getenv("TC_WT_BUFS")) a.out_bufs = atoi(e);
-    if (const char* e = getenv("TC_WT_IMGS")) a.img_sets = atoi(e);
     int stages = 0;
     const int st = fn(vx, vy, &a, nullptr, nullptr, nullptr, nullptr, TC_INST_CARVE, &stages, nullptr);
     if (st != TC_OK) return st;
-    if (const char* e = getenv("TC_WT_STAGES")) stages = std::min(stages, std::max(2, atoi(e)));
     a.ring_stages = stages;
-    if (const char* e = getenv("TC_WT_DEBUG_PTR")) a.ws = reinterpret_cast<void*>(strtoull(e, nullptr, 0));
-    if (const char* e = getenv("TC_WT_DEBUG_FAULT")) a.test_fault = atoi(e);
   }
   if (!fn) return TC_ERR_UNSUPPORTED;
   // Plans whose contraction runs as sequential passes (fp32 tensor-core chains kept short on outputs too large

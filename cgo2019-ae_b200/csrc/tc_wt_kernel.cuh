@@ -174,35 +174,6 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
 
-// Bounded wait by a whole warp: its first lane polls (with a pause between polls where the wait is expected to be
-// long -- a warp that spins on try_wait competes with the copies and shared-memory accesses of the working warps for
-// the same pipe), the result reaches the other lanes through the warp shuffle, which also orders their later reads
-// behind the first lane's acquire.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code, uint32_t limit,
-                                               uint32_t pause_ns) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) {
-    ok = 0;
-    for (uint32_t i = 0; i < limit; ++i) {
-      if (mbar_try_wait(bar, parity)) { ok = 1; break; }
-      if (pause_ns) __nanosleep(pause_ns);
-    }
-    if (!ok) atomicCAS(status, 0, code);
-  }
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  return ok != 0;
-}
-
-#ifdef TC_WT_TIMING
-#define WT_T0() long long wt_t0 = clock64(), wt_w[4] = {0, 0, 0, 0}
-#define WT_WAIT(i, expr) [&]() { const long long t = clock64(); const bool ok = (expr); wt_w[i] += clock64() - t; return ok; }()
-#define WT_END(role) if (blockIdx.x == 0 && (tid & 31) == 0 && p.ws) { long long* o = reinterpret_cast<long long*>(p.ws) + (warp) * 8; o[0] = clock64() - wt_t0; o[1] = wt_w[0]; o[2] = wt_w[1]; o[3] = wt_w[2]; o[4] = wt_w[3]; o[5] = role; }
-#else
-#define WT_T0()
-#define WT_WAIT(i, expr) (expr)
-#define WT_END(role)
-#endif
-
 template <class CF>
 __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __grid_constant__ TcKernelArgs p,
                                                                          float* __restrict__ C,
@@ -270,16 +241,15 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     const float alpha = (float)p.alpha;
     uint32_t unit = 0, j = 0;
     bool alive = true;
-    WT_T0();
     for (uint32_t tile = first; alive && tile < total; tile += step, ++j) {
       const uint32_t b = j % CBUFS;
       float* ct = ctiles + b * CF::CTILE_ELEMS;
       for (int seg = 0; seg < nseg; ++seg, ++unit) {
         const uint32_t a = unit & 1u;
-        if (!WT_WAIT(0, mbar_wait(acc_full + a, (unit >> 1) & 1u, p.status, 10, limit))) { alive = false; break; }
+        if (!mbar_wait(acc_full + a, (unit >> 1) & 1u, p.status, 10, limit)) { alive = false; break; }
         tc05_fence_after();
         // the buffer holds the tile's old values (`+=`, `-=`) or is simply free (`=`)
-        if (seg == 0 && !WT_WAIT(1, mbar_wait(c_ready + b, (j / CBUFS) & 1u, p.status, 11, limit))) { alive = false; break; }
+        if (seg == 0 && !mbar_wait(c_ready + b, (j / CBUFS) & 1u, p.status, 11, limit)) { alive = false; break; }
         const bool overwrite = !accumulate && seg == 0;
         float v[CPW];
         const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + a * 128u + (uint32_t)cbase;
@@ -310,7 +280,6 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       __syncwarp();
       if (lane == 0) mbar_arrive(c_staged + b);
     }
-    WT_END(0);
     tc05_fence_before();
     group_bar_sync(1, 288);  // tensor memory may go
     return;
@@ -339,18 +308,14 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       reinterpret_cast<float4*>(lo_img)[d] = lo;
     };
     uint32_t g = 0, u = 0;  // stages and image units (eight k each) so far
-    WT_T0();
     for (uint32_t tile = first; tile < total; tile += step) {
       for (int it = 0; it < nk; ++it, ++g) {
         const uint32_t s = g % STAGES;
         const int nh = (kend - (kbeg + (uint32_t)it * BK)) > 8u ? 2 : 1;  // a last step of at most eight k is one unit
-        if (!WT_WAIT(0, mbar_wait(full + s, (g / STAGES) & 1u, p.status, 12, limit))) return;
+        if (!mbar_wait(full + s, (g / STAGES) & 1u, p.status, 12, limit)) return;
         const float* xs = stages + s * CF::STAGE_ELEMS;
         const float* ys = xs + CF::XIMG;
         float4 vy[2], vx[2];
-#ifdef TC_WT_TIMING
-        const long long tq0 = clock64();
-#endif
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           vy[h] = chunk(ys, ry, 2 * h + qy, CF::KVY, CF::LDY);
@@ -359,42 +324,25 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         // the stage is in registers: the loaders may refill it
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);
-#ifdef TC_WT_TIMING
-        wt_w[2] += clock64() - tq0;
-#endif
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (h >= nh) break;
           // unit u (eight k) goes to image slot sl = u % SLOTS: image set sl / 2, position sl % 2 among its two groups of 8 k
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
-          if (use > 0 && !WT_WAIT(1, mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit))) return;
+          if (use > 0 && !mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit)) return;
           float* ua_hi = images + (sl >> 1) * CF::UMMA_ELEMS;
           float* ua_lo = ua_hi + BK * BN;
           float* ub_hi = ua_lo + BK * BN;
           float* ub_lo = ub_hi + BK * BM;
-#ifdef TC_WT_TIMING
-          const long long tq1 = clock64();
-#endif
           put(ua_hi, ua_lo, ry, 2 * (int)(sl & 1u) + qy, vy[h]);
           if (has_x) put(ub_hi, ub_lo, rx, 2 * (int)(sl & 1u) + qx, vx[h]);
-#ifdef TC_WT_TIMING
-          const long long tq2 = clock64();
-#endif
-          if (p.test_fault < 4) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
-          if (lane == 0) {
-            if (p.test_fault == 4) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            mbar_arrive(img_full + sl);
-          }
-#ifdef TC_WT_TIMING
-          wt_w[3] += clock64() - tq2;
-          wt_w[2] += tq2 - tq1;
-#endif
+          if (lane == 0) mbar_arrive(img_full + sl);
         }
       }
     }
-    WT_END(1);
     return;
   }
 
@@ -423,22 +371,12 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     }
     uint32_t g = 0;
     bool alive = true;  // a loader whose wait gave up keeps meeting the others at the role's barrier, without work
-    WT_T0();
     for (uint32_t tile = first; tile < total; tile += step) {
       uint32_t tm, tn;
       tile_coords(p, tile, &tm, &tn);
-#ifdef TC_WT_TIMING
-      const long long tl0 = clock64();
-#endif
       slots_x.rows(p.M, tm * BM, p.Mflat);
       slots_y.rows(p.N, tn * BN, p.Nflat);
-#ifdef TC_WT_TIMING
-      wt_w[1] += clock64() - tl0;
-#endif
       for (int it = 0; it < nk; ++it, ++g) {
-#ifdef TC_WT_TIMING
-        const long long tl1 = clock64();
-#endif
         const int64_t* kr = kring + (keep_all ? it : (int)(g & 1u)) * 32;
         if (!keep_all) {
           if (ptid < 32) {
@@ -447,31 +385,19 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           }
           group_bar_sync(2, 128);  // the ring slot is written (its last readers passed the previous barrier)
         }
-#ifdef TC_WT_TIMING
-        wt_w[2] += clock64() - tl1;
-#endif
         if (!alive) continue;
         const uint32_t s = g % STAGES;
-        if (g >= (uint32_t)STAGES && !WT_WAIT(0, mbar_wait(empty + s, ((g / STAGES) - 1) & 1u, p.status, 14, limit))) { alive = false; continue; }
+        if (g >= (uint32_t)STAGES && !mbar_wait(empty + s, ((g / STAGES) - 1) & 1u, p.status, 14, limit)) { alive = false; continue; }
         const uint32_t k0 = kbeg + it * BK;
         float* xs = stages + s * CF::STAGE_ELEMS;
         float* ys = xs + CF::XIMG;
-#ifdef TC_WT_TIMING
-        const long long tl2 = clock64();
-#endif
-        if (p.test_fault != 8) {
         slots_x.issue(xs, X, kr, k0, kend);
         slots_y.issue(ys, Y, kr + 16, k0, kend);
-        }
         // tests only: one thread leaves one stage unannounced, so that the waits on it run out
         if (p.test_fault == 1 && blockIdx.x == 0 && g == 1 && ptid == 7) continue;
         mbar_arrive_on_copies(full + s);
-#ifdef TC_WT_TIMING
-        wt_w[3] += clock64() - tl2;
-#endif
       }
     }
-    WT_END(2);
     cp_async_wait<0>();
     return;
   }
@@ -483,11 +409,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       constexpr uint32_t IDESC = umma_idesc_tf32(BN, BM);
       uint32_t u = 0, unit = 0;  // image units and accumulator segments so far
       bool alive = true;
-      WT_T0();
-      for (uint32_t tile = first; alive && tile < total; tile += step) {
+        for (uint32_t tile = first; alive && tile < total; tile += step) {
         for (int seg = 0; alive && seg < nseg; ++seg, ++unit) {
           const uint32_t a = unit & 1u;
-          if (unit >= 2 && !WT_WAIT(0, mbar_wait(acc_free + a, ((unit >> 1) - 1) & 1u, p.status, 15, limit))) { alive = false; break; }
+          if (unit >= 2 && !mbar_wait(acc_free + a, ((unit >> 1) - 1) & 1u, p.status, 15, limit)) { alive = false; break; }
           tc05_fence_after();
           const uint32_t d_tmem = tmem + a * 128u;
           const int it_begin = seg_begin(seg), it_end = seg_begin(seg + 1);
@@ -498,35 +423,23 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
               if (h >= nh) break;
               const uint32_t sl = u % SLOTS, use = u / SLOTS;
               ++u;
-              if (!WT_WAIT(1, mbar_wait(img_full + sl, use & 1u, p.status, 16, limit))) { alive = false; break; }
+              if (!mbar_wait(img_full + sl, use & 1u, p.status, 16, limit)) { alive = false; break; }
               tc05_fence_after();
-              if (p.test_fault == 5) asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
               // two 4-k chunks per MMA: 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
               const uint32_t ya = smem_u32(images + (sl >> 1) * CF::UMMA_ELEMS) + (sl & 1u) * 256u, xa = ya + 2 * BK * BN * 4;
               const uint64_t ah = umma_desc_k(ya, 128, (BK / 4) * 128);
               const uint64_t al = umma_desc_k(ya + BK * BN * 4, 128, (BK / 4) * 128);
               const uint64_t bh = umma_desc_k(xa, 128, (BK / 4) * 128);
               const uint64_t bl = umma_desc_k(xa + BK * BM * 4, 128, (BK / 4) * 128);
-#ifdef TC_WT_TIMING
-              const long long tm0 = clock64();
-#endif
               tc05_mma_tf32(d_tmem, al, bh, IDESC, (it > it_begin || h > 0) ? 1u : 0u);
               tc05_mma_tf32(d_tmem, ah, bl, IDESC, 1u);
               tc05_mma_tf32(d_tmem, ah, bh, IDESC, 1u);
-#ifdef TC_WT_TIMING
-              const long long tm1 = clock64();
-#endif
               tc05_commit(img_free + sl);
-#ifdef TC_WT_TIMING
-              wt_w[2] += tm1 - tm0;
-              wt_w[3] += clock64() - tm1;
-#endif
             }
           }
           if (alive) tc05_commit(acc_full + a);
         }
       }
-      WT_END(3);
     }
     __syncwarp();
     tc05_fence_before();
@@ -581,14 +494,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   if (warp == 23) return;
   if (warp == 21) {
     // ---------------------------------------------------------------- fetch ----
-    WT_T0();
     for (uint32_t j = 0; j < ntiles; ++j) {
       const uint32_t b = j % CBUFS;
-      if (j >= (uint32_t)CBUFS && !WT_WAIT(0, mbar_wait(c_free + b, ((j / CBUFS) - 1) & 1u, p.status, 17, limit))) break;
-#ifdef TC_WT_TIMING
-      const long long tf0 = clock64();
-#endif
-      if (accumulate && p.test_fault != 7) {
+      if (j >= (uint32_t)CBUFS && !mbar_wait(c_free + b, ((j / CBUFS) - 1) & 1u, p.status, 17, limit)) break;
+      if (accumulate) {
         int vruns, vn, nb, nchunk;
         uint32_t m0, n0;
         const int total_chunks = chunk_count(j, &vruns, &vn, &nb, &nchunk, &m0, &n0);
@@ -601,11 +510,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       } else if (lane == 0) {
         mbar_arrive(c_ready + b);  // `=`: nothing to fetch, the buffer is simply free
       }
-#ifdef TC_WT_TIMING
-      wt_w[2] += clock64() - tf0;
-#endif
     }
-    WT_END(4);
     return;
   }
 
@@ -614,26 +519,18 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     // With several buffers, the buffer of tile j - 1 is released after tile j's copies have been issued: its read-out
     // overlaps them.  With one buffer the next tile cannot be finished before this one is released: no deferring.
     const bool defer = CBUFS > 1;
-    WT_T0();
     uint32_t j = 0;
     for (; j < ntiles; ++j) {
       const uint32_t b = j % CBUFS;
-      if (!WT_WAIT(0, mbar_wait(c_staged + b, (j / CBUFS) & 1u, p.status, 18, limit))) break;
-#ifdef TC_WT_TIMING
-      const long long ts0 = clock64();
-#endif
+      if (!mbar_wait(c_staged + b, (j / CBUFS) & 1u, p.status, 18, limit)) break;
       int vruns, vn, nb, nchunk;
       uint32_t m0, n0;
       const int total_chunks = chunk_count(j, &vruns, &vn, &nb, &nchunk, &m0, &n0);
       for (int c = lane; c < total_chunks; c += 32) {
         const Chunk k = chunk_of(c, b, vn, nb, nchunk, m0, n0);
-        if (p.test_fault != 6) bulk_store(const_cast<float*>(k.g), k.s, k.bytes);
+        bulk_store(const_cast<float*>(k.g), k.s, k.bytes);
       }
       asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-#ifdef TC_WT_TIMING
-      const long long ts1 = clock64();
-      wt_w[2] += ts1 - ts0;
-#endif
       if (!defer) {
         asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
         __syncwarp();
@@ -643,14 +540,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         __syncwarp();
         if (lane == 0) mbar_arrive(c_free + (j - 1) % CBUFS);
       }
-#ifdef TC_WT_TIMING
-      wt_w[3] += clock64() - ts1;
-#endif
     }
     asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
     __syncwarp();
     if (defer && j > 0 && lane == 0) mbar_arrive(c_free + (j - 1) % CBUFS);
-    WT_END(5);
     asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
   }
 }
