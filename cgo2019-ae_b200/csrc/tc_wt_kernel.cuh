@@ -98,9 +98,13 @@ template <class CF, int ROWS, int MODE, int LD>
 struct WtSlots {
   static constexpr int PER = MODE == 0 ? ROWS * 16 / 128 : (ROWS * 4 + 127) / 128;
   static constexpr uint32_t kNone = 0xffffffffu;
+  // Element slots come in pairs on the same row (two groups of k): one offset per pair.
+  static constexpr int NROW = MODE == 0 ? PER / 2 : PER;
+  static_assert(MODE != 0 || PER % 2 == 0, "element slots pair up");
+  __host__ __device__ static constexpr int row_of(int j) { return MODE == 0 ? j >> 1 : j; }
   uint32_t slot[PER];
-  uint32_t digit[PER];  // row / e0 (bits 8-15) and row % e0 (bits 0-7), e0 = extent of the class's first dimension
-  int64_t eo[PER];
+  uint32_t digit[NROW];  // row / e0 (bits 8-15) and row % e0 (bits 0-7), e0 = extent of the class's first dimension
+  int64_t eo[NROW];
   __device__ __forceinline__ void init(int ptid, int lg, uint32_t e0) {
     const int lane = ptid & 31, warp = ptid >> 5;
 #pragma unroll
@@ -124,8 +128,8 @@ struct WtSlots {
         off = kk * LD + el;
       }
       slot[j] = valid ? ((uint32_t)off | ((uint32_t)kk << 16) | ((uint32_t)el << 24)) : kNone;
-      digit[j] = (((uint32_t)el / e0) << 8) | ((uint32_t)el % e0);
-      eo[j] = -1;
+      digit[row_of(j)] = (((uint32_t)el / e0) << 8) | ((uint32_t)el % e0);
+      eo[row_of(j)] = -1;
     }
   }
   // Operand offsets of this thread's rows in the tile that starts at flattened index `flat0` of class `d`.
@@ -133,16 +137,16 @@ struct WtSlots {
     const uint32_t e0 = d.extent[0];
     const uint32_t rest0 = flat0 / e0, b0 = flat0 - rest0 * e0;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const uint32_t el = slot[j] >> 24;
-      if (slot[j] == kNone || flat0 + el >= limit) { eo[j] = -1; continue; }
+    for (int r = 0; r < NROW; ++r) {
+      const uint32_t sl = slot[MODE == 0 ? 2 * r : r], el = sl >> 24;
+      if (sl == kNone || flat0 + el >= limit) { eo[r] = -1; continue; }
       if (d.n <= 2) {
-        uint32_t d0 = b0 + (digit[j] & 0xffu), carry = digit[j] >> 8;
+        uint32_t d0 = b0 + (digit[r] & 0xffu), carry = digit[r] >> 8;
         if (d0 >= e0) { d0 -= e0; ++carry; }
-        eo[j] = (int64_t)d0 * d.s_in[0] + (d.n == 2 ? (int64_t)(rest0 + carry) * d.s_in[1] : 0);
+        eo[r] = (int64_t)d0 * d.s_in[0] + (d.n == 2 ? (int64_t)(rest0 + carry) * d.s_in[1] : 0);
       } else {
         int64_t unused;
-        decode(d, flat0 + el, limit, &eo[j], &unused);
+        decode(d, flat0 + el, limit, &eo[r], &unused);
       }
     }
   }
@@ -156,8 +160,8 @@ struct WtSlots {
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
       if (slot[j] == kNone || ((slot[j] >> 16) & 0xffu) >= kmax) continue;
-      const bool ok = eo[j] >= 0 && k0 + ((slot[j] >> 16) & 0xffu) < kend;
-      const float* src = ok ? g + eo[j] + ko[j] : g;
+      const bool ok = eo[row_of(j)] >= 0 && k0 + ((slot[j] >> 16) & 0xffu) < kend;
+      const float* src = ok ? g + eo[row_of(j)] + ko[j] : g;
       if constexpr (MODE == 0) cp_async4(sbase + (slot[j] & 0xffffu) * 4u, src, ok);
       else cp_async16(sbase + (slot[j] & 0xffffu) * 4u, src, ok);
     }

@@ -576,18 +576,25 @@ def test_fp32_long_contractions_stay_within_tolerance(pkg, orc, torch_cuda, path
     assert err <= TOL["float32"], (path, err, d)
 
 
-@pytest.mark.parametrize("n_b,mode", [(4096, "slices"), (8192, "passes")])
+@pytest.mark.parametrize("n_b,mode", [(4096, "persistent"), (4096, "slices"), (8192, "passes")])
 def test_fp32_long_contractions_on_large_outputs(pkg, orc, torch_cuda, n_b, mode):
-    """K = 8192 under the default path on outputs of 64 MB (16 K slices fill the 1 GiB of slice scratch exactly) and
-    128 MB (slices would not fit: the contraction runs as 16 sequential passes of 512 products into C).  Either way
-    no tensor-core chain is longer than 512 and the result stays inside the fp32 gate."""
+    """K = 8192 on outputs of 64 MB and 128 MB.  Under the default path the persistent tcgen05 kernel cuts the chain
+    itself (16 segments added into the resident output tile); on the one-CTA-per-tile kernel the planner slices K where
+    16 slices fill the 1 GiB of slice scratch exactly and runs 16 sequential passes of 512 products into C where they
+    would not fit.  Either way no tensor-core chain is longer than 512 and the result stays inside the fp32 gate."""
     expr = "C [a,4096,b,%d] += sum(c,8192) * A [c,a] * B [c,b];" % n_b
     keep = {}
-    err = _slab_check(pkg, orc, torch_cuda, expr, "float32", 33, [{"b": 0}, {"b": n_b - 1}, {"b": 1234}, {"a": 4095}], keep=keep)
+    kw = {} if mode == "persistent" else {"path": pkg.PATH_TCGEN05, "tile": (128, 128), "variant": 1}
+    err = _slab_check(pkg, orc, torch_cuda, expr, "float32", 33, [{"b": 0}, {"b": n_b - 1}, {"b": 1234}, {"a": 4095}], keep=keep, **kw)
     d = keep["desc"]
     keep.clear()
     assert d["math"].startswith("tf32x3") and d["chain"] <= 512, d
-    assert (d["ksplit"] == 16 and d["passes"] == 1) if mode == "slices" else (d["passes"] == 16 and d["ksplit"] == 1), d
+    if mode == "persistent":
+        assert d["kernel"] == "tf32wt_128x128" and d["ksplit"] == 1 and d["passes"] == 1, d
+    elif mode == "slices":
+        assert d["kernel"] == "tf32tc_128x128" and d["ksplit"] == 16 and d["passes"] == 1, d
+    else:
+        assert d["kernel"] == "tf32tc_128x128" and d["passes"] == 16 and d["ksplit"] == 1, d
     assert err <= TOL["float32"], (err, d)
 
 
