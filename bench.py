@@ -67,7 +67,7 @@ TOL = {"f64": 1e-12, "f32": 1e-5}
 # profiles/), keyed by the KERNEL that was captured and the workload: a plan that picks another kernel reports null.
 # cfg5 is 8 x the captured one-eighth slab (traffic is proportional to the number of f values).
 NCU_TRAFFIC_BYTES = {
-    ("dmma_ws_64x96", "cfg2"): 1984793088, ("dmma_ws_128x64", "cfg3"): 1341919744, ("tf32tc_96x128", "cfg4"): 1472193280,
+    ("dmma_ws_64x96", "cfg2"): 1984793088, ("dmma_ws_128x64", "cfg3"): 1341919744, ("tf32tc_96x128", "cfg4"): 1472193280, ("tf32wt_96x128", "cfg4"): 1475810560,
     ("dmma_ws_128x64", "cfg5_shard8"): 8369612032, ("dmma_ws_128x64", "cfg5"): 8 * 8369612032,
     ("dmma_wc_128x64", "cfg5_shard8"): 8197418496, ("dmma_wc_128x64", "cfg5"): 8 * 8197418496,
 }
@@ -703,14 +703,19 @@ def run_ours(args):
 
     # ---- roofline of the (single) kernel of the pass ----
     hbm_peak, hbm_src = measured_peaks()
-    pipe = "dmma_m8n8k4" if dtype == "f64" else "ffma"
-    pipe_peak = pkg.measure_peaks(which=(0,) if dtype == "f64" else (5,))[pipe]
+    # the pipe the chosen kernel computes on; fp32 on the tensor cores costs three TF32 products per product, so its
+    # ceiling in fp32 FLOP/s is a third of the TF32 probe's figure
+    which, scale = {"dmma": (0, 1.0), "dfma": (4, 1.0), "ffma": (5, 1.0), "tf32x3": (6, 1.0 / 3.0),
+                    "tf32x3_tcgen05": (7, 1.0 / 3.0)}.get(desc["math"], (0 if dtype == "f64" else 5, 1.0))
+    pipe, pipe_peak = next(iter(pkg.measure_peaks(which=(which,)).items()))
+    if scale != 1.0:
+        pipe, pipe_peak = pipe + " / 3 (three TF32 products per fp32 product)", pipe_peak * scale
     launch_s = sec / args.steps
     t_hbm = shard_bytes / (hbm_peak * 1e9)
     t_pipe = shard_flops / (pipe_peak * 1e12)
     if t_pipe >= t_hbm:
         roof = {"bound": "tensor", "achieved": shard_flops / launch_s * 1e-12, "peak": pipe_peak, "unit": "TFLOP/s",
-                "peak_source": "live register-only %s probe (bench-only probe library; of measured -- the driver's peak "
+                "peak_source": "live %s probe (bench-only probe library; of measured -- the driver's peak "
                                "file has no fp64/fp32 pipe figure)" % pipe}
     else:
         roof = {"bound": "hbm", "achieved": shard_bytes / launch_s * 1e-9, "peak": hbm_peak, "unit": "GB/s",

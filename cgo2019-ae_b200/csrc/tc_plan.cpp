@@ -438,7 +438,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
         bn = 128;
       }
     }
-    if (c.math == TC_MATH_TF32TC && p->opt.split_k == 0 && p->opt.c_path == 0) {
+    if (c.math == TC_MATH_TF32TC && p->opt.split_k == 0 && p->opt.c_path != 2) {
       // ... as the persistent kernel (two accumulators in tensor memory, output tile resident in shared memory)
       // wherever its tile buffers can hold the output in runs that leave as bulk copies.
       const int tbm = (bm == 96 || bm == 128) ? bm : 128;

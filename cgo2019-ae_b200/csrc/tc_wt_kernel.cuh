@@ -20,11 +20,14 @@
 //                         dependent global load per copy would serialise the issue).
 //   warp 20     MMA       owns tensor memory; its first lane issues lo*hi, hi*lo, hi*hi for every group of eight k
 //                         and commits onto the barriers that free the images and publish the accumulator.
-//   warps 21,23 FETCH     brings the tile's current contents from C up to CBUFS tiles ahead into one of CBUFS tile
-//                         buffers (`+=` / `-=` only) with cp.async, 512 contiguous bytes per instruction.
-//   warp 22     STORE     writes a finished tile back with bulk asynchronous copies and frees its buffer when they
-//                         have read it.  The load/store units carry the reads of C and the copy engine its writes:
-//                         one SM's copy engine moved about 19 bytes per cycle here, too little for both streams.
+//   warp 21     FETCH     only where the caller asked for sums to be stored (tc_options.c_path 1): brings the tile's
+//                         old values from C up to CBUFS tiles ahead into the tile buffer with bulk asynchronous
+//                         copies.  By default nothing is fetched: the buffer holds the products alone.
+//   warp 22     STORE     sends a finished tile to C with bulk asynchronous copies -- reduce-adds for `+=` / `-=`
+//                         (the memory system adds; measured faster than fetching and storing on every shape tried),
+//                         plain stores for `=` -- and frees its buffer when they have read it (one tile late where
+//                         there are several buffers, so that the read-out overlaps the next tile's copies).
+//   warp 23               no work.
 //
 // The tile lies in shared memory in the order it has in C: rows split into runs of E0 = args.epi_run elements that
 // are contiguous in C; element (m, n) sits at (m / E0) * run_stride + n * pitch + m % E0.  Where consecutive n are
@@ -178,6 +181,10 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void bulk_reduce_add(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;\n" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+
 template <class CF>
 __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __grid_constant__ TcKernelArgs p,
                                                                          float* __restrict__ C,
@@ -227,6 +234,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   const int nseg = (nk + CF::SEG_STEPS - 1) / CF::SEG_STEPS;
   auto seg_begin = [&](int seg) { return (int)((int64_t)seg * nk / nseg); };  // segments of (almost) equal length, none empty
   const bool accumulate = p.beta != 0;
+  // `+=` / `-=` reach C as bulk reduce-adds of the products alone (args.c_mode 2, the default: nothing is fetched) or
+  // as sums (args.c_mode 0: the tile's old values are fetched into the buffer first, the sums are stored).
+  const bool reduce = accumulate && p.c_mode == 2;
+  const bool fetch_old = accumulate && !reduce;
   const uint32_t limit = p.spin_limit;
 
   // Layout of a tile buffer (see the head of this file).
@@ -254,7 +265,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         tc05_fence_after();
         // the buffer holds the tile's old values (`+=`, `-=`) or is simply free (`=`)
         if (seg == 0 && !mbar_wait(c_ready + b, (j / CBUFS) & 1u, p.status, 11, limit)) { alive = false; break; }
-        const bool overwrite = !accumulate && seg == 0;
+        const bool overwrite = !fetch_old && seg == 0;
         float v[CPW];
         const uint32_t taddr = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + a * 128u + (uint32_t)cbase;
 #pragma unroll
@@ -501,7 +512,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     for (uint32_t j = 0; j < ntiles; ++j) {
       const uint32_t b = j % CBUFS;
       if (j >= (uint32_t)CBUFS && !mbar_wait(c_free + b, ((j / CBUFS) - 1) & 1u, p.status, 17, limit)) break;
-      if (accumulate) {
+      if (fetch_old) {
         int vruns, vn, nb, nchunk;
         uint32_t m0, n0;
         const int total_chunks = chunk_count(j, &vruns, &vn, &nb, &nchunk, &m0, &n0);
@@ -512,7 +523,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           bulk_load(k.s, k.g, k.bytes, c_ready + b);
         }
       } else if (lane == 0) {
-        mbar_arrive(c_ready + b);  // `=`: nothing to fetch, the buffer is simply free
+        mbar_arrive(c_ready + b);  // nothing to fetch: the buffer is simply free
       }
     }
     return;
@@ -532,7 +543,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       const int total_chunks = chunk_count(j, &vruns, &vn, &nb, &nchunk, &m0, &n0);
       for (int c = lane; c < total_chunks; c += 32) {
         const Chunk k = chunk_of(c, b, vn, nb, nchunk, m0, n0);
-        bulk_store(const_cast<float*>(k.g), k.s, k.bytes);
+        if (reduce) bulk_reduce_add(const_cast<float*>(k.g), k.s, k.bytes);
+        else bulk_store(const_cast<float*>(k.g), k.s, k.bytes);
       }
       asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
       if (!defer) {

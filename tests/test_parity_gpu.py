@@ -523,6 +523,9 @@ def test_persistent_tcgen05_kernel(pkg, orc, torch_cuda, expr, tile):
     err, d = _run(pkg, orc, torch_cuda, expr, "float32", 24, **kw)
     assert d["kernel"].startswith("tf32wt_") and d["chain"] <= 512 and d["ksplit"] == 1 and d["passes"] == 1, d
     assert err <= TOL["float32"], (expr, err, d)
+    # (default: the tile leaves as bulk reduce-adds of the products)  The other way: old values fetched, sums stored.
+    err, d = _run(pkg, orc, torch_cuda, expr, "float32", 27, c_path=1, **kw)
+    assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, "fetch and store", err, d)
 
 
 def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):
