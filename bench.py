@@ -67,7 +67,7 @@ TOL = {"f64": 1e-12, "f32": 1e-5}
 # profiles/), keyed by the KERNEL that was captured and the workload: a plan that picks another kernel reports null.
 # cfg5 is 8 x the captured one-eighth slab (traffic is proportional to the number of f values).
 NCU_TRAFFIC_BYTES = {
-    ("dmma_ws_64x96", "cfg2"): 1984793088, ("dmma_ws_128x64", "cfg3"): 1341919744, ("tf32tc_96x128", "cfg4"): 1472193280, ("tf32wt_96x128", "cfg4"): 1475810560,
+    ("dmma_ws_64x96", "cfg2"): 1984793088, ("dmma_ws_128x64", "cfg3"): 1341919744, ("tf32tc_96x128", "cfg4"): 1472193280, ("tf32wt_96x128", "cfg4"): 1475021824,
     ("dmma_ws_128x64", "cfg5_shard8"): 8369612032, ("dmma_ws_128x64", "cfg5"): 8 * 8369612032,
     ("dmma_wc_128x64", "cfg5_shard8"): 8197418496, ("dmma_wc_128x64", "cfg5"): 8 * 8197418496,
 }
