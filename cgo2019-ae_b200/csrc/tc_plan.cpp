@@ -439,10 +439,14 @@ int tc_plan_build(tc_plan* p, std::string* why) {
       }
     }
     if (c.math == TC_MATH_TF32TC && p->opt.split_k == 0 && p->opt.c_path != 2) {
-      // ... as the persistent kernel (two accumulators in tensor memory, output tile resident in shared memory)
-      // wherever its tile buffers can hold the output in runs that leave as bulk copies.
+      // ... as the persistent kernel (two accumulators in tensor memory, output tile staged in shared memory)
+      // wherever its tile buffers can hold the output in runs that leave as bulk copies and both operands are
+      // fetched 16 bytes at a time: its four loader warps issue element gathers slower than the 24 warps of three
+      // resident one-tile CTAs do (measured on the fp32 items of the reference's benchmark list, one operand
+      // gathered by element: 12.0-14.7 against 15.5-16.7 TFLOP/s; with vector loads on both sides it is 8-27 % ahead).
       const int tbm = (bm == 96 || bm == 128) ? bm : 128;
-      if (wt_eligible(a, tbm, es) && tc_kernel_exists(TC_F32, TC_MATH_TF32TC, tbm, 128, 1)) { bm = tbm; bn = 128; variant = 1; }
+      const bool vector_loads = (c.vec_x || c.kvec_x) && (c.vec_y || c.kvec_y);
+      if (vector_loads && wt_eligible(a, tbm, es) && tc_kernel_exists(TC_F32, TC_MATH_TF32TC, tbm, 128, 1)) { bm = tbm; bn = 128; variant = 1; }
     }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
     if (ctas < 2 * sms) {
