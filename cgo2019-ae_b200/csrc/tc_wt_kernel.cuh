@@ -191,7 +191,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
                                                                          const float* __restrict__ X,
                                                                          const float* __restrict__ Y) {
   constexpr int BM = CF::BM, BN = CF::BN, BK = CF::BK;
-  const int STAGES = p.ring_stages, CBUFS = p.out_bufs, IMGS = p.img_sets, SLOTS = 2 * IMGS;
+  const int STAGES = p.ring_stages, CBUFS = p.out_bufs, IMGS = p.img_sets;
+  // Image units, handed from the split warps to the MMA thread through two slots.  With one image set a unit is a
+  // group of eight k (the two halves of the set take turns: finer hand-over, which short contractions want); with two
+  // sets a unit is a whole K step of sixteen and a slot is a set (half as many waits, fences and commits per product,
+  // which is what bounds long contractions).
+  const bool whole = IMGS == 2;
+  constexpr uint32_t SLOTS = 2;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
   uint64_t* full = bars;                             // [STAGES] a stage's copies have landed
@@ -213,7 +219,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, CF::THREADS); mbar_init(empty + s, CF::SPLIT_WARPS); }
-    for (int h = 0; h < SLOTS; ++h) { mbar_init(img_full + h, CF::SPLIT_WARPS); mbar_init(img_free + h, 1); }
+    for (uint32_t h = 0; h < SLOTS; ++h) { mbar_init(img_full + h, CF::SPLIT_WARPS); mbar_init(img_free + h, 1); }
     for (int h = 0; h < 2; ++h) { mbar_init(acc_full + h, 1); mbar_init(acc_free + h, CF::EPI_WARPS); }
     for (int b = 0; b < CBUFS; ++b) { mbar_init(c_ready + b, 1); mbar_init(c_staged + b, CF::EPI_WARPS); mbar_init(c_free + b, 1); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -339,19 +345,38 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         // the stage is in registers: the loaders may refill it
         __syncwarp();
         if (lane == 0) mbar_arrive(empty + s);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (h >= nh) break;
-          // unit u (eight k) goes to image slot sl = u % SLOTS: image set sl / 2, position sl % 2 among its two groups of 8 k
+        if (whole) {
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
           if (use > 0 && !mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit)) return;
-          float* ua_hi = images + (sl >> 1) * CF::UMMA_ELEMS;
+          float* ua_hi = images + sl * CF::UMMA_ELEMS;
           float* ua_lo = ua_hi + BK * BN;
           float* ub_hi = ua_lo + BK * BN;
           float* ub_lo = ub_hi + BK * BM;
-          put(ua_hi, ua_lo, ry, 2 * (int)(sl & 1u) + qy, vy[h]);
-          if (has_x) put(ub_hi, ub_lo, rx, 2 * (int)(sl & 1u) + qx, vx[h]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (h >= nh) break;
+            put(ua_hi, ua_lo, ry, 2 * h + qy, vy[h]);
+            if (has_x) put(ub_hi, ub_lo, rx, 2 * h + qx, vx[h]);
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(img_full + sl);
+          continue;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (h >= nh) break;
+          // unit u (eight k) goes to slot sl = u % 2: position sl among the image set's two groups of 8 k
+          const uint32_t sl = u % SLOTS, use = u / SLOTS;
+          ++u;
+          if (use > 0 && !mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit)) return;
+          float* ua_hi = images;
+          float* ua_lo = ua_hi + BK * BN;
+          float* ub_hi = ua_lo + BK * BN;
+          float* ub_lo = ub_hi + BK * BM;
+          put(ua_hi, ua_lo, ry, 2 * (int)sl + qy, vy[h]);
+          if (has_x) put(ub_hi, ub_lo, rx, 2 * (int)sl + qx, vx[h]);
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
           if (lane == 0) mbar_arrive(img_full + sl);
@@ -433,6 +458,27 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           const int it_begin = seg_begin(seg), it_end = seg_begin(seg + 1);
           for (int it = it_begin; alive && it < it_end; ++it) {
             const int nh = (kend - (kbeg + (uint32_t)it * BK)) > 8u ? 2 : 1;
+            // per group of 8 k: two 4-k chunks per MMA, 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
+            auto three = [&](uint32_t set, uint32_t pos, uint32_t acc) {
+              const uint32_t ya = smem_u32(images + set * CF::UMMA_ELEMS) + pos * 256u, xa = ya + 2 * BK * BN * 4;
+              const uint64_t ah = umma_desc_k(ya, 128, (BK / 4) * 128);
+              const uint64_t al = umma_desc_k(ya + BK * BN * 4, 128, (BK / 4) * 128);
+              const uint64_t bh = umma_desc_k(xa, 128, (BK / 4) * 128);
+              const uint64_t bl = umma_desc_k(xa + BK * BM * 4, 128, (BK / 4) * 128);
+              tc05_mma_tf32(d_tmem, al, bh, IDESC, acc);
+              tc05_mma_tf32(d_tmem, ah, bl, IDESC, 1u);
+              tc05_mma_tf32(d_tmem, ah, bh, IDESC, 1u);
+            };
+            if (whole) {
+              const uint32_t sl = u % SLOTS, use = u / SLOTS;
+              ++u;
+              if (!mbar_wait(img_full + sl, use & 1u, p.status, 16, limit)) { alive = false; break; }
+              tc05_fence_after();
+              three(sl, 0u, it > it_begin ? 1u : 0u);
+              if (nh == 2) three(sl, 1u, 1u);
+              tc05_commit(img_free + sl);
+              continue;
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               if (h >= nh) break;
@@ -440,15 +486,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
               ++u;
               if (!mbar_wait(img_full + sl, use & 1u, p.status, 16, limit)) { alive = false; break; }
               tc05_fence_after();
-              // two 4-k chunks per MMA: 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
-              const uint32_t ya = smem_u32(images + (sl >> 1) * CF::UMMA_ELEMS) + (sl & 1u) * 256u, xa = ya + 2 * BK * BN * 4;
-              const uint64_t ah = umma_desc_k(ya, 128, (BK / 4) * 128);
-              const uint64_t al = umma_desc_k(ya + BK * BN * 4, 128, (BK / 4) * 128);
-              const uint64_t bh = umma_desc_k(xa, 128, (BK / 4) * 128);
-              const uint64_t bl = umma_desc_k(xa + BK * BM * 4, 128, (BK / 4) * 128);
-              tc05_mma_tf32(d_tmem, al, bh, IDESC, (it > it_begin || h > 0) ? 1u : 0u);
-              tc05_mma_tf32(d_tmem, ah, bl, IDESC, 1u);
-              tc05_mma_tf32(d_tmem, ah, bh, IDESC, 1u);
+              three(0u, sl, (it > it_begin || h > 0) ? 1u : 0u);
               tc05_commit(img_free + sl);
             }
           }
