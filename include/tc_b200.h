@@ -62,7 +62,10 @@ typedef struct tc_options {
   int c_path;      /* how `+=`/`-=` reach the output: 0 = planner's choice, 1 = read-modify- */
                    /*   write in the epilogue, 2 = accumulators start from the output,       */
                    /*   3 = bulk asynchronous reduce-add from shared memory (persistent      */
-                   /*   kernels, rows contiguous in the output; falls back to 1 elsewhere)   */
+                   /*   kernels, rows contiguous in the output; falls back to 1 elsewhere).  */
+                   /*   The persistent fp32 kernel stages its tile in shared memory either   */
+                   /*   way: 0 and 3 send it as reduce-adds, 1 fetches the old values and    */
+                   /*   stores the sums, 2 runs the tiles one CTA per tile instead.          */
   int tma;         /* tiled TMA copies in the persistent fp64 kernel (operand tiles that are plain 2-D boxes;
                       output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
                       2 = operands only, 3 = output only, 4 = both but the output per warp, never per tile */
