@@ -1,25 +1,26 @@
 // Persistent, warp-specialised fp32 contraction kernel for sm_100a: three TF32 products per fp32 product on
-// tcgen05.mma, two accumulators in tensor memory, the output tile resident in shared memory.
+// tcgen05.mma, two accumulators in tensor memory, the output tile staged in shared memory.
 //
 // Same tiling, address scheme, operand images, split (v = hi + lo) and MMA descriptors as the one-CTA-per-tile
 // tcgen05 path of tc_contract_kernel (tc_kernels.cuh); what changes is WHO does what and WHEN.  One CTA per SM lives
 // for the whole contraction and walks a strided list of BM x 128 output tiles; its warps have fixed roles that meet
 // only through mbarriers in shared memory:
 //
-//   warps 0-7   EPILOGUE  one thread per lane of D (n) and half of its columns.  Waits for an accumulator, reads it with tcgen05.ld 32
-//                         columns (m) at a time, frees it, and adds alpha * D into the output tile that waits in
-//                         shared memory.  A contraction longer than SEG_STEPS K steps is cut into segments that
-//                         alternate between the two accumulators and are added into the tile one after another in
+//   warps 0-7   EPILOGUE  one thread per lane of D (n) and half of its columns (m).  Waits for an accumulator, reads
+//                         its columns with tcgen05.ld, frees the accumulator, and puts alpha * D into the tile buffer
+//                         in shared memory.  A contraction longer than SEG_STEPS K steps is cut into segments that
+//                         alternate between the two accumulators and are added into the buffer one after another in
 //                         round-to-nearest fp32, so no tensor-core accumulation chain exceeds 512 products and the
 //                         output still moves once.
 //   warps 8-15  SPLIT     turn the gathered fp32 stage into the hi and lo TF32 images the MMA reads (128-byte core
-//                         matrices, K-major), eight k at a time; one 16-byte chunk of each operand per thread.
-//   warps 16-19 LOADERS   decode the tile's operand offsets and issue every cp.async of its stages (the three
-//                         loaders of tc_kernels.cuh), running ahead across tile boundaries by the depth of the ring.
-//                         Row offsets live in registers, the contraction offsets of a step in shared memory (a
-//                         dependent global load per copy would serialise the issue).
+//                         matrices, K-major); one 16-byte chunk of each operand per thread and group of eight k.
+//   warps 16-19 LOADERS   issue every cp.async of the stages (the three loader shapes of tc_kernels.cuh), running
+//                         ahead across tile boundaries by the depth of the ring.  Row offsets live in registers, the
+//                         contraction offsets of a step in shared memory (a dependent global load per copy would
+//                         serialise the issue).
 //   warp 20     MMA       owns tensor memory; its first lane issues lo*hi, hi*lo, hi*hi for every group of eight k
-//                         and commits onto the barriers that free the images and publish the accumulator.
+//                         and commits onto the barriers that free the images and publish the accumulator.  Images
+//                         change hands eight k at a time (short contractions) or a K step at a time (long ones).
 //   warp 21     FETCH     only where the caller asked for sums to be stored (tc_options.c_path 1): brings the tile's
 //                         old values from C up to CBUFS tiles ahead into the tile buffer with bulk asynchronous
 //                         copies.  By default nothing is fetched: the buffer holds the products alone.
@@ -56,7 +57,7 @@ struct WtCfg {
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
   static constexpr int UMMA_ELEMS = 2 * BK * (BM + BN);  // hi and lo images of both operands for one K step
   static constexpr int GROUPS = 1;                       // tiles a CTA works on at a time (launch arithmetic)
-  // Six warpgroups: epilogue, epilogue, split, split, loaders, {MMA, fetch, store, fetch}.
+  // Six warpgroups: epilogue, epilogue, split, split, loaders, {MMA, fetch, store, a warp without work}.
   static constexpr int CTA_THREADS = 24 * 32;
   static constexpr int SPLIT_WARPS = 8, SPLIT_THREADS = 256, EPI_WARPS = 8;
   // Registers follow the roles (setmaxnreg, every warp of a warpgroup executes it): the CTA starts with 80 per thread
@@ -72,7 +73,7 @@ struct WtCfg {
   // output tile buffers: room for the padded layout (pitch E0 + 4 only where E0 >= 64: at most BM / 64 runs)
   static constexpr int CTILE_ELEMS = BN * (BM + 4 * (BM / 64));
   // Shared memory is carved at run time (args.out_bufs tile buffers, args.img_sets image sets, args.ring_stages
-  // stages; see wt_carve): short contractions want tile buffers (the output stream is what has to be kept in flight),
+  // stages, chosen at launch): short contractions want tile buffers (the output stream is what has to be kept in flight),
   // long ones want operand stages and a second image set (the MMAs are).
   static constexpr int MAX_STAGES = 8, MAX_CBUFS = 3, MAX_IMGS = 2;
   static constexpr int NBARS = (2 * MAX_STAGES + 4 * MAX_IMGS + 4 + 3 * MAX_CBUFS + 1) / 2 * 2;  // even: what follows stays 16-byte aligned
@@ -80,7 +81,7 @@ struct WtCfg {
   static constexpr int HEAD_BYTES = NBARS * 8 + 16 + KSTEPS_KEPT * 32 * 8;  // barriers, tensor-memory slot, contraction offsets
   static constexpr int SMEM_BYTES = 232448;
   static_assert(HEAD_BYTES % 16 == 0, "images, tile buffers and stages start on 16 bytes");
-  static_assert(BM % 32 == 0 && BM <= 128, "columns are read 32 at a time; an accumulator has 128 columns");
+  static_assert(BM % 32 == 0 && BM <= 128, "a warp reads BM / 2 columns, 16 at a time; an accumulator has 128 columns");
   // stages that fit beside `cbufs` tile buffers and `imgs` image sets
   static constexpr int stages_for(int cbufs, int imgs) {
     const int left = SMEM_BYTES - HEAD_BYTES - cbufs * CTILE_ELEMS * 4 - imgs * UMMA_ELEMS * 4;
@@ -442,7 +443,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     return;
   }
 
-  reg_dec<CF::SMALL_REGS>();  // the last warpgroup: MMA, fetch, store, fetch
+  reg_dec<CF::SMALL_REGS>();  // the last warpgroup: MMA, fetch, store and a warp without work
   if (warp == 20) {
     // ------------------------------------------------------------------ MMA ----
     if (lane == 0) {
