@@ -69,7 +69,8 @@ int run_persistent(Kern kern, const TcKernelArgs* a, void* C, const void* X, con
   int dev = 0, sms = 0;
   TC_CUDA_OK(cudaGetDevice(&dev));
   TC_CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const unsigned tiles = a->tiles_m * a->tiles_n, per_cta = CF::GROUPS;  // a CTA's groups take consecutive tiles
+  // work items: tiles, times the K slices where the plan has them; a CTA's groups take consecutive items
+  const unsigned tiles = a->tiles_m * a->tiles_n * (a->ksplit > 1 ? a->ksplit : 1u), per_cta = CF::GROUPS;
   const unsigned grid = (tiles + per_cta - 1) / per_cta < (unsigned)sms ? (tiles + per_cta - 1) / per_cta : (unsigned)sms;  // one persistent CTA per SM
   kern<<<grid, CF::CTA_THREADS, CF::SMEM_BYTES, stream>>>(*a, static_cast<T*>(C), static_cast<const T*>(X),
                                                            static_cast<const T*>(Y));

@@ -365,6 +365,7 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   //   * anything that would leave most SMs without a tile: 64 x 64, one CTA per tile.
   const int64_t sms = p->sm_count > 0 ? p->sm_count : TC_DEFAULT_SMS;
   int bm = 128, bn = 128, variant = 0;
+  bool slice_persistent = false;  // the persistent reduce-add kernel with K slices (few tiles, long contraction)
   if (p->opt.tile_m > 0 || p->opt.tile_n > 0) {
     bm = p->opt.tile_m;
     bn = p->opt.tile_n;
@@ -450,8 +451,22 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     }
     const int64_t ctas = ((mf + bm - 1) / bm) * ((nf + bn - 1) / bn);
     if (ctas < 2 * sms) {
-      bm = 64; bn = 64; variant = 0;
-      if (c.math == TC_MATH_TF32TC) c.math = TC_MATH_TF32X3;  // no 64-wide tcgen05 tile: same arithmetic on mma.sync
+      // Too few tiles to fill the GPU.  fp64 with a long contraction stays on the persistent 128 x 64 kernel and
+      // slices K over its CTAs instead (16-byte loads along k, tiled TMA operands and two consumer groups are worth
+      // more than small tiles: measured 3-4 x on few-tile, long-K items of the reference's list); everything else
+      // runs one CTA per 64 x 64 tile, with K slices where K is long.
+      const int64_t t128 = ((mf + 127) / 128) * ((nf + 63) / 64), t64 = ((mf + 63) / 64) * ((nf + 63) / 64);
+      // ... unless its 128-row tiles pad the problem much more than 64-row ones would while the small kernel can
+      // at least load one operand by vector (measured on 312 x 296 outputs: 20 % more padded work cost 20 %)
+      const bool padding_ok = 2 * t128 * 100 <= t64 * 112 || (!c.vec_x && !c.vec_y);
+      if (c.math == TC_MATH_DMMA && p->opt.split_k == 0 && (kf + TC_BK - 1) / TC_BK >= 64 && t128 * ((kf + TC_BK - 1) / TC_BK / 16) >= 2 * sms &&
+          padding_ok && tc_kernel_exists(TC_F64, TC_MATH_DMMA, 128, 64, 2)) {
+        bm = 128; bn = 64; variant = 2;
+        slice_persistent = true;
+      } else {
+        bm = 64; bn = 64; variant = 0;
+        if (c.math == TC_MATH_TF32TC) c.math = TC_MATH_TF32X3;  // no 64-wide tcgen05 tile: same arithmetic on mma.sync
+      }
     }
     if (p->opt.variant > 0) variant = p->opt.variant - 1;
   }
@@ -477,8 +492,14 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   // K split: only when the tile count cannot fill the GPU and K is long.
   int64_t ksplit = 1;
   const int64_t ksteps = (kf + bk - 1) / bk;
-  const bool persistent = tc_kernel_is_persistent(c);  // these kernels do not split K
-  if (persistent) ksplit = 1;
+  const bool persistent = tc_kernel_is_persistent(c);
+  // Persistent kernels do not split K, except the fp64 reduce-add kernel: on request (forced tile and split_k), or
+  // where the planner kept it for a problem of few tiles (about four work items per SM, slices of at least 16 steps).
+  const bool ws_kernel = c.math == TC_MATH_DMMA && c.variant == 2;
+  if (persistent && ws_kernel && p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
+  else if (persistent && ws_kernel && slice_persistent)
+    ksplit = std::max<int64_t>(1, std::min<int64_t>((4 * sms + tiles - 1) / tiles, ksteps / 16));
+  else if (persistent) ksplit = 1;
   else if (p->opt.split_k > 1) ksplit = std::min<int64_t>(p->opt.split_k, ksteps);
   else if (p->opt.split_k == 0 && tiles * 2 <= sms && ksteps >= 16)
     ksplit = std::max<int64_t>(1, std::min<int64_t>((2 * sms) / tiles, ksteps / 8));

@@ -302,14 +302,24 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   }
   __syncthreads();
 
-  const uint32_t total = p.tiles_m * p.tiles_n;
+  // Work items: output tiles, or -- where the planner sliced the contraction (few tiles, long K) -- (slice, tile)
+  // pairs, slices of one tile spread over the CTAs; a slice's result goes to the plan's workspace as a partial tile
+  // and tc_combine_kernel adds the slices in ascending order.
+  const uint32_t tiles = p.tiles_m * p.tiles_n;
+  const uint32_t total = tiles * p.ksplit;
+  const bool sliced = p.ksplit > 1;
   const uint32_t first = 2u * blockIdx.x + gi, step = 2u * gridDim.x;
-  const int nk = (int)((p.Kflat + BK - 1) / BK);
-  const uint32_t kend = p.Kflat;
   const bool accumulate = p.beta != 0;
+  // contraction range [kb, ke) and number of K steps of work item `item`
+  auto k_range = [&](uint32_t item, uint32_t* kb, uint32_t* ke) {
+    const uint32_t slice = item / tiles;
+    *kb = slice * p.k_chunk;
+    *ke = min(p.Kflat, *kb + p.k_chunk);
+    return (int)((*ke - *kb + BK - 1) / BK);
+  };
 
   // Whole-tile output: the geometry allows it, the kernel has the room, and the epilogue is the bulk one.
-  const bool tile_out = CF::TILE_OK && p.c_tensor == 2 && p.c_mode == 2;
+  const bool tile_out = CF::TILE_OK && p.c_tensor == 2 && p.c_mode == 2 && !sliced;
 
   if (is_store) {
     // --------------------------------------------------------------- store ----
@@ -360,8 +370,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       int64_t* offy_n = offc_m + BM;
       int64_t* offc_n = offy_n + BN;
       if (!mbar_wait(&tab_empty[par], ((titer >> 1) & 1) ^ 1, p.status, 1, p.spin_limit)) return;
-      uint32_t tm, tn;
-      tile_coords(p, tile, &tm, &tn);
+      uint32_t tm, tn, kbeg, kend;
+      tile_coords(p, tile % tiles, &tm, &tn);
+      const int nk = k_range(tile, &kbeg, &kend);
       const uint32_t m0 = tm * BM, n0 = tn * BN;
       for (int i = ptid; i < BM + BN; i += CF::THREADS) {
         if (i < BM) decode(p.M, m0 + i, p.Mflat, &offx_m[i], &offc_m[i]);
@@ -377,14 +388,14 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
           if (cm >= 0 && cn >= 0) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(C + cn + cm));
         }
       };
-      const bool pf = accumulate && p.prefetch_dist != 0;
+      const bool pf = accumulate && p.prefetch_dist != 0 && !sliced;
       if (pf && !p.c_stream) prefetch_c();
       for (int ks = 0; ks < nk; ++ks, ++it) {
         const uint32_t s = it % STAGES;
         if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, p.status, 2, p.spin_limit)) return;
         double* xs = gstage + s * CF::STAGE_ELEMS;
         double* ys = xs + CF::XIMG;
-        const uint32_t k0 = (uint32_t)ks * BK;
+        const uint32_t k0 = kbeg + (uint32_t)ks * BK;
         if constexpr (CF::ANY_TMA) {
           if (ptid == 0) {
             mbar_arrive_expect_tx(&full[s], CF::TMA_BYTES);
@@ -425,7 +436,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // Optional (c_mode 1, 32-byte-contiguous output): the accumulators start as alpha*C.  The producers
     // prefetched this tile's C into L2 a whole tile ago, all loads go out at once and overlap the wait for
     // the first stage; the epilogue is then stores only.
-    const bool from_c = accumulate && p.c_mode == 1 && p.vec_c == 4;
+    uint32_t kbeg, kend;
+    const int nk = k_range(tile, &kbeg, &kend);
+    const bool from_c = accumulate && p.c_mode == 1 && p.vec_c == 4 && !sliced;
     if (from_c) {
       if (!mbar_wait(&tab_full[par], (titer >> 1) & 1, p.status, 5, p.spin_limit)) return;
 #pragma unroll
@@ -450,7 +463,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
       if (!mbar_wait(&full[s], (it / STAGES) & 1, p.status, 3, p.spin_limit)) return;
       const double* xs = gstage + s * CF::STAGE_ELEMS;
       const double* ys = xs + CF::XIMG;
-      const int kleft = (int)kend - ks * BK;
+      const int kleft = (int)(kend - kbeg) - ks * BK;
       const int nks = kleft >= BK ? BK / 4 : (kleft + 3) / 4;
 #pragma unroll
       for (int kq = 0; kq < BK / 4; ++kq) {
@@ -491,9 +504,23 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // TMA reduce-add (or store) per batch replaces eight per-row copies.  Rows and columns beyond the tensor are
     // clipped by the copy engine; boxes that lie outside altogether are not issued.
     uint32_t tm, tn;
-    tile_coords(p, tile, &tm, &tn);
+    tile_coords(p, tile % tiles, &tm, &tn);
     const uint32_t m_idx = tm * BM + wm0, n_base = tn * BN + wn0;
-    if (tile_out) {
+    if (sliced) {
+      // partial tile of this slice, [n][m] as tc_combine_kernel reads it (every element, padding included)
+      double* ws = reinterpret_cast<double*>(p.ws) +
+                   ((size_t)(tile / tiles) * tiles + (size_t)tn * p.tiles_m + tm) * (size_t)(BM * BN);
+#pragma unroll
+      for (int nb = 0; nb < 2 * NB2; ++nb) {
+        double* row = ws + (size_t)(wn0 + 16 * (nb >> 1) + 2 * g + (nb & 1)) * BM + wm0 + 4 * t;
+#pragma unroll
+        for (int i = 0; i < MB2; ++i) {
+          double2* dst = reinterpret_cast<double2*>(row + 16 * i);
+          dst[0] = make_double2(acc[nb][2 * i][0], acc[nb][2 * i + 1][0]);
+          dst[1] = make_double2(acc[nb][2 * i][1], acc[nb][2 * i + 1][1]);
+        }
+      }
+    } else if (tile_out) {
       // Whole tile through the shared staging area, filled in the order g0, g1, g0, ...: use number u may start
       // once use u - 1 has been read out.  After the first wait the two groups stay out of phase.
       // The area is used in the order (0,g0) (0,g1) (1,g0) (1,g1) ...: group 1 may write tile t once group 0's tile

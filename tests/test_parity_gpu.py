@@ -601,6 +601,22 @@ def test_fp32_long_contractions_on_large_outputs(pkg, orc, torch_cuda, n_b, mode
     assert err <= TOL["float32"], (err, d)
 
 
+def test_persistent_fp64_kernel_with_k_slices(pkg, orc, torch_cuda):
+    """Few output tiles and a long contraction: the planner keeps the persistent fp64 kernel and slices K over its
+    CTAs (partial tiles in the plan's workspace, added in slice order by the combine kernel); also on request, with
+    ragged tiles, a contraction that is no multiple of the K step, every operator and every loader."""
+    err, d = _run(pkg, orc, torch_cuda, "C [a,312,b,296] += sum(c,312,d,96) * A [c,a,d] * B [d,c,b];", "float64", 51)
+    assert d["kernel"] == "dmma_ws_128x64" and d["ksplit"] > 1 and d["workspace_bytes"] > 0, d
+    assert err <= TOL["float64"], (err, d)
+    for expr in ("C [a,200,b,70] -= sum(c,1003) * A [c,a] * B [b,c];",          # 2-D operands: tiled TMA copies
+                 "C [a,200,b,70] = sum(c,1003) * A [a,c] * B [c,b];",           # the other way round
+                 "C [a,40,b,9,c,30] += sum(d,77,e,13) * A [e,a,d,b] * B [d,c,e];"):   # element gathers
+        for split in (2, 5, 64):
+            err, d = _run(pkg, orc, torch_cuda, expr, "float64", 52, tile=(128, 64), variant=3, split_k=split)
+            assert d["kernel"] == "dmma_ws_128x64" and d["ksplit"] > 1, d
+            assert err <= TOL["float64"], (expr, split, err, d)
+
+
 def test_a_wait_that_gives_up_is_reported_and_the_context_survives(pkg, orc, torch_cuda):
     """Failure detection without a fault: with tc_options.test_fault the persistent kernel's producers leave one
     stage unannounced and waits give up after 2^14 polls.  The kernel must end by itself, the status word must
