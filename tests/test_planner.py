@@ -206,6 +206,24 @@ def test_index_classes_reproduce_the_contraction(pkg, orc):
     assert seen_split > 0  # the digit re-ordering was exercised
 
 
+def test_few_tiles_and_a_long_contraction(pkg):
+    """fp64 problems that cannot fill the GPU with tiles: the persistent kernel with K slices where its tiles do not
+    pad much more than small ones (or the small kernel would gather both operands by element), else one CTA per tile."""
+    both_gathered = _plan(pkg, "t3 [a,312,b,296] += sum(c,312,d,312) * t2 [c,a,d] * v2 [d,c,b];").describe()
+    assert both_gathered["kernel"] == "dmma_ws_128x64" and both_gathered["ksplit"] > 1 and both_gathered["tiles"] == [3, 5]
+    assert both_gathered["workspace_bytes"] == both_gathered["ksplit"] * 15 * 128 * 64 * 8
+    assert both_gathered["k_chunk"] % 16 == 0 and both_gathered["k_chunk"] >= 256
+    one_vector = _plan(pkg, "t3 [a,312,b,296] += sum(c,296,d,312) * t2 [a,c,d] * v2 [d,b,c];").describe()
+    assert one_vector["kernel"] == "dmma_64x64_w4" and one_vector["ksplit"] > 1
+    narrow = _plan(pkg, "t3 [a,72,b,72,c,72] += sum(d,72,e,72) * t2 [a,d,e,c] * v2 [e,b,d];").describe()
+    assert narrow["kernel"] == "dmma_ws_128x64" and narrow["ksplit"] > 1 and narrow["tiles"] == [41, 2]
+    short = _plan(pkg, "C [a,312,b,296] += sum(c,40) * A [c,a] * B [c,b];").describe()
+    assert short["kernel"] == "dmma_64x64_w4" and short["ksplit"] == 1
+    # on request the persistent kernel slices K whatever the shape
+    forced = _plan(pkg, "C [a,200,b,70] -= sum(c,1003) * A [c,a] * B [b,c];", tile=(128, 64), variant=3, split_k=5).describe()
+    assert forced["kernel"] == "dmma_ws_128x64" and forced["ksplit"] == 5
+
+
 def test_no_default_fp32_plan_runs_a_tensor_core_chain_longer_than_512(pkg):
     """fp32 on the tensor cores accumulates with truncation, so the planner bounds every accumulation chain:
     K slices where their scratch fits 1 GiB, sequential passes into C beyond that."""
