@@ -77,7 +77,11 @@ struct WsCfg {
   static constexpr int WGM = 2, WGN = BN == 96 ? 3 : 2, CW = WGM * WGN;  // consumer warps per group
   static constexpr int WM = BM / WGM, WN = BN / WGN;
   static constexpr int CONSUMER_THREADS = CW * 32;
-  static constexpr int THREADS = 64;            // producer threads per group
+  // producer threads per group: two warps where every operand arrives 16 bytes (or a tiled copy) at a time, four
+  // where one is gathered element by element (48 eight-byte copies per thread and stage with two warps: the
+  // producers, not the tensor pipe, set the pace)
+  // (not on the 64 x 96 tile, whose store warpgroup already makes the CTA 640 threads)
+  static constexpr int THREADS = ((MODEX == LM_ELEM || MODEY == LM_ELEM) && BN != 96) ? 128 : 64;
   // Whole-tile output (below) pays on the 64 x 96 tile, whose six consumer warps otherwise queue 24 small
   // copies per tile; on 128 x 64 the extra warpgroup costs the consumers registers and measured slower.
   static constexpr bool TILE_OUT = BN == 96;
@@ -269,9 +273,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   constexpr int CW = CF::CW;
-  const bool is_store = CF::STORE_THREADS > 0 && warp >= 2 * CW + 4;
+  constexpr int PW = CF::THREADS / 32;  // producer warps per group
+  const bool is_store = CF::STORE_THREADS > 0 && warp >= 2 * CW + 2 * PW;
   const bool is_producer = !is_store && warp >= 2 * CW;
-  const int gi = is_producer ? (warp - 2 * CW) >> 1 : is_store ? 0 : warp / CW;  // group served
+  const int gi = is_producer ? (warp - 2 * CW) / PW : is_store ? 0 : warp / CW;  // group served
   uint64_t* staged = bars + CF::GROUPS * (2 * STAGES + 4);  // [2] a group's tile is in the shared staging area
   uint64_t* cfree = staged + 2;                             // [2] group g's staged tile has been read out
   int* mailbox = reinterpret_cast<int*>(cfree + 2);         // [2][8] tensor coordinates of the staged tile
@@ -327,7 +332,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_ws_dmma_kernel(const __
     // the consumers are allowed to fill the area), issues one tiled TMA reduce-add / store per tile and
     // releases the area once the copy engine has read it.
     reg_dec<CF::STORE_REGS>();
-    if (!tile_out || warp != 2 * CW + 4 || (tid & 31) != 0) return;
+    if (!tile_out || warp != 2 * CW + 2 * PW || (tid & 31) != 0) return;
     const uint64_t tmap = reinterpret_cast<uint64_t>(&p.tmap_ct);
     const uint32_t src = smem_u32(cstages);
     for (uint32_t t = 0;; ++t) {
