@@ -710,6 +710,7 @@ struct TcHostPipe {
   CopyPool* pool_in = nullptr;
   CopyPool* pool_out = nullptr;
   std::vector<cudaEvent_t> slab_done;  // kernel of slab i finished (recorded on its stream)
+  std::vector<cudaEvent_t> slab_in;    // inputs of slab i have arrived (page-locked callers: copies on their own stream)
 };
 
 static void host_pipe_destroy(TcHostPipe* h) {
@@ -731,6 +732,7 @@ static void host_pipe_destroy(TcHostPipe* h) {
     if (h->out_done[i]) cudaEventDestroy(h->out_done[i]);
   }
   for (cudaEvent_t e : h->slab_done) cudaEventDestroy(e);
+  for (cudaEvent_t e : h->slab_in) cudaEventDestroy(e);
   delete h->pool_in;
   delete h->pool_out;
   delete h;
@@ -966,8 +968,54 @@ static int execute_host_locked(tc_plan* p, void* C, const void* A, const void* B
       if (page_c) { drain.close(); drainer.join(); if (code == TC_OK) code = drain.status; }
       return code;
     };
+    // Page-locked callers: copies in, kernels and copies out each on a stream of their own, chained slab by slab
+    // through events.  The whole tensors are resident on the device, so the copies in never wait for a copy out and
+    // both directions of the link stay busy for the whole call.  (Measured on the sharded benchmark configuration,
+    // 65.6 GB per call: 0.81 s, the same as with two streams that each did copy in, kernel, copy out for every other
+    // slab -- 81 GB/s over both directions together is what the link of these hosts gives.)
+    if (!page_c && !page_a && !page_b) {
+      if (!h->out_stream) TC_CUDA_OK(cudaStreamCreateWithFlags(&h->out_stream, cudaStreamNonBlocking));
+      cudaStream_t s_in = h->stream[0], s_k = h->stream[1], s_out = h->out_stream;
+      auto event_of = [&](std::vector<cudaEvent_t>& pool, int k, cudaEvent_t* ev) {
+        while ((int)pool.size() <= k) {
+          cudaEvent_t e;
+          if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return TC_ERR_CUDA;
+          pool.push_back(e);
+        }
+        *ev = pool[k];
+        return TC_OK;
+      };
+      int k = 0;
+      for (int64_t v = 0; v < h->extent; v += h->slab, ++k) {
+        const int64_t n = std::min(h->slab, h->extent - v);
+        tc_plan* q = n == h->slab ? h->plan_slab : h->plan_tail;
+        auto range = [&](int t, size_t* off, size_t* bytes) {
+          *off = (size_t)(v * h->step[t]) * es;
+          *bytes = (size_t)((n - 1) * h->step[t] + h->rest[t]) * es;
+        };
+        size_t oc, bc, oa, ba, ob, bb;
+        range(0, &oc, &bc);
+        range(1, &oa, &ba);
+        range(2, &ob, &bb);
+        if (read_c) TC_CUDA_OK(cudaMemcpyAsync(dC + oc, hC + oc, bc, cudaMemcpyHostToDevice, s_in));
+        if (h->step[1]) TC_CUDA_OK(cudaMemcpyAsync(dA + oa, hA + oa, ba, cudaMemcpyHostToDevice, s_in));
+        if (h->step[2]) TC_CUDA_OK(cudaMemcpyAsync(dB + ob, hB + ob, bb, cudaMemcpyHostToDevice, s_in));
+        cudaEvent_t in_ev, k_ev;
+        st = event_of(h->slab_in, k, &in_ev);
+        if (st == TC_OK) st = event_of(h->slab_done, k, &k_ev);
+        if (st != TC_OK) return st;
+        TC_CUDA_OK(cudaEventRecord(in_ev, s_in));      // (the whole inputs went first on this stream)
+        TC_CUDA_OK(cudaStreamWaitEvent(s_k, in_ev, 0));
+        st = execute_impl(q, dC + oc, dA + (size_t)(v * h->view[1]) * es, dB + (size_t)(v * h->view[2]) * es, q->d_ws,
+                          q->ws_bytes, s_k);
+        if (st != TC_OK) return st;
+        TC_CUDA_OK(cudaEventRecord(k_ev, s_k));
+        TC_CUDA_OK(cudaStreamWaitEvent(s_out, k_ev, 0));
+        TC_CUDA_OK(cudaMemcpyAsync(hC + oc, dC + oc, bc, cudaMemcpyDeviceToHost, s_out));
+      }
+    }
     int i = 0;
-    for (int64_t v = 0; v < h->extent; v += h->slab, ++i) {
+    for (int64_t v = 0; (page_c || page_a || page_b) && v < h->extent; v += h->slab, ++i) {
       const int64_t n = std::min(h->slab, h->extent - v);
       tc_plan* q = n == h->slab ? h->plan_slab : h->plan_tail;
       cudaStream_t s = h->stream[i & 1];
@@ -1002,12 +1050,14 @@ static int execute_host_locked(tc_plan* p, void* C, const void* A, const void* B
     st = finish(TC_OK);
     if (st != TC_OK) return st;
   }
-  // Status words of the plans that ran: a wait that gave up leaves the output invalid.
+  TC_CUDA_OK(cudaStreamSynchronize(h->stream[1]));
+  if (h->out_stream) TC_CUDA_OK(cudaStreamSynchronize(h->out_stream));
+  TC_CUDA_OK(cudaStreamSynchronize(s0));
+  // Status words of the plans that ran (read once every kernel of the call has finished): a wait that gave up leaves
+  // the output invalid.
   int k = 0;
   for (tc_plan* q : used)
     if (q) { TC_CUDA_OK(cudaMemcpyAsync(h->h_status + k, q->d_status, sizeof(int), cudaMemcpyDeviceToHost, s0)); ++k; }
-  TC_CUDA_OK(cudaStreamSynchronize(h->stream[1]));
-  if (h->out_stream) TC_CUDA_OK(cudaStreamSynchronize(h->out_stream));
   TC_CUDA_OK(cudaStreamSynchronize(s0));
   for (int q = 0; q < k; ++q)
     if (h->h_status[q] != 0) {

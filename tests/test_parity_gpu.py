@@ -788,6 +788,33 @@ def test_host_pointer_execute_pipelined_slabs(pkg, orc, torch_cuda):
         plan.close()
 
 
+def test_host_pointer_execute_page_locked_slabs(pkg, orc, torch_cuda):
+    """Page-locked host buffers: copies in, kernels and copies out run on three streams chained by events, slab by slab."""
+    torch = torch_cuda
+    cases = [
+        "C [a,128,b,96,c,40,d,10] += sum(e,6) * A [a,e,b,d] * B [e,c];",
+        "C [a,128,b,96,c,40,d,11] -= sum(e,6) * A [d,e,a] * B [e,c,b];",
+        "C [a,128,b,96,c,40,d,9] = sum(e,6) * A [e,b,a] * B [c,e,d];",
+    ]
+    for expr in cases:
+        c0, a, b = orc.make_inputs(expr, 62)
+        ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+        pinned = [torch.from_numpy(x).pin_memory() for x in (c0, a, b)]
+        c, pa, pb = (t.numpy() for t in pinned)
+        plan = pkg.Plan(expr)
+        plan.execute_host(c, pa, pb)
+        assert orc.rel_error(c, ref) <= 1e-12, expr
+        if " = " not in expr:
+            ref2 = orc.contract(expr, ref.copy(), a, b, threads=orc.max_threads())
+            plan.execute_host(c, pa, pb)
+            assert orc.rel_error(c, ref2) <= 1e-12, expr
+        # a mixed call (page-locked output, pageable inputs) takes the staged path and gives the same answer
+        c2 = torch.from_numpy(c0).pin_memory().numpy()
+        plan.execute_host(c2, a, b)
+        assert orc.rel_error(c2, ref) <= 1e-12, expr
+        plan.close()
+
+
 def test_extents_overridden_at_run_time(pkg, orc, torch_cuda):
     """The sizes written in the expression are only representative, as in the reference drivers."""
     torch = torch_cuda
