@@ -280,6 +280,17 @@ def test_random_midsize_contractions_with_forced_kernels_and_options(pkg, orc, t
         for dt, kw in (("float64", kw64), ("float32", kw32)):
             err, d = _run(pkg, orc, torch_cuda, expr, dt, 700 + done, **kw)
             assert err <= TOL[dt], (expr, dt, kw, err, d["kernel"])
+        # the persistent fp32 kernel wherever the output's layout allows it (the plan is refused elsewhere), both ways
+        # of sending the tile; and the persistent fp64 kernel with K slices
+        kwt = {"path": pkg.PATH_TCGEN05, "tile": rng.choice([(96, 128), (128, 128)]), "variant": 2, "c_path": rng.choice([0, 1, 3])}
+        try:
+            err, d = _run(pkg, orc, torch_cuda, expr, "float32", 800 + done, **kwt)
+            assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, kwt, err, d["kernel"])
+        except pkg.TcError as e:
+            assert e.status == 3, (expr, kwt, e)
+        kws = {"tile": rng.choice([(128, 64), (128, 32), (64, 96)]), "variant": 3, "split_k": rng.choice([2, 3, 7])}
+        err, d = _run(pkg, orc, torch_cuda, expr, "float64", 900 + done, **kws)
+        assert err <= TOL["float64"], (expr, kws, err, d["kernel"], d["ksplit"])
         done += 1
 
 
