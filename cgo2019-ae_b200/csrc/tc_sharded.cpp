@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <sstream>
 #include <string>
 #include <vector>
@@ -37,20 +38,18 @@ constexpr int kNcclFloat32 = 7, kNcclFloat64 = 8, kNcclSum = 0;  // ncclDataType
 
 Nccl* nccl() {
   static Nccl n;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static std::once_flag once;
+  std::call_once(once, [] {
     void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
     if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
-    if (h) {
-      n.CommInitAll = reinterpret_cast<decltype(n.CommInitAll)>(dlsym(h, "ncclCommInitAll"));
-      n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
-      n.GroupStart = reinterpret_cast<decltype(n.GroupStart)>(dlsym(h, "ncclGroupStart"));
-      n.GroupEnd = reinterpret_cast<decltype(n.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
-      n.ReduceScatter = reinterpret_cast<decltype(n.ReduceScatter)>(dlsym(h, "ncclReduceScatter"));
-      n.ok = n.CommInitAll && n.CommDestroy && n.GroupStart && n.GroupEnd && n.ReduceScatter;
-    }
-  }
+    if (!h) return;
+    n.CommInitAll = reinterpret_cast<decltype(n.CommInitAll)>(dlsym(h, "ncclCommInitAll"));
+    n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+    n.GroupStart = reinterpret_cast<decltype(n.GroupStart)>(dlsym(h, "ncclGroupStart"));
+    n.GroupEnd = reinterpret_cast<decltype(n.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
+    n.ReduceScatter = reinterpret_cast<decltype(n.ReduceScatter)>(dlsym(h, "ncclReduceScatter"));
+    n.ok = n.CommInitAll && n.CommDestroy && n.GroupStart && n.GroupEnd && n.ReduceScatter;
+  });
   return &n;
 }
 
