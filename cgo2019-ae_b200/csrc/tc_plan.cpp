@@ -333,12 +333,12 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   loader(a.N, false, &c.vec_y, &c.kvec_y, &a.lanes_k_y);
   // An operand is a plain 2-D matrix (k fastest, then the flattened external index at a constant pitch)
   // when it has one fused contraction dimension of stride 1 and its external dimensions are contiguous
-  // among themselves: then a tile of the flattened class is a box, which TMA can fetch.  fp64 only.
+  // among themselves: then a tile of the flattened class is a box, which TMA can fetch (rows 16 bytes apart or more).
   auto affine = [&](const TcDims& ext, bool k_is_in) {
-    if (es != 8 || kd.n != 1 || (k_is_in ? kd.s_in[0] : kd.s_out[0]) != 1 || ext.n < 1) return false;
+    if (kd.n != 1 || (k_is_in ? kd.s_in[0] : kd.s_out[0]) != 1 || ext.n < 1) return false;
     for (int d = 1; d < ext.n; ++d)
       if (ext.s_in[d] != ext.s_in[d - 1] * (int64_t)ext.extent[d - 1]) return false;
-    return ext.s_in[0] % 2 == 0 && ext.s_in[0] >= (int64_t)kd.extent[0];
+    return ext.s_in[0] % (16 / es) == 0 && ext.s_in[0] >= (int64_t)kd.extent[0];
   };
   c.tma_x = affine(a.M, true);
   c.tma_y = affine(a.N, false);

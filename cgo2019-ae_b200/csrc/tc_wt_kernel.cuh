@@ -14,8 +14,10 @@
 //                         output still moves once.
 //   warps 8-15  SPLIT     turn the gathered fp32 stage into the hi and lo TF32 images the MMA reads (128-byte core
 //                         matrices, K-major); one 16-byte chunk of each operand per thread and group of eight k.
-//   warps 16-19 LOADERS   issue every cp.async of the stages (the three loader shapes of tc_kernels.cuh), running
-//                         ahead across tile boundaries by the depth of the ring.  Row offsets live in registers, the
+//   warps 16-19 LOADERS   issue every cp.async of the stages (the three loader shapes of tc_kernels.cuh) -- or, for an
+//                         operand that is a plain 2-D matrix with the contraction index fastest, one tiled TMA box
+//                         per stage from a single thread -- running ahead across tile boundaries by the depth of the
+//                         ring.  Row offsets live in registers, the
 //                         contraction offsets of a step in shared memory (a dependent global load per copy would
 //                         serialise the issue).
 //   warp 20     MMA       owns tensor memory; its first lane issues lo*hi, hi*lo, hi*hi for every group of eight k
@@ -48,13 +50,22 @@ template <int BM_, int MODEX_, int MODEY_>
 struct WtCfg {
   using T = float;
   static constexpr int BM = BM_, BN = 128, BK = 16;
-  static constexpr int MODEX = MODEX_, MODEY = MODEY_;  // 0 element copies, 1 16 bytes along the external index, 2 along k
+  // 0 element copies, 1 16 bytes along the external index, 2 16 bytes along k, 3 one tiled TMA box per stage
+  static constexpr int MODEX = MODEX_, MODEY = MODEY_;
   static constexpr bool VECX = MODEX == 1, VECY = MODEY == 1, KVX = MODEX == 2, KVY = MODEY == 2;
+  static constexpr bool TMAX = MODEX == 3, TMAY = MODEY == 3, ANY_TMA = TMAX || TMAY;
   static constexpr int ES = 4, VW = 4, LDKV = 16 + 4;
   static constexpr int THREADS = 128, WARPS = 4;  // the LOADER role, as the shared loaders see it
   static constexpr int LDX = BM + 4, LDY = BN + 4;
-  static constexpr int XIMG = KVX ? BM * LDKV : BK * LDX, YIMG = KVY ? BN * LDKV : BK * LDY;
+  // A TMA box lands as rows of 16 k (64 bytes) under the 64-byte swizzle, whose pattern repeats every 512 bytes:
+  // with a box in the stage, both images are rounded to 1024 bytes and the stages lead the shared memory.
+  static constexpr int XIMG_RAW = KVX ? BM * LDKV : TMAX ? BM * BK : BK * LDX;
+  static constexpr int YIMG_RAW = KVY ? BN * LDKV : TMAY ? BN * BK : BK * LDY;
+  static constexpr int XIMG = ANY_TMA ? (XIMG_RAW + 255) / 256 * 256 : XIMG_RAW;
+  static constexpr int YIMG = ANY_TMA ? (YIMG_RAW + 255) / 256 * 256 : YIMG_RAW;
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
+  static constexpr uint32_t TMA_BYTES = (TMAX ? BM * BK * 4 : 0) + (TMAY ? BN * BK * 4 : 0);
+  static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);  // the loaders' copies, and the announcement of the boxes
   static constexpr int UMMA_ELEMS = 2 * BK * (BM + BN);  // hi and lo images of both operands for one K step
   static constexpr int GROUPS = 1;                       // tiles a CTA works on at a time (launch arithmetic)
   // Six warpgroups: epilogue, epilogue, split, split, loaders, {MMA, fetch, store, a warp without work}.
@@ -80,7 +91,8 @@ struct WtCfg {
   static constexpr int KSTEPS_KEPT = 8;  // contractions of at most this many steps keep all their offsets in shared memory
   static constexpr int HEAD_BYTES = NBARS * 8 + 16 + KSTEPS_KEPT * 32 * 8;  // barriers, tensor-memory slot, contraction offsets
   static constexpr int SMEM_BYTES = 232448;
-  static_assert(HEAD_BYTES % 16 == 0, "images, tile buffers and stages start on 16 bytes");
+  static_assert(HEAD_BYTES % 16 == 0 && (STAGE_ELEMS * 4) % 16 == 0, "barriers, images and tile buffers start on 16 bytes");
+  static_assert(!ANY_TMA || (XIMG * 4) % 1024 == 0 && (YIMG * 4) % 1024 == 0, "boxes start on the swizzle's period");
   static_assert(BM % 32 == 0 && BM <= 128, "a warp reads BM / 2 columns, 16 at a time; an accumulator has 128 columns");
   // stages that fit beside `cbufs` tile buffers and `imgs` image sets
   static constexpr int stages_for(int cbufs, int imgs) {
@@ -115,7 +127,9 @@ struct WtSlots {
     for (int j = 0; j < PER; ++j) {
       int kk, el, off;
       bool valid = true;
-      if constexpr (MODE == 2) {
+      if constexpr (MODE == 3) {
+        kk = 0; el = 0; off = 0; valid = false;  // the box is fetched by one thread's TMA copy
+      } else if constexpr (MODE == 2) {
         const int f = ptid + 128 * j;
         el = f >> 2; kk = 4 * (f & 3); off = el * CF::LDKV + kk;
         valid = el < ROWS;
@@ -138,6 +152,7 @@ struct WtSlots {
   }
   // Operand offsets of this thread's rows in the tile that starts at flattened index `flat0` of class `d`.
   __device__ __forceinline__ void rows(const TcDims& d, uint32_t flat0, uint32_t limit) {
+    if constexpr (MODE == 3) return;
     const uint32_t e0 = d.extent[0];
     const uint32_t rest0 = flat0 / e0, b0 = flat0 - rest0 * e0;
 #pragma unroll
@@ -156,6 +171,7 @@ struct WtSlots {
   }
   // (a last step of at most eight k is split and multiplied as one group of eight: nobody reads its k >= 8)
   __device__ __forceinline__ void issue(float* img, const float* __restrict__ g, const int64_t* kr, uint32_t k0, uint32_t kend) const {
+    if constexpr (MODE == 3) return;
     const uint32_t sbase = smem_u32(img);
     const uint32_t kmax = kend - k0 <= 8u ? 8u : 16u;
     int64_t ko[PER];
@@ -200,7 +216,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   const bool whole = IMGS == 2;
   constexpr uint32_t SLOTS = 2;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw);
+  float* stages = reinterpret_cast<float*>(smem_raw);                        // [STAGES][XIMG + YIMG]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stages + STAGES * CF::STAGE_ELEMS);
   uint64_t* full = bars;                             // [STAGES] a stage's copies have landed
   uint64_t* empty = full + CF::MAX_STAGES;           // [STAGES] the split warps have read it
   uint64_t* img_full = empty + CF::MAX_STAGES;       // [SLOTS] hi / lo images of eight k are written
@@ -215,15 +232,16 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   // One image set: Y hi, Y lo (BN rows each), X hi, X lo (BM rows each), all for one K step.
   float* images = reinterpret_cast<float*>(kring + CF::KSTEPS_KEPT * 32);    // [IMGS][UMMA_ELEMS]
   float* ctiles = images + IMGS * CF::UMMA_ELEMS;                            // [CBUFS][CTILE_ELEMS]
-  float* stages = ctiles + CBUFS * CF::CTILE_ELEMS;                          // [STAGES][XIMG + YIMG]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, CF::THREADS); mbar_init(empty + s, CF::SPLIT_WARPS); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, CF::FULL_ARRIVALS); mbar_init(empty + s, CF::SPLIT_WARPS); }
     for (uint32_t h = 0; h < SLOTS; ++h) { mbar_init(img_full + h, CF::SPLIT_WARPS); mbar_init(img_free + h, 1); }
     for (int h = 0; h < 2; ++h) { mbar_init(acc_full + h, 1); mbar_init(acc_free + h, CF::EPI_WARPS); }
     for (int b = 0; b < CBUFS; ++b) { mbar_init(c_ready + b, 1); mbar_init(c_staged + b, CF::EPI_WARPS); mbar_init(c_free + b, 1); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if constexpr (CF::TMAX) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_x)) : "memory");
+    if constexpr (CF::TMAY) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_y)) : "memory");
   }
   if (warp == 20) {
     tmem_alloc(slot, CF::TMEM_COLS);
@@ -316,8 +334,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     const int ry = stid % BN, qy = stid / BN;
     const bool has_x = stid < 2 * BM;
     const int rx = has_x ? stid % BM : 0, qx = has_x ? stid / BM : 0;
-    auto chunk = [&](const float* img, int r, int kc, bool kv, int ld) {
-      if (kv) return *reinterpret_cast<const float4*>(img + r * CF::LDKV + 4 * kc);
+    auto chunk = [&](const float* img, int r, int kc, int mode, int ld) {
+      if (mode == 2) return *reinterpret_cast<const float4*>(img + r * CF::LDKV + 4 * kc);
+      // a TMA box: row r holds its 16 k in 16-byte chunks, chunk c at position c ^ ((r / 2) % 4) (64-byte swizzle)
+      if (mode == 3) return *reinterpret_cast<const float4*>(img + r * BK + 4 * (kc ^ ((r >> 1) & 3)));
       const float* src = img + (4 * kc) * ld + r;
       return make_float4(src[0], src[ld], src[2 * ld], src[3 * ld]);
     };
@@ -340,12 +360,12 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         float4 vy[2], vx[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          vy[h] = chunk(ys, ry, 2 * h + qy, CF::KVY, CF::LDY);
-          vx[h] = has_x ? chunk(xs, rx, 2 * h + qx, CF::KVX, CF::LDX) : make_float4(0.f, 0.f, 0.f, 0.f);
+          vy[h] = chunk(ys, ry, 2 * h + qy, CF::MODEY, CF::LDY);
+          vx[h] = has_x ? chunk(xs, rx, 2 * h + qx, CF::MODEX, CF::LDX) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        // the stage is in registers: the loaders may refill it
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty + s);
+        // The stage goes back to the loaders only after its values have been written into the images: a release
+        // straight after the loads, with the values still waiting in registers for an image slot, let the refill
+        // overtake the reads (wrong rows at the head of a TMA box whenever the MMA warp stalled at a segment boundary).
         if (whole) {
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
@@ -362,7 +382,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           }
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
-          if (lane == 0) mbar_arrive(img_full + sl);
+          if (lane == 0) { mbar_arrive(empty + s); mbar_arrive(img_full + sl); }
           continue;
         }
 #pragma unroll
@@ -380,7 +400,10 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           if (has_x) put(ub_hi, ub_lo, rx, 2 * (int)sl + qx, vx[h]);
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
-          if (lane == 0) mbar_arrive(img_full + sl);
+          if (lane == 0) {
+            if (h == nh - 1) mbar_arrive(empty + s);
+            mbar_arrive(img_full + sl);
+          }
         }
       }
     }
@@ -432,6 +455,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         const uint32_t k0 = kbeg + it * BK;
         float* xs = stages + s * CF::STAGE_ELEMS;
         float* ys = xs + CF::XIMG;
+        if constexpr (CF::ANY_TMA) {
+          if (ptid == 0) {
+            mbar_arrive_expect_tx(full + s, CF::TMA_BYTES);
+            if constexpr (CF::TMAX) tma_load_2d(xs, &p.tmap_x, (int)k0, (int)(tm * BM), full + s);
+            if constexpr (CF::TMAY) tma_load_2d(ys, &p.tmap_y, (int)k0, (int)(tn * BN), full + s);
+          }
+        }
         slots_x.issue(xs, X, kr, k0, kend);
         slots_y.issue(ys, Y, kr + 16, k0, kend);
         // tests only: one thread leaves one stage unannounced, so that the waits on it run out

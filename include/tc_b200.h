@@ -66,8 +66,8 @@ typedef struct tc_options {
                    /*   The persistent fp32 kernel stages its tile in shared memory either   */
                    /*   way: 0 and 3 send it as reduce-adds, 1 fetches the old values and    */
                    /*   stores the sums, 2 runs the tiles one CTA per tile instead.          */
-  int tma;         /* tiled TMA copies in the persistent fp64 kernel (operand tiles that are plain 2-D boxes;
-                      output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
+  int tma;         /* tiled TMA copies in the persistent kernels (operand tiles that are plain 2-D boxes, fp64 and
+                      fp32; fp64 output batches that are boxes of a rank-5 view of C): 0 = both, 1 = neither,
                       2 = operands only, 3 = output only, 4 = both but the output per warp, never per tile */
   int test_fault;  /* tests only, 0 in production.  1: the persistent fp64 kernel's producers leave one stage
                       unannounced and every device-side wait gives up after 2^14 polls instead of 2^24, so the

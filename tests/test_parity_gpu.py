@@ -517,6 +517,9 @@ WT = [
     ("C [a,384,b,256] = sum(c,2100) * A [c,a] * B [c,b];", (128, 128)),                        # segments with `=`
     ("C [a,2048,b,2048] += sum(c,512) * A [c,a] * B [c,b];", (128, 128)),     # long K, several tiles per CTA: one tile buffer
     ("C [a,1536,b,2048] -= sum(c,72) * A [a,c] * B [b,c];", (96, 128)),       # short K, several tiles per CTA: three buffers
+    ("C [a,320,b,8,c,50] += sum(d,52) * A [d,a] * B [d,b,c];", (128, 128)),    # boxes that run off the matrix in rows and in k
+    ("C [a,64,b,5,c,300] += sum(d,60) * A [d,a,b] * B [c,d];", (128, 128)),   # one operand in boxes, the other in 16-byte copies
+    ("C [a,320,b,300] = sum(d,28) * A [a,d] * B [d,b];", (128, 128)),         # ... and the other way round
 ]
 
 
@@ -537,6 +540,32 @@ def test_persistent_tcgen05_kernel(pkg, orc, torch_cuda, expr, tile):
     # (default: the tile leaves as bulk reduce-adds of the products)  The other way: old values fetched, sums stored.
     err, d = _run(pkg, orc, torch_cuda, expr, "float32", 27, c_path=1, **kw)
     assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, "fetch and store", err, d)
+    # operands that are plain matrices arrive as tiled TMA boxes by default; the same plan with per-thread copies
+    if d["tma_x"] or d["tma_y"]:
+        err, d = _run(pkg, orc, torch_cuda, expr, "float32", 28, tma=1, **kw)
+        assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, "no boxes", err, d)
+
+
+def test_persistent_tcgen05_kernel_boxes_on_long_contractions_repeatedly(pkg, orc, torch_cuda):
+    """Both operands in TMA boxes and three to five accumulation segments per tile: the shape on which a stage that was
+    handed back before its values had left the registers' owner came out wrong about once in four hundred stages.
+    Twenty executions per length, each checked."""
+    torch = torch_cuda
+    for k in (1028, 2112):
+        expr = "C [a,384,b,256] = sum(c,%d) * A [c,a] * B [c,b];" % k
+        c0, a, b = orc.make_inputs(expr, 41, "float32")
+        ref = orc.contract(expr, c0.copy(), a, b, threads=orc.max_threads())
+        plan = pkg.Plan(expr, pkg.F32, path=pkg.PATH_TCGEN05, tile=(128, 128), variant=2)
+        da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+        for rep in range(20):
+            dc = torch.from_numpy(c0).cuda()
+            plan.execute(dc, da, db)
+            torch.cuda.synchronize()
+            assert plan.status() == 0
+            assert orc.rel_error(dc.cpu().numpy(), ref) <= TOL["float32"], (expr, rep)
+        d = plan.describe()
+        assert d["tma_x"] and d["tma_y"] and d["kernel"] == "tf32wt_128x128", d
+        plan.close()
 
 
 def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):
