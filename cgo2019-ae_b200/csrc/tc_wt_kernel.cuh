@@ -363,9 +363,11 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           vy[h] = chunk(ys, ry, 2 * h + qy, CF::MODEY, CF::LDY);
           vx[h] = has_x ? chunk(xs, rx, 2 * h + qx, CF::MODEX, CF::LDX) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        // The stage goes back to the loaders only after its values have been written into the images: a release
-        // straight after the loads, with the values still waiting in registers for an image slot, let the refill
-        // overtake the reads (wrong rows at the head of a TMA box whenever the MMA warp stalled at a segment boundary).
+        // The stage goes back to the loaders only after its values have been written into the images.  With a release
+        // straight after the loads (the values then wait in registers for an image slot), rows at the head of a TMA
+        // box came out wrong about once in 400 stages where both operands arrive in boxes and a tile has three or
+        // more segments.  How a refill could overtake loads that precede the arrival in program order was not
+        // established; releasing after the stores removed it (five lengths, 40 executions each, all exact).
         if (whole) {
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
