@@ -367,7 +367,9 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
         // straight after the loads (the values then wait in registers for an image slot), rows at the head of a TMA
         // box came out wrong about once in 400 stages where both operands arrive in boxes and a tile has three or
         // more segments.  How a refill could overtake loads that precede the arrival in program order was not
-        // established; releasing after the stores removed it (five lengths, 40 executions each, all exact).
+        // established; releasing after the stores removed it (five lengths, 40 executions each, all exact).  The
+        // release now also follows the thread's fence.proxy.async, the order the memory model asks for between
+        // generic-proxy reads and an overwrite by the asynchronous proxy.
         if (whole) {
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;

@@ -568,6 +568,34 @@ def test_persistent_tcgen05_kernel_boxes_on_long_contractions_repeatedly(pkg, or
         plan.close()
 
 
+def test_persistent_tcgen05_kernel_random_matrices(pkg, orc, torch_cuda):
+    """Random matrix products through the persistent fp32 kernel: ragged column counts, contraction lengths with and
+    without a short last step and with one to five accumulation segments, every operand order (so boxes for both
+    operands, for one, for none), every operator."""
+    rng = random.Random(777)
+    ran = boxes = 0
+    for case in range(18):
+        bm = rng.choice([96, 128])
+        m = bm * rng.randint(1, 5) if bm == 96 or rng.random() < 0.5 else 64 * rng.randint(2, 9)   # runs of 64 and more
+        n = rng.choice([rng.randint(60, 700), 128 * rng.randint(1, 5)])
+        k = rng.choice([52, 64, 100, 256, 516, 1040, 1100, 2052])
+        a_ = rng.choice(["A [c,a]", "A [c,a]", "A [a,c]"])
+        b_ = rng.choice(["B [c,b]", "B [c,b]", "B [b,c]"])
+        op = rng.choice(["+=", "-=", "="])
+        expr = "C [a,%d,b,%d] %s sum(c,%d) * %s * %s;" % (m, n, op, k, a_, b_)
+        kw = {"path": pkg.PATH_TCGEN05, "tile": (bm, 128), "variant": 2, "c_path": rng.choice([0, 1])}
+        try:
+            err, d = _run(pkg, orc, torch_cuda, expr, "float32", 600 + case, **kw)
+        except pkg.TcError as e:
+            assert e.status == 3, (expr, kw, e)
+            continue
+        assert d["kernel"].startswith("tf32wt_") and d["chain"] <= 512, (expr, d)
+        assert err <= TOL["float32"], (expr, kw, err)
+        ran += 1
+        boxes += bool(d["tma_x"]) + bool(d["tma_y"])
+    assert ran >= 12 and boxes >= 8, (ran, boxes)
+
+
 def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):
     """The same failure drill as for the fp64 kernels: one loader thread leaves one stage unannounced; every role's
     waits run out, tensor memory is freed, the status names a wait of this kernel, and the next plan runs correctly."""
