@@ -117,6 +117,31 @@ static tc_inst_fn pick_inst(const TcKernelChoice& c) {
 
 static int mode_of(bool ext_vec, bool k_vec) { return ext_vec ? 1 : k_vec ? 2 : 0; }
 
+// The transposed operand matrix (fp32): dimension 0 = flattened external index (stride 1), dimension 1 = contraction
+// index at `pitch` elements; box = rows x 16, no swizzle, zero fill outside the tensor.
+static bool encode_operand_map_ext(TcTensorMap* out, const void* base, uint64_t ext_extent, uint64_t k_extent,
+                                   uint64_t pitch, uint32_t rows) {
+  typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static encode_fn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<encode_fn>(f);
+  }();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (pitch * 4) % 16 != 0 || rows > 256 || rows % 4 != 0) return false;
+  const cuuint64_t dims[2] = {ext_extent, k_extent};
+  const cuuint64_t strides[1] = {pitch * 4};
+  const cuuint32_t box[2] = {rows, (cuuint32_t)TC_BK};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Tiled TMA descriptor of an operand seen as a 2-D matrix of `es`-byte elements: dimension 0 = contraction index
 // (stride 1), dimension 1 = flattened external index at `pitch` elements; box = 16 x rows, swizzled over the box
 // row (128 bytes for fp64, 64 for fp32), zero fill outside the tensor.  cuTensorMapEncodeTiled is resolved through the runtime (no link against libcuda).
@@ -207,7 +232,9 @@ static int kernels_prepare_one(const TcKernelChoice& c) {
   if (!fn) return TC_ERR_UNSUPPORTED;
   const int mx = mode_of(c.vec_x, c.kvec_x), my = mode_of(c.vec_y, c.kvec_y);
   const bool ws = tc_kernel_is_persistent(c) && (c.math == TC_MATH_DMMA || tc_kernel_is_tmem_persistent(c));
-  const int xs[3] = {0, mx, (ws && c.tma_x) ? 3 : 0}, ys[3] = {0, my, (ws && c.tma_y) ? 3 : 0};
+  const bool wt = tc_kernel_is_tmem_persistent(c);
+  const int xs[4] = {0, mx, (ws && c.tma_x) ? 3 : 0, (wt && c.tma_xe) ? 4 : 0};
+  const int ys[4] = {0, my, (ws && c.tma_y) ? 3 : 0, (wt && c.tma_ye) ? 4 : 0};
   for (int vx : xs)
     for (int vy : ys) {
       const int st = fn(vx, vy, nullptr, nullptr, nullptr, nullptr, nullptr, TC_INST_PREPARE, nullptr, nullptr);
@@ -272,13 +299,16 @@ int tc_launch_contraction(const tc_plan& p, const TcKernelArgs& args, void* C, c
       a.k_chunk = (uint32_t)(((steps + want - 1) / want) * TC_BK);
     }
   } else if (tc_kernel_is_tmem_persistent(c)) {
-    // Operands that are plain 2-D matrices arrive as one tiled TMA box per stage.  A box always moves sixteen k:
-    // contraction lengths that would leave more than a fifth of the boxes' k outside the tensor keep the per-thread
-    // copies, which fetch only what exists (K = 24: boxes measured 2-3 % slower; long contractions a fifth faster).
+    // Operands that are plain 2-D matrices -- contraction index fastest, or the flattened external index fastest and
+    // the contraction index at a constant pitch -- arrive as one tiled TMA box per stage.  A box always holds sixteen
+    // k: contraction lengths that would leave more than a fifth of the boxes' k outside the tensor keep the
+    // per-thread copies (K = 24: boxes of either kind measured 2-3 % slower; long contractions a fifth faster).
     const bool boxes_pay = (uint64_t)a.Kflat * 5 >= (uint64_t)((a.Kflat + TC_BK - 1) / TC_BK * TC_BK) * 4;
     if (p.opt.tma != 1 && p.opt.tma != 3 && boxes_pay) {
       if (c.tma_x && encode_operand_map(&a.tmap_x, X, a.Kflat, a.Mflat, (uint64_t)a.M.s_in[0], (uint32_t)a.bm, 4)) vx = 3;
       if (c.tma_y && encode_operand_map(&a.tmap_y, Y, a.Kflat, a.Nflat, (uint64_t)a.N.s_in[0], (uint32_t)a.bn, 4)) vy = 3;
+      if (c.tma_xe && encode_operand_map_ext(&a.tmap_x, X, a.Mflat, a.Kflat, (uint64_t)p.kdims.s_in[0], (uint32_t)a.bm)) vx = 4;
+      if (c.tma_ye && encode_operand_map_ext(&a.tmap_y, Y, a.Nflat, a.Kflat, (uint64_t)p.kdims.s_out[0], (uint32_t)a.bn)) vy = 4;
     }
     // How the kernel's shared memory is carved.  Short contractions are bound by the output stream: tile buffers,
     // so that enough of C is in flight.  Long ones are bound by the MMAs: one tile buffer, a second image set and

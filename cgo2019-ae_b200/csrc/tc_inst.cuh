@@ -100,14 +100,15 @@ int run_wt_variant(const TcKernelArgs* a, void* C, const void* X, const void* Y,
 }
 }  // namespace tck
 
-// Persistent fp32 kernel: loader modes 0 element, 1 external vector, 2 contraction vector, 3 tiled TMA box per operand.
+// Persistent fp32 kernel: loader modes 0 element, 1 external vector, 2 contraction vector, 3 / 4 one tiled TMA box per
+// stage (contraction index fastest / external index fastest).
 #define TC_WT_CASE(MX, MY, BM) \
   if (vx == MX && vy == MY) return tck::run_wt_variant<tck::WtCfg<BM, MX, MY>>(a, C, X, Y, s, mode, threads, smem);
-#define TC_WT_ROW(MX, BM) TC_WT_CASE(MX, 0, BM) TC_WT_CASE(MX, 1, BM) TC_WT_CASE(MX, 2, BM) TC_WT_CASE(MX, 3, BM)
+#define TC_WT_ROW(MX, BM) TC_WT_CASE(MX, 0, BM) TC_WT_CASE(MX, 1, BM) TC_WT_CASE(MX, 2, BM) TC_WT_CASE(MX, 3, BM) TC_WT_CASE(MX, 4, BM)
 #define TC_DEFINE_WT_INST(NAME, BM)                                                                          \
   extern "C" int NAME(int vx, int vy, const TcKernelArgs* a, void* C, const void* X, const void* Y,         \
                       cudaStream_t s, int mode, int* threads, int* smem) {                                  \
-    TC_WT_ROW(0, BM) TC_WT_ROW(1, BM) TC_WT_ROW(2, BM) TC_WT_ROW(3, BM)                                     \
+    TC_WT_ROW(0, BM) TC_WT_ROW(1, BM) TC_WT_ROW(2, BM) TC_WT_ROW(3, BM) TC_WT_ROW(4, BM)                    \
     return TC_ERR_INVALID_ARG;                                                                              \
   }
 

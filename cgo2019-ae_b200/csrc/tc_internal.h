@@ -123,6 +123,7 @@ struct TcKernelChoice {
   bool vec_x, vec_y;    // 16-byte loads along the external index of X / Y are legal
   bool kvec_x, kvec_y;  // 16-byte loads along the contraction index of X / Y are legal
   bool tma_x, tma_y;    // X / Y is a plain 2-D (k fastest, flattened external) matrix: tiles are TMA boxes
+  bool tma_xe, tma_ye;  // ... with the flattened external index fastest and k at a constant pitch (fp32 persistent kernel)
   bool tma_c;           // a warp's 8-row output batch is a box of a rank-5 tensor over C
   bool tma_ct;          // ... and so is a whole bm x bn tile
 };

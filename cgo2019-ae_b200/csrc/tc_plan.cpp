@@ -342,6 +342,20 @@ int tc_plan_build(tc_plan* p, std::string* why) {
   };
   c.tma_x = affine(a.M, true);
   c.tma_y = affine(a.N, false);
+  // The transposed case: the whole external class is one contiguous run and the single contraction dimension lies
+  // at a constant pitch (rows of the box are then k, 16 bytes apart or more).
+  auto affine_ext = [&](const TcDims& ext, bool k_is_in) {
+    if (kd.n != 1 || ext.n < 1 || ext.s_in[0] != 1) return false;
+    int64_t run = 1;
+    for (int d = 0; d < ext.n; ++d) {
+      if (ext.s_in[d] != run) return false;
+      run *= (int64_t)ext.extent[d];
+    }
+    const int64_t pitch = k_is_in ? kd.s_in[0] : kd.s_out[0];
+    return pitch % (16 / es) == 0 && pitch >= run;
+  };
+  c.tma_xe = es == 4 && affine_ext(a.M, true);
+  c.tma_ye = es == 4 && affine_ext(a.N, false);
 
   // Contiguous output elements per thread access.
   a.vec_c = 1;
@@ -598,7 +612,8 @@ std::string tc_plan_to_json(const tc_plan& p) {
       << ",\"k_chunk\":" << a.k_chunk << ",\"passes\":" << p.passes << ",\"chain\":" << chain << ",\"vec_x\":" << (p.choice.vec_x ? "true" : "false")
       << ",\"vec_y\":" << (p.choice.vec_y ? "true" : "false") << ",\"kvec_x\":" << (p.choice.kvec_x ? "true" : "false")
       << ",\"kvec_y\":" << (p.choice.kvec_y ? "true" : "false") << ",\"tma_x\":" << (p.choice.tma_x ? "true" : "false")
-      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false") << ",\"tma_ct\":" << (p.choice.tma_ct ? "true" : "false")
+      << ",\"tma_y\":" << (p.choice.tma_y ? "true" : "false") << ",\"tma_xe\":" << (p.choice.tma_xe ? "true" : "false")
+      << ",\"tma_ye\":" << (p.choice.tma_ye ? "true" : "false") << ",\"tma_c\":" << (p.choice.tma_c ? "true" : "false") << ",\"tma_ct\":" << (p.choice.tma_ct ? "true" : "false")
       << ",\"lanes_k_x\":" << a.lanes_k_x
       << ",\"lanes_k_y\":" << a.lanes_k_y << ",\"vec_c\":" << a.vec_c << ",\"epi_run\":" << a.epi_run << ",\"epi_n_span\":" << a.epi_n_span << ",\"beta\":" << a.beta
       << ",\"alpha\":" << a.alpha << ",\"workspace_bytes\":" << p.ws_bytes << ",\"launches\":" << p.launches

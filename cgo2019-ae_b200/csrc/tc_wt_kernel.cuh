@@ -50,21 +50,23 @@ template <int BM_, int MODEX_, int MODEY_>
 struct WtCfg {
   using T = float;
   static constexpr int BM = BM_, BN = 128, BK = 16;
-  // 0 element copies, 1 16 bytes along the external index, 2 16 bytes along k, 3 one tiled TMA box per stage
+  // 0 element copies, 1 16 bytes along the external index, 2 16 bytes along k, 3 one tiled TMA box per stage (rows of
+  // 16 k, 64-byte swizzle), 4 the same for an operand whose external index is the fastest (16 rows of k, dense)
   static constexpr int MODEX = MODEX_, MODEY = MODEY_;
   static constexpr bool VECX = MODEX == 1, VECY = MODEY == 1, KVX = MODEX == 2, KVY = MODEY == 2;
-  static constexpr bool TMAX = MODEX == 3, TMAY = MODEY == 3, ANY_TMA = TMAX || TMAY;
+  static constexpr bool TMAX = MODEX == 3, TMAY = MODEY == 3, TMAXE = MODEX == 4, TMAYE = MODEY == 4;
+  static constexpr bool ANY_TMA = TMAX || TMAY || TMAXE || TMAYE;
   static constexpr int ES = 4, VW = 4, LDKV = 16 + 4;
   static constexpr int THREADS = 128, WARPS = 4;  // the LOADER role, as the shared loaders see it
-  static constexpr int LDX = BM + 4, LDY = BN + 4;
+  static constexpr int LDX = TMAXE ? BM : BM + 4, LDY = TMAYE ? BN : BN + 4;  // a box is dense
   // A TMA box lands as rows of 16 k (64 bytes) under the 64-byte swizzle, whose pattern repeats every 512 bytes:
   // with a box in the stage, both images are rounded to 1024 bytes and the stages lead the shared memory.
-  static constexpr int XIMG_RAW = KVX ? BM * LDKV : TMAX ? BM * BK : BK * LDX;
+  static constexpr int XIMG_RAW = KVX ? BM * LDKV : TMAX ? BM * BK : BK * LDX;  // (mode 4: BK rows of BM)
   static constexpr int YIMG_RAW = KVY ? BN * LDKV : TMAY ? BN * BK : BK * LDY;
   static constexpr int XIMG = ANY_TMA ? (XIMG_RAW + 255) / 256 * 256 : XIMG_RAW;
   static constexpr int YIMG = ANY_TMA ? (YIMG_RAW + 255) / 256 * 256 : YIMG_RAW;
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
-  static constexpr uint32_t TMA_BYTES = (TMAX ? BM * BK * 4 : 0) + (TMAY ? BN * BK * 4 : 0);
+  static constexpr uint32_t TMA_BYTES = (TMAX || TMAXE ? BM * BK * 4 : 0) + (TMAY || TMAYE ? BN * BK * 4 : 0);
   static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);  // the loaders' copies, and the announcement of the boxes
   static constexpr int UMMA_ELEMS = 2 * BK * (BM + BN);  // hi and lo images of both operands for one K step
   static constexpr int GROUPS = 1;                       // tiles a CTA works on at a time (launch arithmetic)
@@ -127,7 +129,7 @@ struct WtSlots {
     for (int j = 0; j < PER; ++j) {
       int kk, el, off;
       bool valid = true;
-      if constexpr (MODE == 3) {
+      if constexpr (MODE >= 3) {
         kk = 0; el = 0; off = 0; valid = false;  // the box is fetched by one thread's TMA copy
       } else if constexpr (MODE == 2) {
         const int f = ptid + 128 * j;
@@ -152,7 +154,7 @@ struct WtSlots {
   }
   // Operand offsets of this thread's rows in the tile that starts at flattened index `flat0` of class `d`.
   __device__ __forceinline__ void rows(const TcDims& d, uint32_t flat0, uint32_t limit) {
-    if constexpr (MODE == 3) return;
+    if constexpr (MODE >= 3) return;
     const uint32_t e0 = d.extent[0];
     const uint32_t rest0 = flat0 / e0, b0 = flat0 - rest0 * e0;
 #pragma unroll
@@ -171,7 +173,7 @@ struct WtSlots {
   }
   // (a last step of at most eight k is split and multiplied as one group of eight: nobody reads its k >= 8)
   __device__ __forceinline__ void issue(float* img, const float* __restrict__ g, const int64_t* kr, uint32_t k0, uint32_t kend) const {
-    if constexpr (MODE == 3) return;
+    if constexpr (MODE >= 3) return;
     const uint32_t sbase = smem_u32(img);
     const uint32_t kmax = kend - k0 <= 8u ? 8u : 16u;
     int64_t ko[PER];
@@ -240,8 +242,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     for (int h = 0; h < 2; ++h) { mbar_init(acc_full + h, 1); mbar_init(acc_free + h, CF::EPI_WARPS); }
     for (int b = 0; b < CBUFS; ++b) { mbar_init(c_ready + b, 1); mbar_init(c_staged + b, CF::EPI_WARPS); mbar_init(c_free + b, 1); }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    if constexpr (CF::TMAX) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_x)) : "memory");
-    if constexpr (CF::TMAY) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_y)) : "memory");
+    if constexpr (CF::TMAX || CF::TMAXE) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_x)) : "memory");
+    if constexpr (CF::TMAY || CF::TMAYE) asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&p.tmap_y)) : "memory");
   }
   if (warp == 20) {
     tmem_alloc(slot, CF::TMEM_COLS);
@@ -464,6 +466,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
             mbar_arrive_expect_tx(full + s, CF::TMA_BYTES);
             if constexpr (CF::TMAX) tma_load_2d(xs, &p.tmap_x, (int)k0, (int)(tm * BM), full + s);
             if constexpr (CF::TMAY) tma_load_2d(ys, &p.tmap_y, (int)k0, (int)(tn * BN), full + s);
+            if constexpr (CF::TMAXE) tma_load_2d(xs, &p.tmap_x, (int)(tm * BM), (int)k0, full + s);
+            if constexpr (CF::TMAYE) tma_load_2d(ys, &p.tmap_y, (int)(tn * BN), (int)k0, full + s);
           }
         }
         slots_x.issue(xs, X, kr, k0, kend);

@@ -541,7 +541,7 @@ def test_persistent_tcgen05_kernel(pkg, orc, torch_cuda, expr, tile):
     err, d = _run(pkg, orc, torch_cuda, expr, "float32", 27, c_path=1, **kw)
     assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, "fetch and store", err, d)
     # operands that are plain matrices arrive as tiled TMA boxes by default; the same plan with per-thread copies
-    if d["tma_x"] or d["tma_y"]:
+    if d["tma_x"] or d["tma_y"] or d["tma_xe"] or d["tma_ye"]:
         err, d = _run(pkg, orc, torch_cuda, expr, "float32", 28, tma=1, **kw)
         assert d["kernel"].startswith("tf32wt_") and err <= TOL["float32"], (expr, "no boxes", err, d)
 
@@ -592,8 +592,8 @@ def test_persistent_tcgen05_kernel_random_matrices(pkg, orc, torch_cuda):
         assert d["kernel"].startswith("tf32wt_") and d["chain"] <= 512, (expr, d)
         assert err <= TOL["float32"], (expr, kw, err)
         ran += 1
-        boxes += bool(d["tma_x"]) + bool(d["tma_y"])
-    assert ran >= 12 and boxes >= 8, (ran, boxes)
+        boxes += bool(d["tma_x"] or d["tma_xe"]) + bool(d["tma_y"] or d["tma_ye"])
+    assert ran >= 12 and boxes >= 16, (ran, boxes)
 
 
 def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):

@@ -246,3 +246,23 @@ def test_no_default_fp32_plan_runs_a_tensor_core_chain_longer_than_512(pkg):
     # the caller may override the rule explicitly, and FFMA never needs it
     assert _plan(pkg, "C [a,4096,b,8192] += sum(c,8192) * A [c,a] * B [c,b];", "float32", split_k=1).describe()["chain"] == 8192
     assert _plan(pkg, "C [a,4096,b,8192] += sum(c,8192) * A [c,a] * B [c,b];", "float32", path=pkg.PATH_FFMA).describe()["passes"] == 1
+
+
+def test_operands_that_are_matrices_are_marked_as_boxes(pkg):
+    """An operand is a TMA box tensor when it is a plain matrix: contraction index fastest with the externals
+    contiguous among themselves (tma_x / tma_y, fp64 and fp32), or the external class one contiguous run with the
+    contraction index at a constant pitch (tma_xe / tma_ye, fp32).  Rows must be 16 bytes apart or more."""
+    def flags(expr, dt):
+        d = pkg.Plan(expr, dt).describe()
+        return tuple(bool(d[k]) for k in ("tma_x", "tma_y", "tma_xe", "tma_ye"))
+    assert flags("C [a,512,b,512] += sum(c,256) * A [c,a] * B [c,b];", pkg.F32) == (True, True, False, False)
+    assert flags("C [a,512,b,512] += sum(c,256) * A [a,c] * B [b,c];", pkg.F32) == (False, False, True, True)
+    assert flags("C [a,512,b,512] += sum(c,256) * A [c,a] * B [b,c];", pkg.F32) == (True, False, False, True)
+    assert flags("C [a,512,b,512] += sum(c,256) * A [c,a] * B [b,c];", pkg.F64) == (True, False, False, False)
+    # rows of 250 floats are not 16 bytes apart; 250 doubles are
+    assert flags("C [a,512,b,512] += sum(c,250) * A [c,a] * B [c,b];", pkg.F32) == (False, False, False, False)
+    assert flags("C [a,512,b,512] += sum(c,250) * A [c,a] * B [c,b];", pkg.F64) == (True, True, False, False)
+    # fused externals stay a box while they are contiguous among themselves; a permuted pair is not
+    assert flags("C [a,64,b,8,c,512] += sum(d,64) * A [d,a,b] * B [d,c];", pkg.F32)[0]
+    assert not flags("C [a,64,b,8,c,512] += sum(d,64) * A [d,b,a] * B [d,c];", pkg.F32)[0]
+    assert flags("C [a,64,b,8,c,512] += sum(d,64) * A [a,b,d] * B [d,c];", pkg.F32)[2]
