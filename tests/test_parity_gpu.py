@@ -596,6 +596,33 @@ def test_persistent_tcgen05_kernel_random_matrices(pkg, orc, torch_cuda):
     assert ran >= 12 and boxes >= 16, (ran, boxes)
 
 
+def test_persistent_tcgen05_kernel_on_blocks_of_larger_matrices(pkg, orc, torch_cuda):
+    """Operands and output that are blocks of larger matrices (leading dimensions beyond the extents, shifted bases):
+    the boxes' tensor maps carry the pitch, and what lies beside the block -- more k, more rows -- is not read."""
+    torch = torch_cuda
+    full = "C [a,512,b,640] += sum(c,300) * A [c,a] * B [b,c];"
+    c0, a, b = orc.make_inputs(full, 51, "float32")
+    sub = "C [a,512,b,384] += sum(c,260) * A [c,a] * B [b,c];"       # b in [64, 448), c in [32, 292)
+    oc, oa, ob = 512 * 64, 32, 64 + 640 * 32
+    ref = c0.copy()
+    orc.contract(sub, ref[oc:], a[oa:], b[ob:], threads=orc.max_threads(), strides={0: [1, 512], 1: [1, 300], 2: [1, 640]})
+    assert (ref != c0).any() and (ref[:oc] == c0[:oc]).all()
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    for tma in (0, 1):
+        plan = pkg.Plan(sub, pkg.F32, path=pkg.PATH_TCGEN05, tile=(128, 128), variant=2, tma=tma)
+        plan.set_strides(pkg.TENSOR_LEFT, [1, 300]).set_strides(pkg.TENSOR_RIGHT, [1, 640])
+        d = plan.describe()
+        assert d["kernel"] == "tf32wt_128x128" and d["tma_x"] and d["tma_ye"], d
+        dc = torch.from_numpy(c0).cuda()
+        plan.execute(dc[oc:], da[oa:], db[ob:])
+        torch.cuda.synchronize()
+        assert plan.status() == 0
+        got = dc.cpu().numpy()
+        assert orc.rel_error(got, ref) <= TOL["float32"], tma
+        assert (got[:oc] == c0[:oc]).all() and (got[oc + 512 * 384:] == c0[oc + 512 * 384:]).all()
+        plan.close()
+
+
 def test_persistent_tcgen05_kernel_wait_that_gives_up(pkg, orc, torch_cuda):
     """The same failure drill as for the fp64 kernels: one loader thread leaves one stage unannounced; every role's
     waits run out, tensor memory is freed, the status names a wait of this kernel, and the next plan runs correctly."""
