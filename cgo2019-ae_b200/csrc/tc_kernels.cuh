@@ -106,6 +106,22 @@ __device__ __forceinline__ void tc05_mma_tf32(uint32_t d_tmem, uint64_t adesc, u
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
       : "memory");
 }
+// The same with A in tensor memory: row i of A in lane i, one column per k (32-bit elements), from column `a_tmem` on.
+__device__ __forceinline__ void tc05_mma_tf32_ta(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+// Four consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane id) from registers; asynchronous
+// until tc05_wait_st().
+__device__ __forceinline__ void tc05_st4(uint32_t taddr, const float4& v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(taddr), "r"(__float_as_uint(v.x)),
+               "r"(__float_as_uint(v.y)), "r"(__float_as_uint(v.z)), "r"(__float_as_uint(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void tc05_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 // 16 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane id) into registers.  The load is
 // asynchronous: nothing may touch the destination registers (not even a move) before tc05_wait_ld(), so the
 // values land directly in the caller's floats.

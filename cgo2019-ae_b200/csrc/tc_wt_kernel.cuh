@@ -1,8 +1,8 @@
 // Persistent, warp-specialised fp32 contraction kernel for sm_100a: three TF32 products per fp32 product on
-// tcgen05.mma, two accumulators in tensor memory, the output tile staged in shared memory.
+// tcgen05.mma, two accumulators and the A operand in tensor memory, the output tile staged in shared memory.
 //
-// Same tiling, address scheme, operand images, split (v = hi + lo) and MMA descriptors as the one-CTA-per-tile
-// tcgen05 path of tc_contract_kernel (tc_kernels.cuh); what changes is WHO does what and WHEN.  One CTA per SM lives
+// Same tiling, address scheme, split (v = hi + lo) and X images as the one-CTA-per-tile tcgen05 path of
+// tc_contract_kernel (tc_kernels.cuh); what changes is WHO does what and WHEN, and where the A operand lives.  One CTA per SM lives
 // for the whole contraction and walks a strided list of BM x 128 output tiles; its warps have fixed roles that meet
 // only through mbarriers in shared memory:
 //
@@ -12,8 +12,11 @@
 //                         alternate between the two accumulators and are added into the buffer one after another in
 //                         round-to-nearest fp32, so no tensor-core accumulation chain exceeds 512 products and the
 //                         output still moves once.
-//   warps 8-15  SPLIT     turn the gathered fp32 stage into the hi and lo TF32 images the MMA reads (128-byte core
-//                         matrices, K-major); one 16-byte chunk of each operand per thread and group of eight k.
+//   warps 8-15  SPLIT     turn the gathered fp32 stage into the hi and lo TF32 values the MMA reads; one 16-byte chunk
+//                         of each operand per thread and group of eight k.  X (the MMA's B operand) goes into
+//                         images in shared memory (128-byte core matrices, K-major); Y (its A operand) goes
+//                         straight into tensor memory with tcgen05.st -- row n in lane n, one column per k -- so
+//                         its images are neither written to shared memory nor read from it three times.
 //   warps 16-19 LOADERS   issue every cp.async of the stages (the three loader shapes of tc_kernels.cuh) -- or, for an
 //                         operand that is a plain 2-D matrix with the contraction index fastest, one tiled TMA box
 //                         per stage from a single thread -- running ahead across tile boundaries by the depth of the
@@ -68,7 +71,7 @@ struct WtCfg {
   static constexpr int STAGE_ELEMS = XIMG + YIMG;
   static constexpr uint32_t TMA_BYTES = (TMAX || TMAXE ? BM * BK * 4 : 0) + (TMAY || TMAYE ? BN * BK * 4 : 0);
   static constexpr int FULL_ARRIVALS = THREADS + (ANY_TMA ? 1 : 0);  // the loaders' copies, and the announcement of the boxes
-  static constexpr int UMMA_ELEMS = 2 * BK * (BM + BN);  // hi and lo images of both operands for one K step
+  static constexpr int UMMA_ELEMS = 2 * BK * BM;         // hi and lo images of X for one K step (those of Y live in tensor memory)
   static constexpr int GROUPS = 1;                       // tiles a CTA works on at a time (launch arithmetic)
   // Six warpgroups: epilogue, epilogue, split, split, loaders, {MMA, fetch, store, a warp without work}.
   static constexpr int CTA_THREADS = 24 * 32;
@@ -82,7 +85,9 @@ struct WtCfg {
                 "register increases must be covered by the decreases");
   static_assert(CTA_THREADS * LAUNCH_REGS <= 65536 && (65536 / CTA_THREADS) / 8 * 8 == LAUNCH_REGS, "launch registers");
   static constexpr int SEG_STEPS = 32;                   // K steps per accumulation chain: 512 products
-  static constexpr int TMEM_COLS = 256;                  // two accumulators of 128 columns
+  // Tensor memory: two accumulators of 128 columns, then the hi / lo values of Y (the MMA's A operand: row n in lane
+  // n, one column per k): per image slot 2 groups of 8 k x (8 hi + 8 lo) columns.
+  static constexpr int TMEM_COLS = 512, A_COLS = 256, A_SLOT_COLS = 32;
   // output tile buffers: room for the padded layout (pitch E0 + 4 only where E0 >= 64: at most BM / 64 runs)
   static constexpr int CTILE_ELEMS = BN * (BM + 4 * (BM / 64));
   // Shared memory is carved at run time (args.out_bufs tile buffers, args.img_sets image sets, args.ring_stages
@@ -231,7 +236,7 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
   uint64_t* c_free = c_staged + CF::MAX_CBUFS;       // [CBUFS] ... and has been read out: the buffer is free
   uint32_t* slot = reinterpret_cast<uint32_t*>(bars + CF::NBARS);
   int64_t* kring = reinterpret_cast<int64_t*>(slot + 4);                     // [steps][X 16 | Y 16] contraction offsets
-  // One image set: Y hi, Y lo (BN rows each), X hi, X lo (BM rows each), all for one K step.
+  // One image set: X hi, X lo (BM rows each) for one K step.
   float* images = reinterpret_cast<float*>(kring + CF::KSTEPS_KEPT * 32);    // [IMGS][UMMA_ELEMS]
   float* ctiles = images + IMGS * CF::UMMA_ELEMS;                            // [CBUFS][CTILE_ELEMS]
 
@@ -343,6 +348,17 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
       const float* src = img + (4 * kc) * ld + r;
       return make_float4(src[0], src[ld], src[2 * ld], src[3 * ld]);
     };
+    // Y: this thread's lane of tensor memory is its row (warp w holds rows 32 (w % 4) .. + 31), its columns the four k
+    // of its chunk, hi values in the group's first eight columns, lo values in the next eight.
+    const uint32_t ylane = tmem + ((uint32_t)(32 * (warp & 3)) << 16) + CF::A_COLS + 4u * (uint32_t)qy;
+    auto put_y = [&](uint32_t set, uint32_t pos, const float4& v4) {
+      float4 hi, lo;
+      split_tf32_bits(v4.x, hi.x, lo.x); split_tf32_bits(v4.y, hi.y, lo.y);
+      split_tf32_bits(v4.z, hi.z, lo.z); split_tf32_bits(v4.w, hi.w, lo.w);
+      const uint32_t col = ylane + set * CF::A_SLOT_COLS + pos * 16u;
+      tc05_st4(col, hi);
+      tc05_st4(col + 8u, lo);
+    };
     auto put = [&](float* hi_img, float* lo_img, int r, int kc, const float4& v4) {
       float4 hi, lo;
       split_tf32_bits(v4.x, hi.x, lo.x); split_tf32_bits(v4.y, hi.y, lo.y);
@@ -376,16 +392,17 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
           if (use > 0 && !mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit)) return;
-          float* ua_hi = images + sl * CF::UMMA_ELEMS;
-          float* ua_lo = ua_hi + BK * BN;
-          float* ub_hi = ua_lo + BK * BN;
+          float* ub_hi = images + sl * CF::UMMA_ELEMS;
           float* ub_lo = ub_hi + BK * BM;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             if (h >= nh) break;
-            put(ua_hi, ua_lo, ry, 2 * h + qy, vy[h]);
+            put_y(sl, (uint32_t)h, vy[h]);
             if (has_x) put(ub_hi, ub_lo, rx, 2 * h + qx, vx[h]);
           }
+          __syncwarp();
+          tc05_wait_st();
+          tc05_fence_before();
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
           if (lane == 0) { mbar_arrive(empty + s); mbar_arrive(img_full + sl); }
@@ -398,12 +415,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           const uint32_t sl = u % SLOTS, use = u / SLOTS;
           ++u;
           if (use > 0 && !mbar_wait(img_free + sl, (use - 1) & 1u, p.status, 13, limit)) return;
-          float* ua_hi = images;
-          float* ua_lo = ua_hi + BK * BN;
-          float* ub_hi = ua_lo + BK * BN;
+          float* ub_hi = images;
           float* ub_lo = ub_hi + BK * BM;
-          put(ua_hi, ua_lo, ry, 2 * (int)sl + qy, vy[h]);
+          put_y(0u, sl, vy[h]);
           if (has_x) put(ub_hi, ub_lo, rx, 2 * (int)sl + qx, vx[h]);
+          __syncwarp();
+          tc05_wait_st();
+          tc05_fence_before();
           asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic writes -> the MMA's reads
           __syncwarp();
           if (lane == 0) {
@@ -499,14 +517,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
             const int nh = (kend - (kbeg + (uint32_t)it * BK)) > 8u ? 2 : 1;
             // per group of 8 k: two 4-k chunks per MMA, 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
             auto three = [&](uint32_t set, uint32_t pos, uint32_t acc) {
-              const uint32_t ya = smem_u32(images + set * CF::UMMA_ELEMS) + pos * 256u, xa = ya + 2 * BK * BN * 4;
-              const uint64_t ah = umma_desc_k(ya, 128, (BK / 4) * 128);
-              const uint64_t al = umma_desc_k(ya + BK * BN * 4, 128, (BK / 4) * 128);
+              const uint32_t xa = smem_u32(images + set * CF::UMMA_ELEMS) + pos * 256u;
+              const uint32_t ah = tmem + CF::A_COLS + set * CF::A_SLOT_COLS + pos * 16u, al = ah + 8u;
               const uint64_t bh = umma_desc_k(xa, 128, (BK / 4) * 128);
               const uint64_t bl = umma_desc_k(xa + BK * BM * 4, 128, (BK / 4) * 128);
-              tc05_mma_tf32(d_tmem, al, bh, IDESC, acc);
-              tc05_mma_tf32(d_tmem, ah, bl, IDESC, 1u);
-              tc05_mma_tf32(d_tmem, ah, bh, IDESC, 1u);
+              tc05_mma_tf32_ta(d_tmem, al, bh, IDESC, acc);
+              tc05_mma_tf32_ta(d_tmem, ah, bl, IDESC, 1u);
+              tc05_mma_tf32_ta(d_tmem, ah, bh, IDESC, 1u);
             };
             if (whole) {
               const uint32_t sl = u % SLOTS, use = u / SLOTS;
