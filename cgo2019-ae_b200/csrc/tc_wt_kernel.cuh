@@ -505,6 +505,8 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
     if (lane == 0) {
       constexpr uint32_t IDESC = umma_idesc_tf32(BN, BM);
       uint32_t u = 0, unit = 0;  // image units and accumulator segments so far
+      const uint32_t a0 = tmem + CF::A_COLS;
+      const uint64_t bh0 = umma_desc_k(smem_u32(images), 128, (BK / 4) * 128);
       bool alive = true;
         for (uint32_t tile = first; alive && tile < total; tile += step) {
         for (int seg = 0; alive && seg < nseg; ++seg, ++unit) {
@@ -515,12 +517,13 @@ __global__ void __launch_bounds__(CF::CTA_THREADS, 1) tc_wt_tf32_kernel(const __
           const int it_begin = seg_begin(seg), it_end = seg_begin(seg + 1);
           for (int it = it_begin; alive && it < it_end; ++it) {
             const int nh = (kend - (kbeg + (uint32_t)it * BK)) > 8u ? 2 : 1;
-            // per group of 8 k: two 4-k chunks per MMA, 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart
+            // per group of 8 k: two 4-k chunks per MMA, 128 bytes apart; 8-row groups (BK / 4) * 128 bytes apart.
+            // The descriptors of a set's groups differ from the first one's only in the address field (16-byte
+            // units, no carry out of it: the images lie in the first 256 KB): one addition each.
             auto three = [&](uint32_t set, uint32_t pos, uint32_t acc) {
-              const uint32_t xa = smem_u32(images + set * CF::UMMA_ELEMS) + pos * 256u;
-              const uint32_t ah = tmem + CF::A_COLS + set * CF::A_SLOT_COLS + pos * 16u, al = ah + 8u;
-              const uint64_t bh = umma_desc_k(xa, 128, (BK / 4) * 128);
-              const uint64_t bl = umma_desc_k(xa + BK * BM * 4, 128, (BK / 4) * 128);
+              const uint32_t ah = a0 + set * CF::A_SLOT_COLS + pos * 16u, al = ah + 8u;
+              const uint64_t bh = bh0 + (uint64_t)(set * (uint32_t)(CF::UMMA_ELEMS * 4 / 16) + pos * 16u);
+              const uint64_t bl = bh + (uint64_t)(BK * BM * 4 / 16);
               tc05_mma_tf32_ta(d_tmem, al, bh, IDESC, acc);
               tc05_mma_tf32_ta(d_tmem, ah, bl, IDESC, 1u);
               tc05_mma_tf32_ta(d_tmem, ah, bh, IDESC, 1u);
