@@ -385,7 +385,6 @@ int tc_plan_build(tc_plan* p, std::string* why) {
     bn = p->opt.tile_n;
     variant = p->opt.variant > 0 ? p->opt.variant - 1 : 0;
   } else {
-    auto waste = [&](int64_t n, int64_t b) { return (double)(((n + b - 1) / b) * b) / (double)n; };
     if (c.math == TC_MATH_DMMA) {
       // fp64 on the tensor pipe: the persistent kernels, chosen by a small cost model (this takes the place of the
       // reference's ranking of mappings by estimated DRAM transactions, cogent/src/algs/bases/cost_models.py:191-574).
