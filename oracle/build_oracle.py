@@ -14,7 +14,7 @@
                                on) and linked against the product library
                                through include/tc_b200_shim.h, so that the
                                drop-in symbol is exercised by the reference's
-                               own main() and judged by its own report
+                               own main() and checked by its own report
 
 No reference source is copied: every driver is compiled in place with its
 `main`, `post_Correctness` and `pre_Initializing_Input_Tensors` renamed through
